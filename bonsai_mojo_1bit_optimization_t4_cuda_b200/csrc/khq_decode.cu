@@ -1,0 +1,620 @@
+// khq_decode.cu -- two-region KHQ decode attention for sm_100a:
+//   khq_attn_compressed_kernel  compressed region, split-K partials (acc, max, sum_exp)
+//   khq_attn_reduce_kernel      LSE merge of the split partials
+//   khq_window_attn_kernel      raw fp16 ring window
+//   khq_merge_gate_kernel       LSE merge of the two regions + sigmoid output gate
+// and the launch_khq_* entry points with the reference's signatures.
+#include "khq_decode.cuh"
+
+namespace khq {
+
+// Nonzero once a bounded wait on an asynchronous copy has run out (read by khq_b200_device_status).
+__device__ int g_status = 0;
+
+// ------------------------------------------------------------------------------------------
+// Tile staging
+// ------------------------------------------------------------------------------------------
+// Copies `ntok` tokens (4*ntok rows) starting at token `tok0` of every payload array into one
+// stage.  Bulk path: thread 0 posts the byte count on the stage's mbarrier and issues eight
+// cp.async.bulk copies.  Plain path (odd tail or unaligned arrays): all threads copy with
+// 32-bit loads, then thread 0 arrives on the barrier.  The choice is CTA-uniform.
+__device__ __forceinline__ void stage_tile(const CompressedKV& P, unsigned char* stage,
+                                           uint64_t* bar, int tok0, int ntok, int tid) {
+    const size_t r0 = (size_t)tok0 * HKV;
+    const int rows = ntok * HKV;
+    const unsigned char* src[8] = {
+        reinterpret_cast<const unsigned char*>(P.k_mask) + r0 * 64,
+        P.k_payload + r0 * K_PAY,
+        P.v_payload + r0 * V_PAY,
+        reinterpret_cast<const unsigned char*>(P.k_norms) + r0 * 2,
+        reinterpret_cast<const unsigned char*>(P.k_r_norms) + r0 * 2,
+        reinterpret_cast<const unsigned char*>(P.v_norms) + r0 * 2,
+        reinterpret_cast<const unsigned char*>(P.v_r_norms) + r0 * 2,
+        P.v_shared_meta + r0 * 4};
+    const int dst[8] = {OFF_MASK, OFF_KPAY, OFF_VPAY, OFF_KN, OFF_KRN, OFF_VN, OFF_VRN, OFF_VSM};
+    const int bpr[8] = {64, K_PAY, V_PAY, 2, 2, 2, 2, 4};
+    const bool bulk = P.bulk_ok && ((tok0 & 1) == 0) && ((ntok & 1) == 0);
+    if (bulk) {
+        if (tid == 0) {
+            mbar_arrive_expect_tx(bar, (uint32_t)(rows * 220));
+#pragma unroll
+            for (int a = 0; a < 8; ++a)
+                bulk_g2s(stage + dst[a], src[a], (uint32_t)(rows * bpr[a]), bar);
+        }
+    } else {
+#pragma unroll
+        for (int a = 0; a < 8; ++a) {
+            const int words = rows * bpr[a] / 4;  // rows is a multiple of 4, so always whole words
+            const unsigned int* s = reinterpret_cast<const unsigned int*>(src[a]);
+            unsigned int* d = reinterpret_cast<unsigned int*>(stage + dst[a]);
+            for (int i = tid; i < words; i += DEC_THREADS) d[i] = s[i];
+        }
+        fence_proxy_async();
+        __syncthreads();
+        if (tid == 0) mbar_arrive(bar);
+    }
+}
+
+// RoPE cos/sin of one tile: entry (t, m) for position start_pos + tok0 + t and pair m < 32.
+// The angle is formed in double so that it stays exact at positions beyond 1e5.
+__device__ __forceinline__ void fill_rope(float2* tab, const float* freq, int pos0, int tid) {
+    for (int e = tid; e < TT * 32; e += DEC_THREADS) {
+        const int t = e >> 5, m = e & 31;
+        double th = (double)(pos0 + t) * (double)freq[m];
+        th -= rint(th * 0.15915494309189535) * 6.283185307179586;
+        float s, c;
+        __sincosf((float)th, &s, &c);
+        tab[e] = make_float2(c, s);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Compressed region
+// ------------------------------------------------------------------------------------------
+// grid = num_splits * cluster_size CTAs, cluster (cluster_size,1,1): the CTAs of one cluster
+// share one of the caller's splits and merge through distributed shared memory, so one partial
+// per split leaves the cluster whatever the cluster size.
+__global__ void __launch_bounds__(DEC_THREADS, 1)
+khq_attn_compressed_kernel(const __half* __restrict__ q, CompressedKV P, float* __restrict__ out_attn,
+                           float* __restrict__ out_partial, int num_splits, int L_q, int l_idx,
+                           int s_limit, float scale) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kvh = warp & 3, sub = warp >> 2;
+    const int csize = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
+    const int split_id = blockIdx.x / csize;
+
+    float2* rope_tab = reinterpret_cast<float2*>(smem + SM_ROPE);
+    float* rotor_s = reinterpret_cast<float*>(smem + SM_ROTOR);
+    float* freq_s = reinterpret_cast<float*>(smem + SM_FREQ);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM_BARS);
+    int* flags = reinterpret_cast<int*>(smem + SM_BARS + NSTAGE * 8);
+
+    // ---- token range of this split, then of this CTA inside the split ----------------------
+    int s_lo = 0, s_hi = s_limit;
+    if (num_splits > 1) {
+        const int per = (s_limit + num_splits - 1) / num_splits;
+        s_lo = min(split_id * per, s_limit);
+        s_hi = min(s_lo + per, s_limit);
+    }
+    const int len = s_hi - s_lo;
+    const int chunk = (((len + csize - 1) / csize) + 1) & ~1;
+    const int my_lo = min(s_lo + crank * chunk, s_hi);
+    const int my_hi = min(my_lo + chunk, s_hi);
+    const int base = my_lo & ~1;
+    const int ntiles = (my_hi > my_lo) ? (my_hi - base + TT - 1) / TT : 0;
+
+    // ---- one-time set-up ---------------------------------------------------------------------
+    if (tid < 32) freq_s[tid] = powf(P.rope_base, -2.0f * (float)tid / 64.0f);
+    if (tid == 0) {
+        for (int s = 0; s < NSTAGE; ++s) mbar_init(&bars[s], 1);
+        fence_barrier_init();
+        flags[0] = 1;  // K rotor is the identity until a lane finds otherwise
+    }
+    __syncthreads();
+    // K rotor -> shared memory as fp32, 36-float stride per owning lane (conflict-free float4)
+    for (int e = tid; e < NP * 16; e += DEC_THREADS) {
+        const float v = __half2float(P.k_rotor[e]);
+        const int patch = e >> 4, idx = e & 15;
+        rotor_s[(patch >> 1) * 36 + (patch & 1) * 16 + idx] = v;
+        const float want = ((idx >> 2) == (idx & 3)) ? 1.0f : 0.0f;
+        if (v != want) flags[0] = 0;
+    }
+    if (ntiles > 0) fill_rope(rope_tab, freq_s, P.start_pos + base, tid);
+
+    // per-lane constants
+    float cbase[8], dinv[8], qv[NREP][8], c3[2][2];
+    {
+        const uint4 cr = *reinterpret_cast<const uint4*>(P.cents_k + 2 * D + lane * 8);
+        const uint4 dr = *reinterpret_cast<const uint4*>(P.d_k + lane * 8);
+        const __half* hc = reinterpret_cast<const __half*>(&cr);
+        const __half* hd = reinterpret_cast<const __half*>(&dr);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            cbase[j] = __half2float(hc[j]);
+            dinv[j] = (1.0f / 256.0f) / (__half2float(hd[j]) + 1e-8f);
+        }
+#pragma unroll
+        for (int h = 0; h < NREP; ++h) {
+            const int head = kvh * NREP + h;
+            const uint4 qr = *reinterpret_cast<const uint4*>(q + ((size_t)head * L_q + l_idx) * 2 * D + lane * 8);
+            const __half* hq = reinterpret_cast<const __half*>(&qr);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) qv[h][j] = __half2float(hq[j]) * scale;
+        }
+#pragma unroll
+        for (int p = 0; p < 2; ++p) {
+            c3[p][0] = __half2float(P.cents_v[0 * D + (lane * 2 + p) * 4 + 3]) * P.alpha_v;
+            c3[p][1] = __half2float(P.cents_v[1 * D + (lane * 2 + p) * 4 + 3]) * P.alpha_v;
+        }
+    }
+    WarpState st;
+    st.init();
+
+    // ---- prologue: fill NSTAGE-1 stages --------------------------------------------------------
+#pragma unroll 1
+    for (int i = 0; i < NSTAGE - 1 && i < ntiles; ++i) {
+        const int tok0 = base + i * TT;
+        stage_tile(P, smem + SM_STAGES + i * STAGE_BYTES, &bars[i], tok0, min(TT, P.c_len - tok0), tid);
+    }
+    __syncthreads();
+    const bool rotor_identity = flags[0] != 0;
+
+    // ---- main loop ---------------------------------------------------------------------------
+#pragma unroll 1
+    for (int i = 0; i < ntiles; ++i) {
+        const int stg = i % NSTAGE;
+        {
+            const int nx = i + NSTAGE - 1;
+            if (nx < ntiles) {
+                const int tok0 = base + nx * TT;
+                stage_tile(P, smem + SM_STAGES + (nx % NSTAGE) * STAGE_BYTES, &bars[nx % NSTAGE], tok0,
+                           min(TT, P.c_len - tok0), tid);
+            }
+        }
+        if (i + 1 < ntiles)
+            fill_rope(rope_tab + ((i + 1) & 1) * TT * 32, freq_s, P.start_pos + base + (i + 1) * TT, tid);
+        mbar_wait_bounded(&bars[stg], (uint32_t)((i / NSTAGE) & 1), &g_status);
+
+        const unsigned char* S = smem + SM_STAGES + stg * STAGE_BYTES;
+        const float2* rt = rope_tab + (i & 1) * TT * 32;
+        const int tile0 = base + i * TT;
+
+#pragma unroll 1
+        for (int t = sub; t < TT; t += DEC_WPK) {
+            const int s_abs = tile0 + t;
+            if (s_abs < my_lo || s_abs >= my_hi) continue;  // warp-uniform
+            const int row = t * HKV + kvh;
+
+            // ===== K: code words -> rotated-domain values ===================================
+            const unsigned int* kp = reinterpret_cast<const unsigned int*>(S + OFF_KPAY + row * K_PAY);
+            const unsigned int mw = reinterpret_cast<const unsigned int*>(S + OFF_MASK + row * 64)[lane >> 1];
+            const unsigned int ow = (lane & 1) ? (mw >> 16) : (mw & 0xFFFFu);
+            const int cnt = __popc(ow & (ow >> 1) & 0x5555u);
+            int incl = cnt;
+#pragma unroll
+            for (int dlt = 1; dlt < 32; dlt <<= 1) {
+                const int tmp = __shfl_up_sync(0xFFFFFFFFu, incl, dlt);
+                if (lane >= dlt) incl += tmp;
+            }
+            int jcur = incl - cnt;  // ordinal of this lane's first outlier
+            float mult = (float)kp[0] / 1000.0f;
+            if (mult < 0.1f || mult > 10.0f || isnan(mult)) mult = 1.0f;
+            const float rscale = hbits2f(reinterpret_cast<const uint16_t*>(S + OFF_KRN)[row]);
+            const float knorm = hbits2f(reinterpret_cast<const uint16_t*>(S + OFF_KN)[row]);
+            const int j0 = min(jcur, MAX_OUT);
+            unsigned int nwin, swin;
+            {
+                const int nb = 32 + 4 * j0;       // bit offset of residual nibble j0
+                nwin = __funnelshift_r(kp[nb >> 5], kp[(nb >> 5) + 1], nb & 31);
+                const int sb = 232 + j0;          // bit offset of sign bit j0
+                swin = __funnelshift_r(kp[sb >> 5], kp[min((sb >> 5) + 1, 9)], sb & 31);
+            }
+            const float kscale = P.alpha_k * knorm;
+            float y[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const unsigned sym = (ow >> (2 * j)) & 3u;
+                const bool is3 = sym == 3u;
+                const bool valid = is3 && (jcur < MAX_OUT);
+                const float code = valid ? (float)(nwin & 15u) : 0.0f;
+                const bool pos_sign = valid && (swin & 1u);
+                float mag = (sym != 0u) ? cbase[j] * mult : 0.0f;
+                mag = fmaf(code, rscale, mag);
+                const bool neg = (sym == 1u) || (is3 && !pos_sign);
+                y[j] = (neg ? -mag : mag) * kscale;
+                if (valid) { nwin >>= 4; swin >>= 1; }
+                jcur += is3 ? 1 : 0;
+            }
+            // inverse rotor (transpose of the compress-side rotor)
+            if (!rotor_identity) {
+                float z[8];
+#pragma unroll
+                for (int p = 0; p < 2; ++p)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const float4 rr = *reinterpret_cast<const float4*>(&rotor_s[lane * 36 + p * 16 + c * 4]);
+                        z[p * 4 + c] = y[p * 4 + 0] * rr.x + y[p * 4 + 1] * rr.y + y[p * 4 + 2] * rr.z +
+                                       y[p * 4 + 3] * rr.w;
+                    }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) y[j] = z[j];
+            }
+            fwht256_lane8(y, lane);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) y[j] *= dinv[j];
+            // RoPE on dims 0..63: lanes 0..3 hold m = 8*lane+j, lanes 4..7 hold m+32
+            {
+                const float2* rl = rt + t * 32 + (lane & 3) * 8;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float other = __shfl_xor_sync(0xFFFFFFFFu, y[j], 4);
+                    if (lane < 8) {
+                        const float2 cs = rl[j];
+                        y[j] = (lane < 4) ? (y[j] * cs.x - other * cs.y) : (other * cs.y + y[j] * cs.x);
+                    }
+                }
+            }
+            float sc[NREP];
+#pragma unroll
+            for (int h = 0; h < NREP; ++h) {
+                float a = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) a = fmaf(qv[h][j], y[j], a);
+                sc[h] = a;
+            }
+            reduce6(sc, lane);
+            float pw[NREP];
+            softmax_step(st, sc, pw);
+
+            // ===== V: code words -> rotated-domain row ======================================
+            const unsigned int* vp = reinterpret_cast<const unsigned int*>(S + OFF_VPAY + row * V_PAY);
+            const float vnorm = hbits2f(reinterpret_cast<const uint16_t*>(S + OFF_VN)[row]);
+            const float energy = hbits2f(reinterpret_cast<const uint16_t*>(S + OFF_VRN)[row]);
+            const float smv = reinterpret_cast<const float*>(S + OFF_VSM)[row];
+            const float pre_v = P.alpha_v * vnorm * energy;
+            const float pre_res = smv * vnorm * (1.0f / 7.0f);
+            const int bo = 24 * (lane & 3);
+            const int wi = 3 * (lane >> 2) + (bo >> 5);
+            const unsigned int f24 = __funnelshift_r(vp[wi], vp[wi + 1], bo & 31) & 0xFFFFFFu;
+            const unsigned int hb = (vp[24 + (lane >> 4)] >> (2 * (lane & 15))) & 3u;
+            float v[8];
+#pragma unroll
+            for (int p = 0; p < 2; ++p) {
+                const unsigned f = (f24 >> (12 * p)) & 0xFFFu;
+                const unsigned code = (f & 0x7Fu) | (((hb >> p) & 1u) << 7);
+                const unsigned short* e =
+                    reinterpret_cast<const unsigned short*>(P.vq) + ((size_t)(lane * 2 + p) * 256 + code) * 3;
+                v[p * 4 + 0] = hbits2f(__ldg(e + 0)) * pre_v;
+                v[p * 4 + 1] = hbits2f(__ldg(e + 1)) * pre_v;
+                v[p * 4 + 2] = hbits2f(__ldg(e + 2)) * pre_v;
+                const float c = ((f >> 7) & 1u) ? c3[p][1] : c3[p][0];
+                v[p * 4 + 3] = fmaf(c, vnorm, ((float)((f >> 8) & 0xFu) - 8.0f) * pre_res);
+            }
+            accumulate_v(st, pw, v);
+        }
+        __syncthreads();  // every warp is done with this stage and this rope buffer
+    }
+
+    // ---- merge warps -> CTA -> cluster, then the V epilogue on cluster rank 0 ------------------
+    merge_cta_and_cluster(st, reinterpret_cast<float*>(smem + SM_MERGE_A), kvh, sub, lane);
+    if (crank == 0 && sub == 0) {
+        float dvi[8];
+        {
+            const uint4 dr = *reinterpret_cast<const uint4*>(P.d_v + lane * 8);
+            const __half* hd = reinterpret_cast<const __half*>(&dr);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) dvi[j] = (1.0f / 16.0f) / (__half2float(hd[j]) + 1e-8f);
+        }
+        float rv[2][16];
+#pragma unroll
+        for (int p = 0; p < 2; ++p)
+#pragma unroll
+            for (int i = 0; i < 16; ++i) rv[p][i] = __half2float(P.v_rotor[(lane * 2 + p) * 16 + i]);
+#pragma unroll
+        for (int h = 0; h < NREP; ++h) {
+            float z[8];
+#pragma unroll
+            for (int p = 0; p < 2; ++p)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    float a = 0.0f;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) a = fmaf(st.acc[h][p * 4 + k], rv[p][c * 4 + k], a);
+                    z[p * 4 + c] = a;
+                }
+            fwht256_lane8(z, lane);
+            const int total_id = (kvh * NREP + h) * L_q + l_idx;
+            float* ob = (num_splits > 1)
+                            ? out_partial + ((size_t)total_id * num_splits + split_id) * PART
+                            : out_attn + (size_t)total_id * PART;
+#pragma unroll
+            for (int j = 0; j < 8; j += 2)
+                *reinterpret_cast<float2*>(ob + lane * 8 + j) = make_float2(z[j] * dvi[j], z[j + 1] * dvi[j + 1]);
+            if (lane == 0) {
+                ob[D] = st.m[h];
+                ob[D + 1] = st.l[h];
+            }
+        }
+    }
+}
+
+// LSE merge over splits: partial (nq, splits, 258) -> out (nq, 258), unnormalised.
+__global__ void __launch_bounds__(D) khq_attn_reduce_kernel(const float* __restrict__ partial,
+                                                            float* __restrict__ out, int num_splits) {
+    const int qid = blockIdx.x, d = threadIdx.x;
+    const float* base = partial + (size_t)qid * num_splits * PART;
+    float M = NEG_BIG;
+    for (int sp = 0; sp < num_splits; ++sp) M = fmaxf(M, base[(size_t)sp * PART + D]);
+    float num = 0.0f, den = 0.0f;
+    for (int sp = 0; sp < num_splits; ++sp) {
+        const float* p = base + (size_t)sp * PART;
+        const float w = __expf(p[D] - M);
+        num = fmaf(p[d], w, num);
+        den = fmaf(p[D + 1], w, den);
+    }
+    float* o = out + (size_t)qid * PART;
+    o[d] = num;
+    if (d == 0) {
+        o[D] = M;
+        o[D + 1] = den;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Raw ring window
+// ------------------------------------------------------------------------------------------
+// One cluster; slot (win_start + s) % ring_cap, rows token-major (slot*H_kv + kv)*D.  Token s is
+// served by warp (kv, sub) of CTA c when s % (cluster_size*DEC_WPK) == c*DEC_WPK + sub.
+__global__ void __launch_bounds__(DEC_THREADS, 1)
+khq_window_attn_kernel(const __half* __restrict__ q, const __half* __restrict__ ring_k,
+                       const __half* __restrict__ ring_v, float* __restrict__ out, int win_start,
+                       int win_len, int ring_cap, float scale) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kvh = warp & 3, sub = warp >> 2;
+    const int csize = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
+
+    float qv[NREP][8];
+#pragma unroll
+    for (int h = 0; h < NREP; ++h) {
+        const uint4 qr = *reinterpret_cast<const uint4*>(q + (size_t)(kvh * NREP + h) * 2 * D + lane * 8);
+        const __half* hq = reinterpret_cast<const __half*>(&qr);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) qv[h][j] = __half2float(hq[j]) * scale;
+    }
+    WarpState st;
+    st.init();
+    const int stride = csize * DEC_WPK;
+#pragma unroll 1
+    for (int s = crank * DEC_WPK + sub; s < win_len; s += stride) {
+        const int slot = (win_start + s) % ring_cap;
+        const size_t off = ((size_t)slot * HKV + kvh) * D + lane * 8;
+        const uint4 kr = *reinterpret_cast<const uint4*>(ring_k + off);
+        const uint4 vr = *reinterpret_cast<const uint4*>(ring_v + off);
+        const __half* hk = reinterpret_cast<const __half*>(&kr);
+        const __half* hv = reinterpret_cast<const __half*>(&vr);
+        float sc[NREP];
+#pragma unroll
+        for (int h = 0; h < NREP; ++h) {
+            float a = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) a = fmaf(qv[h][j], __half2float(hk[j]), a);
+            sc[h] = a;
+        }
+        reduce6(sc, lane);
+        float pw[NREP];
+        softmax_step(st, sc, pw);
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __half2float(hv[j]);
+        accumulate_v(st, pw, v);
+    }
+    merge_cta_and_cluster(st, reinterpret_cast<float*>(smem), kvh, sub, lane);
+    if (crank == 0 && sub == 0) {
+#pragma unroll
+        for (int h = 0; h < NREP; ++h) {
+            float* ob = out + (size_t)(kvh * NREP + h) * PART;
+#pragma unroll
+            for (int j = 0; j < 8; j += 2)
+                *reinterpret_cast<float2*>(ob + lane * 8 + j) = make_float2(st.acc[h][j], st.acc[h][j + 1]);
+            if (lane == 0) {
+                ob[D] = st.m[h];
+                ob[D + 1] = st.l[h];
+            }
+        }
+    }
+}
+
+// LSE merge of the two regions, /(den + 1e-8), sigmoid gate, fp16 store.
+__global__ void khq_merge_gate_kernel(const float* __restrict__ attn_c, const float* __restrict__ attn_w,
+                                      const __half* __restrict__ q_gate, __half* __restrict__ out, int H_q,
+                                      int d_v, int has_w) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= H_q * d_v) return;
+    const int h = i / d_v, d = i % d_v;
+    const float* cc = attn_c + (size_t)h * (d_v + 2);
+    float num = cc[d], den = cc[d_v + 1];
+    if (has_w) {
+        const float* cw = attn_w + (size_t)h * (d_v + 2);
+        const float mc = cc[d_v], mw = cw[d_v];
+        const float M = fmaxf(mc, mw);
+        const float wc = __expf(mc - M), ww = __expf(mw - M);
+        num = num * wc + cw[d] * ww;
+        den = den * wc + cw[d_v + 1] * ww;
+    }
+    const float val = num / (den + 1e-8f);
+    const float g = __half2float(q_gate[(size_t)h * 2 * d_v + d_v + d]);
+    out[i] = __float2half(val * (1.0f / (1.0f + __expf(-g))));
+}
+
+__global__ void khq_gather_q_kernel(const __half* __restrict__ q_gate, __half* __restrict__ q_out, int H_q,
+                                    int d_v) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= H_q * d_v) return;
+    q_out[i] = q_gate[(size_t)(i / d_v) * 2 * d_v + (i % d_v)];
+}
+
+// ------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------
+static inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+template <typename Kernel, typename... Args>
+static cudaError_t launch_cluster(Kernel kernel, unsigned grid, unsigned cluster, size_t smem_bytes,
+                                  cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(DEC_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
+static cudaError_t ensure_smem_attrs() {
+    static cudaError_t once = [] {
+        cudaError_t e = cudaFuncSetAttribute(khq_attn_compressed_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SM_TOTAL);
+        if (e != cudaSuccess) return e;
+        return cudaFuncSetAttribute(khq_window_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    2 * HKV * MERGE_FLOATS * 4);
+    }();
+    return once;
+}
+
+}  // namespace khq
+
+using namespace khq;
+
+extern "C" int launch_khq_attn_fp16(const void* q, const void* k_payload, const void* v_payload,
+                                    const void* v_shared_meta, const void* k_mask, const void* k_norms,
+                                    const void* k_r_norms, const void* v_norms, const void* v_r_norms,
+                                    const void* centroids_k, const void* centroids_v,
+                                    const void* vq_centroids, const void* k_rotor, const void* v_rotor,
+                                    const void* d_vec_k, const void* d_vec_v, void* out_attn,
+                                    void* out_partial, int num_queries, int num_heads, int L_q, int c_len,
+                                    int stride_s, int n_rep, float scale, float alpha_k, float alpha_v,
+                                    float rope_base, int start_pos, int num_splits, cudaStream_t stream) {
+    (void)stride_s;
+    if (num_queries <= 0 || c_len <= 0) return -100;
+    if (num_splits < 1) num_splits = 1;
+    if (num_splits > 1 && out_partial == nullptr) return -101;
+    if (n_rep != NREP || num_heads != HQ || L_q < 1 || num_queries != num_heads * L_q) return -103;
+    const void* tables[] = {q, centroids_k, centroids_v, vq_centroids, k_rotor, v_rotor, d_vec_k, d_vec_v};
+    for (const void* t : tables)
+        if (!aligned(t, 16)) return -104;
+    const void* arrays[] = {k_payload, v_payload, v_shared_meta, k_mask, k_norms, k_r_norms, v_norms, v_r_norms};
+    bool bulk_ok = true;
+    for (const void* a : arrays) {
+        if (!aligned(a, 4)) return -104;
+        bulk_ok = bulk_ok && aligned(a, 16);
+    }
+    if (!aligned(out_attn, 8) || (out_partial && !aligned(out_partial, 8))) return -104;
+    cudaError_t err = ensure_smem_attrs();
+    if (err != cudaSuccess) return static_cast<int>(err);
+
+    CompressedKV P;
+    P.k_payload = static_cast<const unsigned char*>(k_payload);
+    P.v_payload = static_cast<const unsigned char*>(v_payload);
+    P.v_shared_meta = static_cast<const unsigned char*>(v_shared_meta);
+    P.k_mask = static_cast<const unsigned int*>(k_mask);
+    P.k_norms = static_cast<const __half*>(k_norms);
+    P.k_r_norms = static_cast<const __half*>(k_r_norms);
+    P.v_norms = static_cast<const __half*>(v_norms);
+    P.v_r_norms = static_cast<const __half*>(v_r_norms);
+    P.cents_k = static_cast<const __half*>(centroids_k);
+    P.cents_v = static_cast<const __half*>(centroids_v);
+    P.vq = static_cast<const __half*>(vq_centroids);
+    P.k_rotor = static_cast<const __half*>(k_rotor);
+    P.v_rotor = static_cast<const __half*>(v_rotor);
+    P.d_k = static_cast<const __half*>(d_vec_k);
+    P.d_v = static_cast<const __half*>(d_vec_v);
+    P.alpha_k = alpha_k;
+    P.alpha_v = alpha_v;
+    P.rope_base = rope_base;
+    P.start_pos = start_pos;
+    P.c_len = c_len;
+    P.bulk_ok = bulk_ok ? 1 : 0;
+
+    for (int l = 0; l < L_q; ++l) {
+        const int s_limit = (L_q > 1) ? (c_len < l + 1 ? c_len : l + 1) : c_len;
+        const int per = (s_limit + num_splits - 1) / num_splits;
+        // CTAs per split: aim at ~TT tokens per CTA, at most a portable cluster of 8.
+        int cluster = (per + TT - 1) / TT;
+        if (cluster < 1) cluster = 1;
+        if (cluster > 8) cluster = 8;
+        err = launch_cluster(khq_attn_compressed_kernel, (unsigned)(num_splits * cluster), (unsigned)cluster,
+                             (size_t)SM_TOTAL, stream, static_cast<const __half*>(q), P,
+                             static_cast<float*>(out_attn), static_cast<float*>(out_partial), num_splits, L_q,
+                             l, s_limit, scale);
+        if (err != cudaSuccess) return static_cast<int>(err);
+    }
+    if (num_splits > 1) {
+        khq_attn_reduce_kernel<<<(unsigned)num_queries, D, 0, stream>>>(
+            static_cast<const float*>(out_partial), static_cast<float*>(out_attn), num_splits);
+        err = cudaGetLastError();
+        if (err != cudaSuccess) return static_cast<int>(err);
+    }
+    return 0;
+}
+
+extern "C" int launch_khq_window_attn_fp16(const void* q, const void* ring_k, const void* ring_v,
+                                           void* out_attn, int win_start, int win_len, int ring_cap,
+                                           int H_q, int H_kv, int d, float scale, cudaStream_t stream) {
+    if (H_q <= 0 || win_len <= 0) return -100;
+    if (H_q != HQ || H_kv != HKV || d != D || ring_cap <= 0) return -103;
+    if (!aligned(q, 16) || !aligned(ring_k, 16) || !aligned(ring_v, 16) || !aligned(out_attn, 8)) return -104;
+    cudaError_t err = ensure_smem_attrs();
+    if (err != cudaSuccess) return static_cast<int>(err);
+    int cluster = (win_len + DEC_WPK * 4 - 1) / (DEC_WPK * 4);
+    if (cluster < 1) cluster = 1;
+    if (cluster > 8) cluster = 8;
+    err = launch_cluster(khq_window_attn_kernel, (unsigned)cluster, (unsigned)cluster,
+                         (size_t)(2 * HKV * MERGE_FLOATS * 4), stream, static_cast<const __half*>(q),
+                         static_cast<const __half*>(ring_k), static_cast<const __half*>(ring_v),
+                         static_cast<float*>(out_attn), win_start, win_len, ring_cap, scale);
+    return (err == cudaSuccess) ? 0 : static_cast<int>(err);
+}
+
+extern "C" int launch_khq_merge_gate_fp16(const void* attn_c, const void* attn_w, const void* q_gate,
+                                          void* out, int H_q, int d, int has_w, cudaStream_t stream) {
+    if (H_q <= 0 || d <= 0) return -100;
+    const int total = H_q * d, threads = 256;
+    khq_merge_gate_kernel<<<(total + threads - 1) / threads, threads, 0, stream>>>(
+        static_cast<const float*>(attn_c), static_cast<const float*>(attn_w),
+        static_cast<const __half*>(q_gate), static_cast<__half*>(out), H_q, d, has_w);
+    const cudaError_t err = cudaGetLastError();
+    return (err == cudaSuccess) ? 0 : static_cast<int>(err);
+}
+
+extern "C" int launch_khq_gather_q_fp16(const void* q_gate, void* q_out, int H_q, int d,
+                                        cudaStream_t stream) {
+    if (H_q <= 0 || d <= 0) return -100;
+    const int total = H_q * d, threads = 256;
+    khq_gather_q_kernel<<<(total + threads - 1) / threads, threads, 0, stream>>>(
+        static_cast<const __half*>(q_gate), static_cast<__half*>(q_out), H_q, d);
+    const cudaError_t err = cudaGetLastError();
+    return (err == cudaSuccess) ? 0 : static_cast<int>(err);
+}
+
+static void* g_khq_slots[3] = {nullptr, nullptr, nullptr};
+extern "C" void* khq_state_slot(int which) {
+    if (which < 0 || which > 2) which = 0;
+    return static_cast<void*>(&g_khq_slots[which]);
+}
+extern "C" int bonsai_cuda_sm75_init(void) { return 0; }
+extern "C" const char* khq_b200_version(void) { return "khq-b200 0.1 sm_100a"; }
+extern "C" int khq_b200_device_status(void) {
+    int v = 0;
+    const cudaError_t err = cudaMemcpyFromSymbol(&v, khq::g_status, sizeof(int));
+    return (err == cudaSuccess) ? v : -static_cast<int>(err);
+}

@@ -1,0 +1,70 @@
+"""Launch wrappers over the C ABI -- the counterpart of the reference's ``khq_*_try_launch``
+functions (``src/ops.mojo:1101-1279``), taking torch CUDA tensors instead of raw pointers.
+
+Differences from the reference wrappers: the library is loaded once (the reference re-opens it
+and re-reads ``BONSAI_DISABLE_CUDA_FFI`` on every call), launches go to torch's current stream
+(the reference passes a NULL stream), and a non-zero return raises instead of returning False.
+"""
+from __future__ import annotations
+
+from . import lib as _lib
+from .lib import check, current_stream, ptr
+
+
+class CudaOps:
+    """The product's only compute backend: every method is one call into the CUDA library."""
+
+    name = "cuda"
+
+    def __init__(self):
+        self.lib = _lib.load()
+
+    # -- launch_khq_compress_fp16 ------------------------------------------------------------
+    def compress(self, x, d_vec, rotor, centroids, vq_centroids, out_mask, out_norms, out_r_norms,
+                 out_payload, out_shared_meta, n, d, ts, alpha, is_v):
+        rc = self.lib.launch_khq_compress_fp16(
+            ptr(x), ptr(d_vec), ptr(rotor), ptr(centroids), ptr(vq_centroids), ptr(out_mask),
+            ptr(out_norms), ptr(out_r_norms), ptr(out_payload), ptr(out_shared_meta), int(n),
+            int(d), float(ts), float(alpha), 1 if is_v else 0, current_stream())
+        check("launch_khq_compress_fp16", rc)
+
+    # -- launch_khq_attn_fp16 ----------------------------------------------------------------
+    def attn(self, q, k_payload, v_payload, v_shared_meta, k_mask, k_norms, k_r_norms, v_norms,
+             v_r_norms, centroids_k, centroids_v, vq_centroids, k_rotor, v_rotor, d_vec_k, d_vec_v,
+             out_attn, out_partial, num_queries, num_heads, L_q, c_len, stride_s, n_rep, scale,
+             alpha_k, alpha_v, rope_base, start_pos, num_splits):
+        rc = self.lib.launch_khq_attn_fp16(
+            ptr(q), ptr(k_payload), ptr(v_payload), ptr(v_shared_meta), ptr(k_mask), ptr(k_norms),
+            ptr(k_r_norms), ptr(v_norms), ptr(v_r_norms), ptr(centroids_k), ptr(centroids_v),
+            ptr(vq_centroids), ptr(k_rotor), ptr(v_rotor), ptr(d_vec_k), ptr(d_vec_v),
+            ptr(out_attn), ptr(out_partial), int(num_queries), int(num_heads), int(L_q),
+            int(c_len), int(stride_s), int(n_rep), float(scale), float(alpha_k), float(alpha_v),
+            float(rope_base), int(start_pos), int(num_splits), current_stream())
+        check("launch_khq_attn_fp16", rc)
+
+    # -- launch_khq_window_attn_fp16 -----------------------------------------------------------
+    def window_attn(self, q, ring_k, ring_v, out_attn, win_start, win_len, ring_cap, H_q, H_kv, d,
+                    scale):
+        rc = self.lib.launch_khq_window_attn_fp16(
+            ptr(q), ptr(ring_k), ptr(ring_v), ptr(out_attn), int(win_start), int(win_len),
+            int(ring_cap), int(H_q), int(H_kv), int(d), float(scale), current_stream())
+        check("launch_khq_window_attn_fp16", rc)
+
+    # -- launch_khq_merge_gate_fp16, with the argument selection of khq_merge_gate_try
+    #    (src/ops.mojo:1255-1279): window only -> attn_c := attn_w and has_w = 0 ----------------
+    def merge_gate(self, attn_c, attn_w, q_gate, out, H_q, d, has_w, has_c):
+        src_c = attn_c if has_c else attn_w
+        rc = self.lib.launch_khq_merge_gate_fp16(
+            ptr(src_c), ptr(attn_w), ptr(q_gate), ptr(out), int(H_q), int(d),
+            1 if (has_w and has_c) else 0, current_stream())
+        check("launch_khq_merge_gate_fp16", rc)
+
+    # -- ring appends (khq_ring_dual_sm75_gpu / copy_vec_sm75_gpu,
+    #    src/kernels/elementwise_sm75.mojo:277-312): device-to-device copies ------------------
+    def ring_write(self, dst_row, src):
+        dst_row.copy_(src.reshape(dst_row.shape), non_blocking=True)
+
+    def synchronize(self):
+        import torch
+
+        torch.cuda.current_stream().synchronize()

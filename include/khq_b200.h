@@ -1,0 +1,119 @@
+/*
+ * khq_b200.h -- C ABI of libbonsai_khq_b200.so: Bonsai-27B full-attention path over a
+ * KHQ-compressed KV cache, hand-written for NVIDIA B200 (sm_100a).
+ *
+ * Section 1 re-exports, with identical names, argument order and meaning, the entry points the
+ * reference host binds by dlsym() for this path (reference paths are relative to the reference
+ * project's root).  Section 2 are additions the reference has no counterpart for (batching,
+ * fusion, context-parallel partials, prefill).
+ *
+ * Conventions shared by every launcher, as in the reference:
+ *   - returns int: 0 = enqueued; negative = contract violation (nothing was launched);
+ *     positive = the cudaError_t reported by cudaGetLastError() after the launch;
+ *   - the last argument is the CUDA stream to launch on (the reference host passes NULL);
+ *   - every pointer is a DEVICE pointer owned by the caller; launchers allocate nothing, never
+ *     synchronise and keep no reference to the buffers after the kernels have run;
+ *   - shapes are Bonsai-27B's attention: head_dim D = 256, H_q = 24, H_kv = 4 (n_rep = 6),
+ *     rotary dims 0..63 in half-split pairs (m, m+32).  Other H_kv / n_rep return -103.
+ *
+ * Fixed byte layouts (rows are token-major with the kv-heads interleaved: row = token*H_kv + kv):
+ *   k_mask        (rows, 16) uint32   2-bit symbol per dim, dim i at bits 2*(i%16) of word i/16
+ *   k_payload     (rows, 40) uint8    [0:4] u32 base multiplier*1000, [4:29] 4-bit outlier
+ *                                     residuals, [29:36] outlier sign bits, [36] 0x02, [37:40] 0
+ *   v_payload     (rows, 104) uint8   24 words of 8x12-bit patch fields + 2 words of VQ bit 7
+ *   *_norms, *_r_norms (rows) fp16;   v_shared_meta (rows) fp32 stored in 4 bytes
+ *   q / q_gate    (H_q, 2*D) fp16     query at [0,D), output-gate logits at [D,2D) of each head
+ *   partial/attn  (.., D+2) fp32      unnormalised accumulator[D], running max, sum of exps
+ */
+#ifndef KHQ_B200_H_
+#define KHQ_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef KHQ_B200_STREAM_T
+#define KHQ_B200_STREAM_T
+typedef struct CUstream_st* khq_stream_t; /* == cudaStream_t */
+#endif
+
+/* ------------------------------------------------------------------------------------------
+ * Section 1: drop-in replacements for the reference's FFI symbols
+ * ---------------------------------------------------------------------------------------- */
+
+/* Replaces bonsai_cuda_sm75_init (src/csrc/qmv_sm75_kernel.cu:3974). Always 0. */
+int bonsai_cuda_sm75_init(void);
+
+/* Replaces khq_state_slot (src/csrc/qmv_sm75_kernel.cu:3968-3972; bound at src/ops.mojo:1025-1040):
+ * address of one of three static void* cells the host parks module state in; `which` outside
+ * 0..2 is clamped to 0. */
+void* khq_state_slot(int which);
+
+/* Replaces launch_khq_compress_fp16 (src/csrc/qmv_sm75_kernel.cu:4279-4310; typedef
+ * src/ops.mojo:1060-1073).  n rows of d==256 fp16 values -> KHQ code words.  is_v==0: writes
+ * out_mask, out_norms, out_r_norms (residual scale), out_payload (40 B/row) and zeroes
+ * out_shared_meta.  is_v==1: writes out_norms, out_r_norms (energy correction), out_payload
+ * (104 B/row) and out_shared_meta (fp32 max residual); out_mask is not touched.
+ * Returns -100 if n<=0 or d!=256.  Code words are bit-identical to the reference kernel's. */
+int launch_khq_compress_fp16(const void* x, const void* d_vec, const void* rotor,
+                             const void* centroids, const void* vq_centroids, void* out_mask,
+                             void* out_norms, void* out_r_norms, void* out_payload,
+                             void* out_shared_meta, int n, int d, float threshold_scale,
+                             float alpha, int is_v, khq_stream_t stream);
+
+/* Replaces launch_khq_attn_fp16 (src/csrc/qmv_sm75_kernel.cu:4314-4375; typedef
+ * src/ops.mojo:1075-1098).  Attention of num_queries = num_heads*L_q query rows over c_len
+ * compressed tokens, positions start_pos..start_pos+c_len-1.  Writes out_attn
+ * (num_queries, D+2).  When num_splits>1, out_partial (num_queries, num_splits, D+2) receives
+ * the per-split partials in the reference layout and is merged into out_attn.
+ * stride_s is ignored.  Returns -100 if num_queries<=0 or c_len<=0, -101 if num_splits>1 and
+ * out_partial is NULL, -103 for unsupported head shapes. */
+int launch_khq_attn_fp16(const void* q, const void* k_payload, const void* v_payload,
+                         const void* v_shared_meta, const void* k_mask, const void* k_norms,
+                         const void* k_r_norms, const void* v_norms, const void* v_r_norms,
+                         const void* centroids_k, const void* centroids_v,
+                         const void* vq_centroids, const void* k_rotor, const void* v_rotor,
+                         const void* d_vec_k, const void* d_vec_v, void* out_attn,
+                         void* out_partial, int num_queries, int num_heads, int L_q, int c_len,
+                         int stride_s, int n_rep, float scale, float alpha_k, float alpha_v,
+                         float rope_base, int start_pos, int num_splits, khq_stream_t stream);
+
+/* Replaces launch_khq_window_attn_fp16 (src/csrc/qmv_sm75_kernel.cu:4378-4396; typedef
+ * src/ops.mojo:1181-1196).  Attention over win_len raw fp16 ring slots (win_start+s) % ring_cap;
+ * ring rows are token-major (slot*H_kv + kv)*d; K is already RoPE'd.  Writes (H_q, D+2)
+ * unnormalised.  Returns -100 if H_q<=0 or win_len<=0, -103 for unsupported shapes. */
+int launch_khq_window_attn_fp16(const void* q, const void* ring_k, const void* ring_v,
+                                void* out_attn, int win_start, int win_len, int ring_cap, int H_q,
+                                int H_kv, int d, float scale, khq_stream_t stream);
+
+/* Replaces launch_khq_merge_gate_fp16 (src/csrc/qmv_sm75_kernel.cu:4414-4429; typedef
+ * src/ops.mojo:1245-1252).  LSE-merges the compressed and window partials when has_w!=0
+ * (otherwise uses attn_c alone), divides by (den + 1e-8), multiplies by sigmoid(gate) and
+ * writes fp16 (H_q, d).  Returns -100 if H_q<=0 or d<=0. */
+int launch_khq_merge_gate_fp16(const void* attn_c, const void* attn_w, const void* q_gate,
+                               void* out, int H_q, int d, int has_w, khq_stream_t stream);
+
+/* Replaces launch_khq_gather_q_fp16 (src/csrc/qmv_sm75_kernel.cu:4399-4411): de-interleaves the
+ * query half of q_gate into (H_q, d).  Used only by the reference's dump path. */
+int launch_khq_gather_q_fp16(const void* q_gate, void* q_out, int H_q, int d,
+                             khq_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Section 2: additions (no counterpart in the reference)
+ * ---------------------------------------------------------------------------------------- */
+
+/* Library identification: "khq-b200 <version> sm_100a". */
+const char* khq_b200_version(void);
+
+/* Word written by the decode kernels when a bounded wait on an asynchronous copy gave up
+ * (0 = never).  Reads the device flag of the current device with a blocking 4-byte copy, so
+ * call it outside the hot loop.  Returns the flag, or -(cudaError_t) on failure. */
+int khq_b200_device_status(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KHQ_B200_H_ */

@@ -1,0 +1,69 @@
+"""Seeded test cases shared by the parity tests and by the golden-vector generator."""
+from __future__ import annotations
+
+import numpy as np
+
+from bonsai_mojo_1bit_optimization_t4_cuda_b200 import synth
+from bonsai_mojo_1bit_optimization_t4_cuda_b200.calib import KhqLayerTables
+
+H_Q, H_KV, D = 24, 4, 256
+SCALE = 1.0 / 16.0
+
+# name -> make_tables keyword arguments
+VARIANTS = {
+    # what the reference's calibration produces in shape: K-static centroids (base multiplier
+    # clamps to 1), random V rotor; K rotor random so the inverse-rotor path is exercised
+    "calib": dict(vq_scale=1.0 / 16.0),
+    # BASELINE's literal codebook (N(0,1)) and the identity K rotor the real calibration leaves
+    "n01_idrot": dict(vq_scale=1.0, k_rotor_identity=True),
+    # unscaled centroids: the per-row adaptive base multiplier is live (c_mult != 1000)
+    "adaptive": dict(vq_scale=1.0 / 16.0, adaptive_mult=True),
+}
+
+
+def make_case(seed: int, n_tok: int, variant: str = "calib", layer_id: int = 3, q_pos=None):
+    """n_tok tokens of K (un-RoPE'd and RoPE'd at positions 0..n_tok-1), V, one q_gate at the last
+    position, and tables.  All arrays numpy; fp16 where the device expects fp16."""
+    rng = np.random.default_rng(seed)
+    sk, sv = synth.channel_scales(rng), synth.channel_scales(rng)
+    k_u, v = synth.make_kv(rng, n_tok, sk, sv)
+    k_r = synth.partial_rope(k_u, np.arange(n_tok)[:, None].repeat(H_KV, 1))
+    tb = synth.make_tables(rng, layer_id, k_u.reshape(-1, D), v.reshape(-1, D), **VARIANTS[variant])
+    q_gate = synth.make_q_gate(rng, n_tok - 1 if q_pos is None else q_pos)
+    return dict(k_unroped=k_u, k_roped=k_r, v=v, q_gate=q_gate, tables=tb, f16=tb.as_f16())
+
+
+def compress_with(ops_compress, case, n_tok: int):
+    """Run K and V compression of the first n_tok tokens through ``ops_compress`` (a callable with
+    the oracle's ``compress`` signature) and return the eight payload arrays."""
+    tb, f = case["tables"], case["f16"]
+    rows = n_tok * H_KV
+    ck = ops_compress(case["k_unroped"][:n_tok].reshape(-1, D), f["d_k"], f["rotor_k"], f["cents_k"],
+                      f["cents_k"], rows, tb.ts_k, tb.alpha_k, False)
+    cv = ops_compress(case["v"][:n_tok].reshape(-1, D), f["d_v"], f["rotor_v"], f["cents_v"], f["vq"],
+                      rows, tb.ts_v, tb.alpha_v, True)
+    return dict(k_mask=ck["mask"], k_payload=ck["payload"], k_norms=ck["norms"], k_r_norms=ck["r_norms"],
+                v_payload=cv["payload"], v_norms=cv["norms"], v_r_norms=cv["r_norms"],
+                v_shared_meta=cv["shared_meta"], near_ties=cv["near_ties"])
+
+
+def tables_dict(f16):
+    return dict(cents_k=f16["cents_k"], cents_v=f16["cents_v"], vq=f16["vq"], rotor_k=f16["rotor_k"],
+                rotor_v=f16["rotor_v"], d_k=f16["d_k"], d_v=f16["d_v"])
+
+
+def attention_close(got, ref, atol=2e-3, rtol=1e-2):
+    """The path's floating-point bar: |got-ref| <= 2e-3 + 1e-2*|ref| elementwise.
+    Returns (ok, max_abs_err, worst_excess)."""
+    got = np.asarray(got, np.float64)
+    ref = np.asarray(ref, np.float64)
+    err = np.abs(got - ref)
+    lim = atol + rtol * np.abs(ref)
+    return bool((err <= lim).all()), float(err.max()), float((err - lim).max())
+
+
+def normalised(partial):
+    """(.., 258) unnormalised partial -> acc / sum_exp, the quantity that is comparable across
+    different split/merge orders."""
+    p = np.asarray(partial, np.float64)
+    return p[..., :D] / np.maximum(p[..., D + 1:D + 2], 1e-30)
