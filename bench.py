@@ -1,0 +1,380 @@
+#!/usr/bin/env python
+"""Benchmark of the KHQ decode-attention path on B200.
+
+Workload (BASELINE.json configs[3]): batched decode of 256 independent sequences with contexts
+uniform in [4096, 32768] (compressed prefix + raw window of 128..256 tokens), 16 attention layers,
+H_q 24 / H_kv 4 / head_dim 256, fp16 payloads, fp32 accumulate.  A "step" generates one token for
+every sequence: per layer one batched launch over all sequences.  Seeded synthetic state (the
+reference measures on real weights, which are not available): see the package's ``engine.py``.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  ``value``: tokens/s with all state resident in HBM.  ``e2e``: the same
+step through ``BatchEngine.decode_step`` with this step's q/K/V coming from pinned host memory
+and the outputs copied back.  ``roofline``: algorithmic payload bytes of one layer launch divided
+by that launch's CUDA-event duration, against the measured copy bandwidth.  ``cpu_baseline``: the
+CPU port of the reference math (oracle/) on a bounded sample of the same workload.
+With N>1 (torchrun, one rank per GPU) every rank owns its own 256 sequences: sharding is by
+sequence with no collective, so scaling is weak by construction.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+import numpy as np  # noqa: E402
+
+METRIC = "KHQ batched decode attention throughput (16 attention layers)"
+UNIT = "tok/s"
+N_LAYERS = 16
+LAYER_IDS = [4 * i + 3 for i in range(N_LAYERS)]  # Bonsai-27B's full-attention layers
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--seqs", type=int, default=256, help="sequences per GPU")
+    ap.add_argument("--ctx-min", type=int, default=4096)
+    ap.add_argument("--ctx-max", type=int, default=32768)
+    ap.add_argument("--layers", type=int, default=N_LAYERS)
+    ap.add_argument("--cpu-sample-mult", type=int, default=4, help="CPU sample = mult x host threads sequences")
+    ap.add_argument("--no-extras", action="store_true")
+    return ap.parse_args()
+
+
+def workload(args, rank: int):
+    """Per-rank contexts: total ctx ~ U{ctx_min..ctx_max}, window ~ U{128..256}, compressed length
+    = 128 * floor((ctx - window) / 128)."""
+    from bonsai_mojo_1bit_optimization_t4_cuda_b200 import synth
+
+    rng = np.random.default_rng(synth.seed_for(3, 0, rank))
+    ctx = rng.integers(args.ctx_min, args.ctx_max + 1, size=args.seqs)
+    win = rng.integers(128, 257, size=args.seqs)
+    c_len = 128 * ((ctx - win) // 128)
+    win = np.minimum(ctx - c_len, 256)  # whatever is left over stays raw, at most a full ring
+    return c_len.astype(np.int64), win.astype(np.int64)
+
+
+def make_tables(n_layers: int):
+    from bonsai_mojo_1bit_optimization_t4_cuda_b200 import synth
+
+    out = []
+    for li in range(n_layers):
+        rng = np.random.default_rng(synth.seed_for(3, LAYER_IDS[li % N_LAYERS]))
+        k, v = synth.make_kv(rng, 128)
+        # identity K rotor: what the reference's calibration writes (src/khq/calib.mojo:386-390)
+        out.append(synth.make_tables(rng, LAYER_IDS[li % N_LAYERS], k.reshape(-1, 256), v.reshape(-1, 256),
+                                     vq_scale=1.0 / 16.0, k_rotor_identity=True))
+    return out
+
+
+class ClockSampler:
+    """nvidia-smi clocks/throttle reasons sampled every 200 ms while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows, self.proc, self.gpu = [], None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for nm, val in zip(names, r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU port of the reference math on a bounded sample (test infrastructure used as a baseline only)
+# ------------------------------------------------------------------------------------------------
+def random_payload(rng, n_tok: int):
+    """Valid KHQ code words drawn directly (the decode cost does not depend on their values):
+    symbols with the Gaussian cell probabilities of the 0.47/1.60 sigma thresholds, at most 50
+    outliers per row, random residual nibbles / signs / VQ fields, plausible fp16 norms."""
+    rows = n_tok * 4
+    lut = np.repeat(np.arange(4, dtype=np.uint32), [93, 67, 68, 28])  # 0.36 / 0.26 / 0.27 / 0.11
+    sym = lut[rng.integers(0, 256, size=(rows, 256), dtype=np.uint8)]
+    over = (np.cumsum(sym == 3, axis=1) > 50) & (sym == 3)
+    sym[over] = 2
+    sh = (2 * (np.arange(256) % 16)).astype(np.uint32)
+    mask = np.zeros((rows, 16), np.uint32)
+    for w in range(16):
+        mask[:, w] = (sym[:, 16 * w:16 * w + 16] << sh[:16]).sum(axis=1, dtype=np.uint32)
+    kp = rng.integers(0, 256, size=(rows, 40), dtype=np.uint8)
+    kp[:, 0:4] = np.frombuffer(np.uint32(1000).tobytes(), np.uint8)
+    kp[:, 36] = 2
+    kp[:, 37:] = 0
+    vp = rng.integers(0, 256, size=(rows, 104), dtype=np.uint8)
+    f16 = lambda lo, hi: rng.uniform(lo, hi, size=rows).astype(np.float16)
+    return dict(k_mask=mask, k_payload=kp, v_payload=vp, k_norms=f16(10, 40), k_r_norms=f16(0.01, 0.1),
+                v_norms=f16(10, 40), v_r_norms=f16(0.5, 1.5),
+                v_shared_meta=np.ascontiguousarray(rng.uniform(0.01, 0.1, size=rows).astype(np.float32)).view(np.uint8).reshape(rows, 4))
+
+
+class CpuSample:
+    """n_seqs sequences of the workload's context distribution, ONE layer, decoded through the
+    oracle (compressed region + window + merge + gate): one sequence per host thread."""
+
+    def __init__(self, args, threads: int):
+        # one oracle call spreads over the 4 kv-heads with OpenMP; sequences run on a thread pool
+        os.environ.setdefault("OMP_NUM_THREADS", "4")
+        from bonsai_mojo_1bit_optimization_t4_cuda_b200 import synth
+        from oracle import khq_oracle as O
+
+        O.build()
+        self.O, self.ops, self.threads, self.args = O, O.OracleOps(), threads, args
+        self.pool = max(1, threads // 4)
+        n_seqs = min(args.seqs, 64, max(2, args.cpu_sample_mult * self.pool))
+        c_len, win = workload(args, 0)
+        self.tb = make_tables(1)[0]
+        self.f = self.tb.as_f16()
+        rng = np.random.default_rng(synth.seed_for(3, 3, 999))
+        self.probs = []
+        bases = [random_payload(rng, int(c_len[:n_seqs].max())) for _ in range(min(4, n_seqs))]
+        for i in range(n_seqs):
+            cl, wl = int(c_len[i]), int(win[i])
+            p = {k: v[:cl * 4] for k, v in bases[i % len(bases)].items()}
+            p.update(ring_k=rng.standard_normal((256, 4, 256)).astype(np.float16),
+                     ring_v=rng.standard_normal((256, 4, 256)).astype(np.float16), cl=cl, wl=wl, ws=cl % 256,
+                     q=synth.make_q_gate(rng, cl + wl - 1))
+            self.probs.append(p)
+        self.n_seqs = n_seqs
+        self.ctx = (c_len[:n_seqs] + win[:n_seqs])
+
+    def _one(self, p):
+        f, tb, ops = self.f, self.tb, self.ops
+        ac = np.zeros((24, 258), np.float32)
+        aw = np.zeros((24, 258), np.float32)
+        out = np.zeros((24, 256), np.float16)
+        ops.attn(p["q"], p["k_payload"], p["v_payload"], p["v_shared_meta"], p["k_mask"], p["k_norms"], p["k_r_norms"],
+                 p["v_norms"], p["v_r_norms"], f["cents_k"], f["cents_v"], f["vq"], f["rotor_k"], f["rotor_v"],
+                 f["d_k"], f["d_v"], ac, None, 24, 24, 1, p["cl"], p["cl"], 6, 1 / 16, tb.alpha_k, tb.alpha_v, 1e7, 0, 1)
+        ops.window_attn(p["q"], p["ring_k"], p["ring_v"], aw, p["ws"], p["wl"], 256, 24, 4, 256, 1 / 16)
+        ops.merge_gate(ac, aw, p["q"], out, 24, 256, True, True)
+        return out
+
+    def time_once(self) -> float:
+        from concurrent.futures import ThreadPoolExecutor
+
+        t0 = time.perf_counter()
+        with ThreadPoolExecutor(self.pool) as ex:
+            list(ex.map(self._one, self.probs))
+        return time.perf_counter() - t0
+
+    def result(self, dt: float):
+        # n_seqs sequences advanced by one LAYER in dt; one token needs `layers` layer steps
+        tok_s = self.n_seqs / (dt * self.args.layers)
+        return {"value": tok_s, "unit": UNIT, "cores": self.threads, "kind": "port",
+                "sample": f"{self.n_seqs} sequences (ctx {int(self.ctx.min())}..{int(self.ctx.max())}) x 1 layer in "
+                          f"{dt:.2f} s on {self.threads} host threads, scaled to {self.args.layers} layers; "
+                          "code words drawn at random (decode cost is value-independent)"}
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    t_all = time.perf_counter()
+    cores = os.cpu_count() or 1
+    smp = CpuSample(args, cores)
+    for _ in range(min(args.warmup, 1)):
+        smp.time_once()
+    reps = max(1, min(args.steps, 5))
+    dt = float(np.mean([smp.time_once() for _ in range(reps)]))
+    base = smp.result(dt)
+    v = base["value"]
+    line = {
+        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * args.seqs / v, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config_dict(args, world), "cpu_baseline": base,
+        "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference has no CPU KHQ kernel: this is the CPU port of its math (oracle/) on the host cores; "
+                "timed repetitions of the bounded sample: %d" % reps,
+        "wall_s": time.perf_counter() - t_all,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def config_dict(args, world):
+    return {"workload": "BASELINE configs[3]: batched decode, %d sequences per GPU, ctx U[%d,%d] = KHQ-compressed "
+                        "prefix + raw window 128..256, %d attention layers, H_q 24 / H_kv 4 / d 256" %
+                        (args.seqs, args.ctx_min, args.ctx_max, args.layers),
+            "sequences_per_gpu": args.seqs, "layers": args.layers, "sharding": "by sequence, no collective",
+            "l2": "inputs larger than L2: every layer launch streams GBs of payload against a 126 MB L2",
+            "world": world}
+
+
+# ------------------------------------------------------------------------------------------------
+def main():
+    args = parse()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from bonsai_mojo_1bit_optimization_t4_cuda_b200.engine import BatchEngine
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    c_len, win = workload(args, rank)
+    tables = make_tables(args.layers)
+    t_setup = time.perf_counter()
+    eng = BatchEngine(tables, c_len, win, device=f"cuda:{local_rank}")
+    eng.fill_synthetic(20260914 + 1000 * 3 + rank)
+    torch.cuda.synchronize()
+    setup_s = time.perf_counter() - t_setup
+    bytes_layer = eng.algorithmic_bytes_per_layer
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    stream = torch.cuda.current_stream()
+
+    # ---- resident timing: K steps, per-launch events for the roofline --------------------------
+    def resident_step(evs=None):
+        for l in range(eng.L):
+            if evs is not None:
+                e0 = torch.cuda.Event(enable_timing=True)
+                e1 = torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+            eng.attention_resident(l)
+            if evs is not None:
+                e1.record(stream)
+                evs.append((e0, e1))
+
+    for _ in range(args.warmup):
+        resident_step()
+    sampler = ClockSampler(local_rank)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    evs = []
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record(stream)
+    for _ in range(args.steps):
+        resident_step(evs)
+    s1.record(stream)
+    barrier()
+    ms_total = s0.elapsed_time(s1)
+    launch_ms = [a.elapsed_time(b) for a, b in evs]
+
+    # ---- end-to-end timing: host buffers in, host buffers out ----------------------------------
+    g = torch.Generator().manual_seed(7 + rank)
+    for t in (eng.h_q, eng.h_kr, eng.h_ku, eng.h_v):
+        t.copy_(torch.randn(t.shape, generator=g).half())
+    for _ in range(args.warmup):
+        eng.decode_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        out = eng.decode_step()
+        stream.synchronize()  # the host consumes this step's outputs before the next token
+        _ = float(out[0, 0, 0])
+    e1.record(stream)
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    status = eng.lib.khq_b200_device_status()
+
+    t = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total, ms_e2e = float(t[0]), float(t[1])
+
+    if rank == 0:
+        peaks = {}
+        pk = ROOT / "MEASURED_PEAKS.json"
+        if pk.exists():
+            peaks = json.loads(pk.read_text())
+        peak_gbs = float(peaks.get("hbm_gbs", 6650.0))
+        peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
+        ms_step = ms_total / args.steps
+        value = args.seqs * world / (ms_step / 1e3)
+        e2e_val = args.seqs * world / (ms_e2e / args.steps / 1e3)
+        avg_launch_ms = float(np.mean(launch_ms))
+        achieved = bytes_layer / (avg_launch_ms / 1e3) / 1e9
+        cfg = config_dict(args, world)
+        cfg["l2"] = "inputs larger than L2 (%.2f GB of payload per layer launch vs 126 MB L2)" % (bytes_layer / 1e9)
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
+            "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": eng.h2d_bytes_per_step,
+                    "d2h_bytes_per_step": eng.d2h_bytes_per_step, "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": 2 * eng.L * args.steps,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
+                         "frac": achieved / peak_gbs, "traffic": None, "peak_source": peak_src,
+                         "kernel": "khq_decode_batched_kernel (+ its merge kernel and a 256 B memset, inside the same events)",
+                         "algorithmic_bytes_per_launch": bytes_layer, "avg_launch_ms": avg_launch_ms},
+            "us_per_layer_step_per_sequence": 1e3 * avg_launch_ms / args.seqs,
+            "clocks": clocks, "device_status": status, "setup_s": setup_s,
+        }
+        if not args.no_extras and world == 1:
+            try:
+                smp = CpuSample(args, os.cpu_count() or 1)
+                line["cpu_baseline"] = smp.result(smp.time_once())
+            except Exception as e:  # the checker is optional equipment of the box
+                line["cpu_baseline"] = {"error": repr(e)}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

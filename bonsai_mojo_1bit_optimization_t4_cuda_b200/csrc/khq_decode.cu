@@ -71,47 +71,31 @@ __device__ __forceinline__ void fill_rope(float2* tab, const float* freq, int po
 // ------------------------------------------------------------------------------------------
 // Compressed region
 // ------------------------------------------------------------------------------------------
-// grid = num_splits * cluster_size CTAs, cluster (cluster_size,1,1): the CTAs of one cluster
-// share one of the caller's splits and merge through distributed shared memory, so one partial
-// per split leaves the cluster whatever the cluster size.
-__global__ void __launch_bounds__(DEC_THREADS, 1)
-khq_attn_compressed_kernel(const __half* __restrict__ q, CompressedKV P, float* __restrict__ out_attn,
-                           float* __restrict__ out_partial, int num_splits, int L_q, int l_idx,
-                           int s_limit, float scale) {
-    extern __shared__ __align__(128) unsigned char smem[];
-    cg::cluster_group cluster = cg::this_cluster();
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int kvh = warp & 3, sub = warp >> 2;
-    const int csize = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
-    const int split_id = blockIdx.x / csize;
+// V codebook in shared memory: entry (code, patch) is 4 halfs (3 used) at slot
+// code*64 + (patch>>1) + 32*(patch&1).  A lane reads patches 2*lane and 2*lane+1, so the 16
+// lanes of an LDS.64 phase always hit 16 different bank pairs whatever their codes are.
+__device__ __forceinline__ void load_codebook(unsigned short* vq_s, const __half* vq, int tid) {
+    const unsigned int* src = reinterpret_cast<const unsigned int*>(vq);
+    for (int w = tid; w < NP * 256 * 3 / 2; w += DEC_THREADS) {
+        const unsigned int two = __ldg(src + w);
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+            const int hidx = 2 * w + b;
+            const int entry = hidx / 3, k = hidx - entry * 3;
+            const int patch = entry >> 8, code = entry & 255;
+            vq_s[(code * 64 + (patch >> 1) + 32 * (patch & 1)) * 4 + k] = (unsigned short)(two >> (16 * b));
+        }
+    }
+}
 
-    float2* rope_tab = reinterpret_cast<float2*>(smem + SM_ROPE);
+// Per-CTA constants of one (sequence, layer): must be followed by __syncthreads().
+// Returns nothing; flags[0] ends up 1 when the K rotor is the identity.
+__device__ __forceinline__ void setup_tables(unsigned char* smem, const CompressedKV& P, int tid) {
     float* rotor_s = reinterpret_cast<float*>(smem + SM_ROTOR);
     float* freq_s = reinterpret_cast<float*>(smem + SM_FREQ);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM_BARS);
     int* flags = reinterpret_cast<int*>(smem + SM_BARS + NSTAGE * 8);
-
-    // ---- token range of this split, then of this CTA inside the split ----------------------
-    int s_lo = 0, s_hi = s_limit;
-    if (num_splits > 1) {
-        const int per = (s_limit + num_splits - 1) / num_splits;
-        s_lo = min(split_id * per, s_limit);
-        s_hi = min(s_lo + per, s_limit);
-    }
-    const int len = s_hi - s_lo;
-    const int chunk = (((len + csize - 1) / csize) + 1) & ~1;
-    const int my_lo = min(s_lo + crank * chunk, s_hi);
-    const int my_hi = min(my_lo + chunk, s_hi);
-    const int base = my_lo & ~1;
-    const int ntiles = (my_hi > my_lo) ? (my_hi - base + TT - 1) / TT : 0;
-
-    // ---- one-time set-up ---------------------------------------------------------------------
     if (tid < 32) freq_s[tid] = powf(P.rope_base, -2.0f * (float)tid / 64.0f);
-    if (tid == 0) {
-        for (int s = 0; s < NSTAGE; ++s) mbar_init(&bars[s], 1);
-        fence_barrier_init();
-        flags[0] = 1;  // K rotor is the identity until a lane finds otherwise
-    }
+    if (tid == 0) flags[0] = 1;  // K rotor is the identity until a thread finds otherwise
     __syncthreads();
     // K rotor -> shared memory as fp32, 36-float stride per owning lane (conflict-free float4)
     for (int e = tid; e < NP * 16; e += DEC_THREADS) {
@@ -121,6 +105,28 @@ khq_attn_compressed_kernel(const __half* __restrict__ q, CompressedKV P, float* 
         const float want = ((idx >> 2) == (idx & 3)) ? 1.0f : 0.0f;
         if (v != want) flags[0] = 0;
     }
+}
+
+// Attention of the six query heads of this warp's kv-head over compressed tokens
+// [my_lo, my_hi) of P, accumulated into st (rotated V domain).  All DEC_THREADS threads of the
+// CTA call it together; tiles are dealt to the DEC_WPK warps of a kv-head token by token.
+// `bar_uses` counts how often each stage barrier has completed so far in this CTA's life (the
+// barriers are initialised once per CTA and reused across work items).
+template <bool VQS>
+__device__ __forceinline__ void compressed_range(unsigned char* smem, const __half* __restrict__ q,
+                                                 size_t q_head_stride, const CompressedKV& P, int my_lo,
+                                                 int my_hi, float scale, WarpState& st, unsigned& tiles_done) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kvh = warp & 3, sub = warp >> 2;
+    float2* rope_tab = reinterpret_cast<float2*>(smem + SM_ROPE);
+    const float* rotor_s = reinterpret_cast<const float*>(smem + SM_ROTOR);
+    const float* freq_s = reinterpret_cast<const float*>(smem + SM_FREQ);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM_BARS);
+    const int* flags = reinterpret_cast<const int*>(smem + SM_BARS + NSTAGE * 8);
+    const unsigned short* vq_s = reinterpret_cast<const unsigned short*>(smem + SM_VQ);
+
+    const int base = my_lo & ~1;
+    const int ntiles = (my_hi > my_lo) ? (my_hi - base + TT - 1) / TT : 0;
     if (ntiles > 0) fill_rope(rope_tab, freq_s, P.start_pos + base, tid);
 
     // per-lane constants
@@ -137,8 +143,7 @@ khq_attn_compressed_kernel(const __half* __restrict__ q, CompressedKV P, float* 
         }
 #pragma unroll
         for (int h = 0; h < NREP; ++h) {
-            const int head = kvh * NREP + h;
-            const uint4 qr = *reinterpret_cast<const uint4*>(q + ((size_t)head * L_q + l_idx) * 2 * D + lane * 8);
+            const uint4 qr = *reinterpret_cast<const uint4*>(q + (size_t)(kvh * NREP + h) * q_head_stride + lane * 8);
             const __half* hq = reinterpret_cast<const __half*>(&qr);
 #pragma unroll
             for (int j = 0; j < 8; ++j) qv[h][j] = __half2float(hq[j]) * scale;
@@ -149,14 +154,15 @@ khq_attn_compressed_kernel(const __half* __restrict__ q, CompressedKV P, float* 
             c3[p][1] = __half2float(P.cents_v[1 * D + (lane * 2 + p) * 4 + 3]) * P.alpha_v;
         }
     }
-    WarpState st;
-    st.init();
 
     // ---- prologue: fill NSTAGE-1 stages --------------------------------------------------------
+    const unsigned t0 = tiles_done;  // tile i of this range uses stage (t0+i)%NSTAGE
 #pragma unroll 1
     for (int i = 0; i < NSTAGE - 1 && i < ntiles; ++i) {
         const int tok0 = base + i * TT;
-        stage_tile(P, smem + SM_STAGES + i * STAGE_BYTES, &bars[i], tok0, min(TT, P.c_len - tok0), tid);
+        const unsigned g = t0 + i;
+        stage_tile(P, smem + SM_STAGES + (g % NSTAGE) * STAGE_BYTES, &bars[g % NSTAGE], tok0,
+                   min(TT, P.c_len - tok0), tid);
     }
     __syncthreads();
     const bool rotor_identity = flags[0] != 0;
@@ -164,23 +170,24 @@ khq_attn_compressed_kernel(const __half* __restrict__ q, CompressedKV P, float* 
     // ---- main loop ---------------------------------------------------------------------------
 #pragma unroll 1
     for (int i = 0; i < ntiles; ++i) {
-        const int stg = i % NSTAGE;
+        const unsigned g = t0 + i;
+        const int stg = g % NSTAGE;
         {
             const int nx = i + NSTAGE - 1;
             if (nx < ntiles) {
                 const int tok0 = base + nx * TT;
-                stage_tile(P, smem + SM_STAGES + (nx % NSTAGE) * STAGE_BYTES, &bars[nx % NSTAGE], tok0,
+                const unsigned gn = t0 + nx;
+                stage_tile(P, smem + SM_STAGES + (gn % NSTAGE) * STAGE_BYTES, &bars[gn % NSTAGE], tok0,
                            min(TT, P.c_len - tok0), tid);
             }
         }
         if (i + 1 < ntiles)
             fill_rope(rope_tab + ((i + 1) & 1) * TT * 32, freq_s, P.start_pos + base + (i + 1) * TT, tid);
-        mbar_wait_bounded(&bars[stg], (uint32_t)((i / NSTAGE) & 1), &g_status);
+        mbar_wait_bounded(&bars[stg], (uint32_t)((g / NSTAGE) & 1), &g_status);
 
         const unsigned char* S = smem + SM_STAGES + stg * STAGE_BYTES;
         const float2* rt = rope_tab + (i & 1) * TT * 32;
         const int tile0 = base + i * TT;
-
 #pragma unroll 1
         for (int t = sub; t < TT; t += DEC_WPK) {
             const int s_abs = tile0 + t;
@@ -284,11 +291,18 @@ khq_attn_compressed_kernel(const __half* __restrict__ q, CompressedKV P, float* 
             for (int p = 0; p < 2; ++p) {
                 const unsigned f = (f24 >> (12 * p)) & 0xFFFu;
                 const unsigned code = (f & 0x7Fu) | (((hb >> p) & 1u) << 7);
-                const unsigned short* e =
-                    reinterpret_cast<const unsigned short*>(P.vq) + ((size_t)(lane * 2 + p) * 256 + code) * 3;
-                v[p * 4 + 0] = hbits2f(__ldg(e + 0)) * pre_v;
-                v[p * 4 + 1] = hbits2f(__ldg(e + 1)) * pre_v;
-                v[p * 4 + 2] = hbits2f(__ldg(e + 2)) * pre_v;
+                if (VQS) {
+                    const uint2 e = *reinterpret_cast<const uint2*>(vq_s + (code * 64 + 32 * p + lane) * 4);
+                    v[p * 4 + 0] = hbits2f((unsigned short)(e.x & 0xFFFFu)) * pre_v;
+                    v[p * 4 + 1] = hbits2f((unsigned short)(e.x >> 16)) * pre_v;
+                    v[p * 4 + 2] = hbits2f((unsigned short)(e.y & 0xFFFFu)) * pre_v;
+                } else {
+                    const unsigned short* e =
+                        reinterpret_cast<const unsigned short*>(P.vq) + ((size_t)(lane * 2 + p) * 256 + code) * 3;
+                    v[p * 4 + 0] = hbits2f(__ldg(e + 0)) * pre_v;
+                    v[p * 4 + 1] = hbits2f(__ldg(e + 1)) * pre_v;
+                    v[p * 4 + 2] = hbits2f(__ldg(e + 2)) * pre_v;
+                }
                 const float c = ((f >> 7) & 1u) ? c3[p][1] : c3[p][0];
                 v[p * 4 + 3] = fmaf(c, vnorm, ((float)((f >> 8) & 0xFu) - 8.0f) * pre_res);
             }
@@ -297,46 +311,99 @@ khq_attn_compressed_kernel(const __half* __restrict__ q, CompressedKV P, float* 
         __syncthreads();  // every warp is done with this stage and this rope buffer
     }
 
-    // ---- merge warps -> CTA -> cluster, then the V epilogue on cluster rank 0 ------------------
-    merge_cta_and_cluster(st, reinterpret_cast<float*>(smem + SM_MERGE_A), kvh, sub, lane);
-    if (crank == 0 && sub == 0) {
-        float dvi[8];
-        {
-            const uint4 dr = *reinterpret_cast<const uint4*>(P.d_v + lane * 8);
-            const __half* hd = reinterpret_cast<const __half*>(&dr);
+    tiles_done = t0 + (unsigned)ntiles;
+}
+
+// Inverse V rotor + FWHT + /16/(d_v+1e-8) of the merged state of head h, stored as one
+// (acc[256], max, sum_exp) record.  Called by one warp per kv-head.
+__device__ __forceinline__ void v_epilogue_store(const WarpState& st, const CompressedKV& P, int lane,
+                                                 float* const (&ob)[NREP]) {
+    float dvi[8];
+    {
+        const uint4 dr = *reinterpret_cast<const uint4*>(P.d_v + lane * 8);
+        const __half* hd = reinterpret_cast<const __half*>(&dr);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) dvi[j] = (1.0f / 16.0f) / (__half2float(hd[j]) + 1e-8f);
-        }
-        float rv[2][16];
+        for (int j = 0; j < 8; ++j) dvi[j] = (1.0f / 16.0f) / (__half2float(hd[j]) + 1e-8f);
+    }
+    float rv[2][16];
+#pragma unroll
+    for (int p = 0; p < 2; ++p)
+#pragma unroll
+        for (int i = 0; i < 16; ++i) rv[p][i] = __half2float(P.v_rotor[(lane * 2 + p) * 16 + i]);
+#pragma unroll
+    for (int h = 0; h < NREP; ++h) {
+        float z[8];
 #pragma unroll
         for (int p = 0; p < 2; ++p)
 #pragma unroll
-            for (int i = 0; i < 16; ++i) rv[p][i] = __half2float(P.v_rotor[(lane * 2 + p) * 16 + i]);
+            for (int c = 0; c < 4; ++c) {
+                float a = 0.0f;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) a = fmaf(st.acc[h][p * 4 + k], rv[p][c * 4 + k], a);
+                z[p * 4 + c] = a;
+            }
+        fwht256_lane8(z, lane);
+#pragma unroll
+        for (int j = 0; j < 8; j += 2)
+            *reinterpret_cast<float2*>(ob[h] + lane * 8 + j) = make_float2(z[j] * dvi[j], z[j + 1] * dvi[j + 1]);
+        if (lane == 0) {
+            ob[h][D] = st.m[h];
+            ob[h][D + 1] = st.l[h];
+        }
+    }
+}
+
+// grid = num_splits * cluster_size CTAs, cluster (cluster_size,1,1): the CTAs of one cluster
+// share one of the caller's splits and merge through distributed shared memory, so one partial
+// per split leaves the cluster whatever the cluster size.
+template <bool VQS>
+__global__ void __launch_bounds__(DEC_THREADS, 1)
+khq_attn_compressed_kernel(const __half* __restrict__ q, CompressedKV P, float* __restrict__ out_attn,
+                           float* __restrict__ out_partial, int num_splits, int L_q, int l_idx,
+                           int s_limit, float scale) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kvh = warp & 3, sub = warp >> 2;
+    const int csize = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
+    const int split_id = blockIdx.x / csize;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM_BARS);
+
+    // ---- token range of this split, then of this CTA inside the split ----------------------
+    int s_lo = 0, s_hi = s_limit;
+    if (num_splits > 1) {
+        const int per = (s_limit + num_splits - 1) / num_splits;
+        s_lo = min(split_id * per, s_limit);
+        s_hi = min(s_lo + per, s_limit);
+    }
+    const int len = s_hi - s_lo;
+    const int chunk = (((len + csize - 1) / csize) + 1) & ~1;
+    const int my_lo = min(s_lo + crank * chunk, s_hi);
+    const int my_hi = min(my_lo + chunk, s_hi);
+
+    if (tid == 0) {
+        for (int s = 0; s < NSTAGE; ++s) mbar_init(&bars[s], 1);
+        fence_barrier_init();
+    }
+    setup_tables(smem, P, tid);
+    if (VQS && my_hi > my_lo) load_codebook(reinterpret_cast<unsigned short*>(smem + SM_VQ), P.vq, tid);
+    WarpState st;
+    st.init();
+    unsigned tiles_done = 0;
+    compressed_range<VQS>(smem, q + (size_t)l_idx * 2 * D, (size_t)L_q * 2 * D, P, my_lo, my_hi, scale, st,
+                          tiles_done);
+
+    // ---- merge warps -> CTA -> cluster, then the V epilogue on cluster rank 0 ------------------
+    merge_cta_and_cluster(st, reinterpret_cast<float*>(smem + SM_MERGE_A), kvh, sub, lane);
+    if (crank == 0 && sub == 0) {
+        float* ob[NREP];
 #pragma unroll
         for (int h = 0; h < NREP; ++h) {
-            float z[8];
-#pragma unroll
-            for (int p = 0; p < 2; ++p)
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    float a = 0.0f;
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) a = fmaf(st.acc[h][p * 4 + k], rv[p][c * 4 + k], a);
-                    z[p * 4 + c] = a;
-                }
-            fwht256_lane8(z, lane);
             const int total_id = (kvh * NREP + h) * L_q + l_idx;
-            float* ob = (num_splits > 1)
-                            ? out_partial + ((size_t)total_id * num_splits + split_id) * PART
-                            : out_attn + (size_t)total_id * PART;
-#pragma unroll
-            for (int j = 0; j < 8; j += 2)
-                *reinterpret_cast<float2*>(ob + lane * 8 + j) = make_float2(z[j] * dvi[j], z[j + 1] * dvi[j + 1]);
-            if (lane == 0) {
-                ob[D] = st.m[h];
-                ob[D + 1] = st.l[h];
-            }
+            ob[h] = (num_splits > 1) ? out_partial + ((size_t)total_id * num_splits + split_id) * PART
+                                     : out_attn + (size_t)total_id * PART;
         }
+        v_epilogue_store(st, P, lane, ob);
     }
 }
 
@@ -365,18 +432,12 @@ __global__ void __launch_bounds__(D) khq_attn_reduce_kernel(const float* __restr
 // ------------------------------------------------------------------------------------------
 // Raw ring window
 // ------------------------------------------------------------------------------------------
-// One cluster; slot (win_start + s) % ring_cap, rows token-major (slot*H_kv + kv)*D.  Token s is
-// served by warp (kv, sub) of CTA c when s % (cluster_size*DEC_WPK) == c*DEC_WPK + sub.
-__global__ void __launch_bounds__(DEC_THREADS, 1)
-khq_window_attn_kernel(const __half* __restrict__ q, const __half* __restrict__ ring_k,
-                       const __half* __restrict__ ring_v, float* __restrict__ out, int win_start,
-                       int win_len, int ring_cap, float scale) {
-    extern __shared__ __align__(128) unsigned char smem[];
-    cg::cluster_group cluster = cg::this_cluster();
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int kvh = warp & 3, sub = warp >> 2;
-    const int csize = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
-
+// Window tokens s = first, first+step, ... < win_hi of this warp: slot (win_start + s) % ring_cap,
+// rows token-major (slot*H_kv + kv)*D, K already RoPE'd.
+__device__ __forceinline__ void window_range(const __half* __restrict__ q, const __half* __restrict__ ring_k,
+                                             const __half* __restrict__ ring_v, int win_start, int first,
+                                             int step, int win_hi, int ring_cap, float scale, int kvh,
+                                             int lane, WarpState& st) {
     float qv[NREP][8];
 #pragma unroll
     for (int h = 0; h < NREP; ++h) {
@@ -385,11 +446,8 @@ khq_window_attn_kernel(const __half* __restrict__ q, const __half* __restrict__ 
 #pragma unroll
         for (int j = 0; j < 8; ++j) qv[h][j] = __half2float(hq[j]) * scale;
     }
-    WarpState st;
-    st.init();
-    const int stride = csize * DEC_WPK;
 #pragma unroll 1
-    for (int s = crank * DEC_WPK + sub; s < win_len; s += stride) {
+    for (int s = first; s < win_hi; s += step) {
         const int slot = (win_start + s) % ring_cap;
         const size_t off = ((size_t)slot * HKV + kvh) * D + lane * 8;
         const uint4 kr = *reinterpret_cast<const uint4*>(ring_k + off);
@@ -412,20 +470,128 @@ khq_window_attn_kernel(const __half* __restrict__ q, const __half* __restrict__ 
         for (int j = 0; j < 8; ++j) v[j] = __half2float(hv[j]);
         accumulate_v(st, pw, v);
     }
-    merge_cta_and_cluster(st, reinterpret_cast<float*>(smem), kvh, sub, lane);
-    if (crank == 0 && sub == 0) {
+}
+
+__device__ __forceinline__ void raw_store(const WarpState& st, int lane, float* const (&ob)[NREP]) {
 #pragma unroll
-        for (int h = 0; h < NREP; ++h) {
-            float* ob = out + (size_t)(kvh * NREP + h) * PART;
+    for (int h = 0; h < NREP; ++h) {
 #pragma unroll
-            for (int j = 0; j < 8; j += 2)
-                *reinterpret_cast<float2*>(ob + lane * 8 + j) = make_float2(st.acc[h][j], st.acc[h][j + 1]);
-            if (lane == 0) {
-                ob[D] = st.m[h];
-                ob[D + 1] = st.l[h];
-            }
+        for (int j = 0; j < 8; j += 2)
+            *reinterpret_cast<float2*>(ob[h] + lane * 8 + j) = make_float2(st.acc[h][j], st.acc[h][j + 1]);
+        if (lane == 0) {
+            ob[h][D] = st.m[h];
+            ob[h][D + 1] = st.l[h];
         }
     }
+}
+
+// One cluster: token s is served by warp (kv, sub) of CTA c when
+// s % (cluster_size*DEC_WPK) == c*DEC_WPK + sub.
+__global__ void __launch_bounds__(DEC_THREADS, 1)
+khq_window_attn_kernel(const __half* __restrict__ q, const __half* __restrict__ ring_k,
+                       const __half* __restrict__ ring_v, float* __restrict__ out, int win_start,
+                       int win_len, int ring_cap, float scale) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kvh = warp & 3, sub = warp >> 2;
+    const int csize = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
+    WarpState st;
+    st.init();
+    window_range(q, ring_k, ring_v, win_start, crank * DEC_WPK + sub, csize * DEC_WPK, win_len, ring_cap, scale,
+                 kvh, lane, st);
+    merge_cta_and_cluster(st, reinterpret_cast<float*>(smem), kvh, sub, lane);
+    if (crank == 0 && sub == 0) {
+        float* ob[NREP];
+#pragma unroll
+        for (int h = 0; h < NREP; ++h) ob[h] = out + (size_t)(kvh * NREP + h) * PART;
+        raw_store(st, lane, ob);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Batched decode: many (sequence, layer) problems in one persistent launch
+// ------------------------------------------------------------------------------------------
+// One CTA per SM pulls work items off an atomic counter.  An item is a token range of one
+// problem's compressed region (all four kv-heads) or its raw window; its result is one
+// (24, 258) partial in the workspace.  Items arrive ordered by layer so that the layer's
+// tables, and the V codebook in shared memory, are reloaded only when the layer changes.
+template <bool VQS>
+__global__ void __launch_bounds__(DEC_THREADS, 1)
+khq_decode_batched_kernel(const KhqSeqDesc* __restrict__ descs, const KhqTablesDesc* __restrict__ tables,
+                          const KhqWorkItem* __restrict__ items, int n_items, int* __restrict__ counter,
+                          float* __restrict__ partials, float scale, float rope_base, int ring_cap) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ int s_next;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kvh = warp & 3, sub = warp >> 2;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM_BARS);
+    if (tid == 0) {
+        for (int s = 0; s < NSTAGE; ++s) mbar_init(&bars[s], 1);
+        fence_barrier_init();
+    }
+    int cur_table = -1;
+    unsigned tiles_done = 0;
+#pragma unroll 1
+    while (true) {
+        __syncthreads();  // previous item fully retired (merge area, s_next readers)
+        if (tid == 0) s_next = atomicAdd(counter, 1);
+        __syncthreads();
+        const int it = s_next;
+        if (it >= n_items) break;
+        const KhqWorkItem w = items[it];
+        const KhqSeqDesc d = descs[w.desc];
+        float* ob[NREP];
+#pragma unroll
+        for (int h = 0; h < NREP; ++h) ob[h] = partials + ((size_t)w.slot * HQ + kvh * NREP + h) * PART;
+        WarpState st;
+        st.init();
+        if (w.kind == 0) {
+            const KhqTablesDesc t = tables[d.table_id];
+            CompressedKV P;
+            P.k_payload = d.k_payload; P.v_payload = d.v_payload; P.v_shared_meta = d.v_shared_meta;
+            P.k_mask = d.k_mask; P.k_norms = d.k_norms; P.k_r_norms = d.k_r_norms;
+            P.v_norms = d.v_norms; P.v_r_norms = d.v_r_norms;
+            P.cents_k = t.cents_k; P.cents_v = t.cents_v; P.vq = t.vq; P.k_rotor = t.k_rotor;
+            P.v_rotor = t.v_rotor; P.d_k = t.d_k; P.d_v = t.d_v;
+            P.alpha_k = t.alpha_k; P.alpha_v = t.alpha_v; P.rope_base = rope_base;
+            P.start_pos = d.start_pos; P.c_len = d.c_len; P.bulk_ok = 1;
+            if (d.table_id != cur_table) {
+                setup_tables(smem, P, tid);
+                if (VQS) load_codebook(reinterpret_cast<unsigned short*>(smem + SM_VQ), P.vq, tid);
+                cur_table = d.table_id;
+            }
+            compressed_range<VQS>(smem, d.q_gate, (size_t)2 * D, P, w.lo, w.hi, scale, st, tiles_done);
+            merge_cta_and_cluster(st, reinterpret_cast<float*>(smem + SM_MERGE_A), kvh, sub, lane);
+            if (sub == 0) v_epilogue_store(st, P, lane, ob);
+        } else {
+            window_range(d.q_gate, d.ring_k, d.ring_v, d.win_start, w.lo + sub, DEC_WPK, w.hi, ring_cap, scale, kvh,
+                         lane, st);
+            merge_cta_and_cluster(st, reinterpret_cast<float*>(smem + SM_MERGE_A), kvh, sub, lane);
+            if (sub == 0) raw_store(st, lane, ob);
+        }
+    }
+}
+
+// Per problem and query head: LSE merge of the problem's partial slots, /(den+1e-8), sigmoid
+// gate, fp16 store.  grid = n_desc*HQ blocks of D threads.
+__global__ void __launch_bounds__(D)
+khq_batched_merge_gate_kernel(const KhqSeqDesc* __restrict__ descs, const float* __restrict__ partials) {
+    const int di = blockIdx.x / HQ, h = blockIdx.x % HQ, dd = threadIdx.x;
+    const KhqSeqDesc d = descs[di];
+    float M = NEG_BIG;
+    for (int s = 0; s < d.n_slots; ++s)
+        M = fmaxf(M, partials[((size_t)(d.first_slot + s) * HQ + h) * PART + D]);
+    float num = 0.0f, den = 0.0f;
+    for (int s = 0; s < d.n_slots; ++s) {
+        const float* p = partials + ((size_t)(d.first_slot + s) * HQ + h) * PART;
+        const float w = __expf(p[D] - M);
+        num = fmaf(p[dd], w, num);
+        den = fmaf(p[D + 1], w, den);
+    }
+    const float val = num / (den + 1e-8f);
+    const float g = __half2float(d.q_gate[(size_t)h * 2 * D + D + dd]);
+    d.out[(size_t)h * D + dd] = __float2half(val * (1.0f / (1.0f + __expf(-g))));
 }
 
 // LSE merge of the two regions, /(den + 1e-8), sigmoid gate, fp16 store.
@@ -480,15 +646,34 @@ static cudaError_t launch_cluster(Kernel kernel, unsigned grid, unsigned cluster
     return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
+// Opt in to >48 KB of dynamic shared memory, once per device.
 static cudaError_t ensure_smem_attrs() {
-    static cudaError_t once = [] {
-        cudaError_t e = cudaFuncSetAttribute(khq_attn_compressed_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SM_TOTAL);
-        if (e != cudaSuccess) return e;
-        return cudaFuncSetAttribute(khq_window_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    2 * HKV * MERGE_FLOATS * 4);
-    }();
-    return once;
+    static bool done[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64 && done[dev]) return cudaSuccess;
+    const auto attr = cudaFuncAttributeMaxDynamicSharedMemorySize;
+    if ((e = cudaFuncSetAttribute(khq_attn_compressed_kernel<false>, attr, SM_TOTAL)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(khq_attn_compressed_kernel<true>, attr, SM_TOTAL_VQ)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(khq_decode_batched_kernel<false>, attr, SM_TOTAL)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(khq_decode_batched_kernel<true>, attr, SM_TOTAL_VQ)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(khq_window_attn_kernel, attr, 2 * HKV * MERGE_FLOATS * 4)) != cudaSuccess)
+        return e;
+    if (dev >= 0 && dev < 64) done[dev] = true;
+    return cudaSuccess;
+}
+
+static int sm_count() {
+    static int n[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (n[dev] == 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        n[dev] = v;
+    }
+    return n[dev];
 }
 
 }  // namespace khq
@@ -552,10 +737,18 @@ extern "C" int launch_khq_attn_fp16(const void* q, const void* k_payload, const 
         int cluster = (per + TT - 1) / TT;
         if (cluster < 1) cluster = 1;
         if (cluster > 8) cluster = 8;
-        err = launch_cluster(khq_attn_compressed_kernel, (unsigned)(num_splits * cluster), (unsigned)cluster,
-                             (size_t)SM_TOTAL, stream, static_cast<const __half*>(q), P,
-                             static_cast<float*>(out_attn), static_cast<float*>(out_partial), num_splits, L_q,
-                             l, s_limit, scale);
+        // Staging the 128 KB V codebook in shared memory pays once a CTA decodes a few hundred tokens.
+        const int tok_per_cta = (per + cluster - 1) / cluster;
+        if (tok_per_cta >= 192)
+            err = launch_cluster(khq_attn_compressed_kernel<true>, (unsigned)(num_splits * cluster),
+                                 (unsigned)cluster, (size_t)SM_TOTAL_VQ, stream, static_cast<const __half*>(q), P,
+                                 static_cast<float*>(out_attn), static_cast<float*>(out_partial), num_splits, L_q,
+                                 l, s_limit, scale);
+        else
+            err = launch_cluster(khq_attn_compressed_kernel<false>, (unsigned)(num_splits * cluster),
+                                 (unsigned)cluster, (size_t)SM_TOTAL, stream, static_cast<const __half*>(q), P,
+                                 static_cast<float*>(out_attn), static_cast<float*>(out_partial), num_splits, L_q,
+                                 l, s_limit, scale);
         if (err != cudaSuccess) return static_cast<int>(err);
     }
     if (num_splits > 1) {
@@ -603,6 +796,89 @@ extern "C" int launch_khq_gather_q_fp16(const void* q_gate, void* q_out, int H_q
     khq_gather_q_kernel<<<(total + threads - 1) / threads, threads, 0, stream>>>(
         static_cast<const __half*>(q_gate), static_cast<__half*>(q_out), H_q, d);
     const cudaError_t err = cudaGetLastError();
+    return (err == cudaSuccess) ? 0 : static_cast<int>(err);
+}
+
+// ------------------------------------------------------------------------------------------
+// Batched decode entry points (no counterpart in the reference)
+// ------------------------------------------------------------------------------------------
+extern "C" size_t khq_b200_decode_workspace_bytes(int n_slots_total) {
+    if (n_slots_total < 0) n_slots_total = 0;
+    return 256 + (size_t)n_slots_total * HQ * PART * sizeof(float);
+}
+
+// Host planner: cuts every problem's compressed region into items of about tokens_per_item
+// tokens (a multiple of the staging tile) plus one item for its raw window, in problem order.
+extern "C" int khq_b200_plan_decode(const int* c_len, const int* win_len, int n_desc, int tokens_per_item,
+                                    void* items_out, int max_items, int* first_slot, int* n_slots) {
+    if (n_desc < 0 || !c_len || !win_len) return -100;
+    if (tokens_per_item <= 0) {
+        long long total = 0;
+        for (int i = 0; i < n_desc; ++i) total += c_len[i] > 0 ? c_len[i] : 0;
+        long long t = total / (4LL * 148);
+        if (t < 48) t = 48;
+        if (t > 2048) t = 2048;
+        tokens_per_item = (int)t;
+    }
+    tokens_per_item = ((tokens_per_item + TT - 1) / TT) * TT;
+    KhqWorkItem* items = static_cast<KhqWorkItem*>(items_out);
+    int n = 0;
+    for (int i = 0; i < n_desc; ++i) {
+        const int cl = c_len[i] > 0 ? c_len[i] : 0, wl = win_len[i] > 0 ? win_len[i] : 0;
+        const int fs = n;
+        if (cl > 0) {
+            const int pieces = (cl + tokens_per_item - 1) / tokens_per_item;
+            // equal pieces, each a multiple of 2 tokens so that every piece starts 16-byte aligned
+            int per = (((cl + pieces - 1) / pieces) + 1) & ~1;
+            for (int lo = 0; lo < cl; lo += per) {
+                if (items && n < max_items) {
+                    KhqWorkItem w = {i, 0, lo, (lo + per < cl) ? lo + per : cl, n, 0, 0, 0};
+                    items[n] = w;
+                }
+                ++n;
+            }
+        }
+        if (wl > 0) {
+            if (items && n < max_items) {
+                KhqWorkItem w = {i, 1, 0, wl, n, 0, 0, 0};
+                items[n] = w;
+            }
+            ++n;
+        }
+        if (first_slot) first_slot[i] = fs;
+        if (n_slots) n_slots[i] = n - fs;
+    }
+    return n;  // > max_items means the items buffer was too small
+}
+
+extern "C" int launch_khq_decode_batched_fp16(const void* descs, const void* tables, const void* items,
+                                              int n_desc, int n_items, void* workspace,
+                                              size_t workspace_bytes, int n_slots_total, float scale,
+                                              float rope_base, int ring_cap, int codebook_in_smem,
+                                              cudaStream_t stream) {
+    if (n_desc <= 0 || n_items <= 0 || !descs || !tables || !items || !workspace) return -100;
+    if (workspace_bytes < khq_b200_decode_workspace_bytes(n_slots_total) || ring_cap <= 0) return -105;
+    if (!aligned(workspace, 256)) return -104;
+    cudaError_t err = ensure_smem_attrs();
+    if (err != cudaSuccess) return static_cast<int>(err);
+    err = cudaMemsetAsync(workspace, 0, 256, stream);
+    if (err != cudaSuccess) return static_cast<int>(err);
+    int* counter = static_cast<int*>(workspace);
+    float* partials = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + 256);
+    const int grid = n_items < sm_count() ? n_items : sm_count();
+    const bool vqs = codebook_in_smem < 0 ? (n_items >= 1) : (codebook_in_smem != 0);
+    if (vqs)
+        khq_decode_batched_kernel<true><<<grid, DEC_THREADS, SM_TOTAL_VQ, stream>>>(
+            static_cast<const KhqSeqDesc*>(descs), static_cast<const KhqTablesDesc*>(tables),
+            static_cast<const KhqWorkItem*>(items), n_items, counter, partials, scale, rope_base, ring_cap);
+    else
+        khq_decode_batched_kernel<false><<<grid, DEC_THREADS, SM_TOTAL, stream>>>(
+            static_cast<const KhqSeqDesc*>(descs), static_cast<const KhqTablesDesc*>(tables),
+            static_cast<const KhqWorkItem*>(items), n_items, counter, partials, scale, rope_base, ring_cap);
+    err = cudaGetLastError();
+    if (err != cudaSuccess) return static_cast<int>(err);
+    khq_batched_merge_gate_kernel<<<n_desc * HQ, D, 0, stream>>>(static_cast<const KhqSeqDesc*>(descs), partials);
+    err = cudaGetLastError();
     return (err == cudaSuccess) ? 0 : static_cast<int>(err);
 }
 

@@ -42,12 +42,46 @@ constexpr int SM_ROPE = SM_STAGES + NSTAGE * STAGE_BYTES;   // 2 x TT x 32 float
 constexpr int SM_ROTOR = SM_ROPE + 2 * TT * 32 * 8;         // 32 lanes x 36 floats
 constexpr int SM_FREQ = SM_ROTOR + 32 * 36 * 4;             // 32 floats
 constexpr int SM_BARS = SM_FREQ + 32 * 4;                   // NSTAGE mbarriers
-constexpr int SM_TOTAL = SM_BARS + 64;
+constexpr int SM_TOTAL = SM_BARS + 64;                      // without the V codebook
+constexpr int SM_VQ = SM_TOTAL;                             // 256 codes x 64 patches x 4 halfs
+constexpr int SM_TOTAL_VQ = SM_VQ + 256 * NP * 8;
+static_assert(SM_VQ % 16 == 0 && SM_TOTAL_VQ <= 227 * 1024, "shared memory budget");
 // Per-kv-head merge record: acc[NREP][D], m[NREP], l[NREP]  (+pad to 16 B)
 constexpr int MERGE_FLOATS = NREP * D + 2 * NREP + 4;       // 1552
 constexpr int SM_MERGE_A = 0;                               // aliases the stages after the loop
 constexpr int SM_MERGE_E = SM_MERGE_A + HKV * MERGE_FLOATS * 4;
 static_assert(SM_MERGE_E + HKV * MERGE_FLOATS * 4 <= NSTAGE * STAGE_BYTES, "merge areas alias the stages");
+
+// ---- batched decode: device-resident descriptor tables (mirrored in include/khq_b200.h) -------
+struct KhqSeqDesc {  // one (sequence, layer) decode problem
+    const __half* q_gate;
+    const unsigned char* k_payload;
+    const unsigned char* v_payload;
+    const unsigned char* v_shared_meta;
+    const unsigned int* k_mask;
+    const __half* k_norms;
+    const __half* k_r_norms;
+    const __half* v_norms;
+    const __half* v_r_norms;
+    const __half* ring_k;
+    const __half* ring_v;
+    __half* out;
+    int table_id, c_len, start_pos, win_start, win_len, first_slot, n_slots, reserved;
+};
+struct KhqTablesDesc {  // one layer's calibration tables
+    const __half* cents_k;
+    const __half* cents_v;
+    const __half* vq;
+    const __half* k_rotor;
+    const __half* v_rotor;
+    const __half* d_k;
+    const __half* d_v;
+    float alpha_k, alpha_v;
+};
+struct KhqWorkItem {  // one CTA-sized piece of a problem
+    int desc, kind, lo, hi, slot, r0, r1, r2;  // kind 0: compressed tokens [lo,hi); 1: window tokens [lo,hi)
+};
+static_assert(sizeof(KhqSeqDesc) == 128 && sizeof(KhqTablesDesc) == 64 && sizeof(KhqWorkItem) == 32, "ABI");
 
 struct CompressedKV {  // device pointers of one sequence-layer's compressed region + tables
     const unsigned char* k_payload;

@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_float, c_int, c_void_p
+from ctypes import POINTER, c_char_p, c_float, c_int, c_size_t, c_void_p
 from pathlib import Path
 
 _PKG_DIR = Path(__file__).resolve().parent
@@ -27,6 +27,10 @@ SIGNATURES = {
     "launch_khq_window_attn_fp16": (c_int, [_P] * 4 + [c_int] * 6 + [c_float, _P]),
     "launch_khq_merge_gate_fp16": (c_int, [_P] * 4 + [c_int, c_int, c_int, _P]),
     "launch_khq_gather_q_fp16": (c_int, [_P, _P, c_int, c_int, _P]),
+    "khq_b200_plan_decode": (c_int, [_P, _P, c_int, c_int, _P, c_int, _P, _P]),
+    "khq_b200_decode_workspace_bytes": (c_size_t, [c_int]),
+    "launch_khq_decode_batched_fp16": (
+        c_int, [_P, _P, _P, c_int, c_int, _P, c_size_t, c_int, c_float, c_float, c_int, c_int, _P]),
     "khq_b200_version": (c_char_p, []),
     "khq_b200_device_status": (c_int, []),
 }

@@ -105,6 +105,74 @@ int launch_khq_gather_q_fp16(const void* q_gate, void* q_out, int H_q, int d,
  * Section 2: additions (no counterpart in the reference)
  * ---------------------------------------------------------------------------------------- */
 
+/* ---- Batched decode: many (sequence, layer) problems in one persistent launch ------------ */
+
+/* One decode problem: a sequence's KHQ state of one attention layer plus this step's query.
+ * 128 bytes, device pointers, stored in a device-resident array. */
+typedef struct khq_seq_desc {
+    const void* q_gate;         /* (24, 512) fp16 */
+    const void* k_payload;      /* compressed region, rows = token*4 + kv_head */
+    const void* v_payload;
+    const void* v_shared_meta;
+    const void* k_mask;
+    const void* k_norms;
+    const void* k_r_norms;
+    const void* v_norms;
+    const void* v_r_norms;
+    const void* ring_k;         /* (ring_cap, 4, 256) fp16, K already RoPE'd */
+    const void* ring_v;
+    void* out;                  /* (24, 256) fp16 gated attention output */
+    int32_t table_id;           /* index into the khq_tables_desc array (the layer) */
+    int32_t c_len;              /* compressed tokens */
+    int32_t start_pos;          /* absolute position of compressed token 0 */
+    int32_t win_start;          /* first ring slot of the raw window */
+    int32_t win_len;            /* raw window tokens */
+    int32_t first_slot;         /* filled by khq_b200_plan_decode */
+    int32_t n_slots;            /* filled by khq_b200_plan_decode */
+    int32_t reserved;
+} khq_seq_desc;
+
+/* One layer's calibration tables (fp16 device arrays in the khq_calib layout). 64 bytes. */
+typedef struct khq_tables_desc {
+    const void* cents_k;
+    const void* cents_v;
+    const void* vq;
+    const void* k_rotor;
+    const void* v_rotor;
+    const void* d_k;
+    const void* d_v;
+    float alpha_k, alpha_v;
+} khq_tables_desc;
+
+/* One CTA-sized piece of a problem; produced by khq_b200_plan_decode. 32 bytes. */
+typedef struct khq_work_item {
+    int32_t desc, kind, lo, hi, slot, r0, r1, r2; /* kind 0: compressed tokens [lo,hi); 1: window */
+} khq_work_item;
+
+/* Host-side planner (pure CPU, no CUDA call).  c_len[i]/win_len[i] describe problem i; problems
+ * should be ordered by table_id so that consecutive items share tables.  tokens_per_item <= 0
+ * picks a size that fills the GPU.  Writes up to max_items items, and per problem the first
+ * partial slot and the slot count (copy them into the descriptors).  Returns the item count
+ * (== total slot count); a value > max_items means items_out was too small.  -100 on bad args. */
+int khq_b200_plan_decode(const int* c_len, const int* win_len, int n_desc, int tokens_per_item,
+                         void* items_out, int max_items, int* first_slot, int* n_slots);
+
+/* Bytes of workspace launch_khq_decode_batched_fp16 needs for n_slots_total partial slots. */
+size_t khq_b200_decode_workspace_bytes(int n_slots_total);
+
+/* Whole decode attention (compressed region + raw window + LSE merge + sigmoid gate) of n_desc
+ * problems: a persistent kernel (one CTA per SM pulling items off an atomic counter in the
+ * workspace) followed by a merge kernel.  descs/tables/items are DEVICE arrays; workspace is a
+ * 256-byte-aligned device buffer of at least khq_b200_decode_workspace_bytes(n_slots_total).
+ * codebook_in_smem: 1 stage each layer's V codebook in shared memory, 0 gather it from global
+ * memory, -1 let the library choose.  Allocates nothing; the only non-kernel call is a 256-byte
+ * cudaMemsetAsync on `stream`.  Returns -100 (empty/NULL arguments), -104 (alignment), -105
+ * (workspace too small). */
+int launch_khq_decode_batched_fp16(const void* descs, const void* tables, const void* items, int n_desc,
+                                   int n_items, void* workspace, size_t workspace_bytes,
+                                   int n_slots_total, float scale, float rope_base, int ring_cap,
+                                   int codebook_in_smem, khq_stream_t stream);
+
 /* Library identification: "khq-b200 <version> sm_100a". */
 const char* khq_b200_version(void);
 
