@@ -882,6 +882,56 @@ extern "C" int launch_khq_decode_batched_fp16(const void* descs, const void* tab
     return (err == cudaSuccess) ? 0 : static_cast<int>(err);
 }
 
+// ------------------------------------------------------------------------------------------
+// Compressed-region attention without a caller-supplied partial buffer
+// ------------------------------------------------------------------------------------------
+// Split partials of launch_khq_attn_static_fp16 live here instead of in a buffer the caller
+// allocates: 24 query heads x at most 32 splits x 258 floats = 792 576 bytes, held by every GPU
+// that loads the library until the process exits.
+constexpr int STATIC_MAX_SPLITS = 32;
+static __device__ __align__(256) float g_static_partials[khq::HQ * STATIC_MAX_SPLITS * khq::PART];
+
+// Device address of g_static_partials on the current device.  In host code the array's name is
+// only a handle for the runtime, not an address a kernel can use, so the address is looked up
+// once per device (with that device current) and cached.
+static cudaError_t static_partials_address(float** out) {
+    static float* cached[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (cached[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_partials);
+        if (e != cudaSuccess) return e;
+        cached[dev] = static_cast<float*>(p);
+    }
+    *out = cached[dev];
+    return cudaSuccess;
+}
+
+extern "C" int launch_khq_attn_static_fp16(const void* q, const void* k_payload, const void* v_payload,
+                                           const void* v_shared_meta, const void* k_mask,
+                                           const void* k_norms, const void* k_r_norms, const void* v_norms,
+                                           const void* v_r_norms, const void* centroids_k,
+                                           const void* centroids_v, const void* vq_centroids,
+                                           const void* k_rotor, const void* v_rotor, const void* d_vec_k,
+                                           const void* d_vec_v, void* out_attn, int num_queries,
+                                           int num_heads, int L_q, int c_len, int n_rep, float scale,
+                                           float alpha_k, float alpha_v, float rope_base, int start_pos,
+                                           int num_splits, cudaStream_t stream) {
+    if (num_queries <= 0 || c_len <= 0) return -100;
+    // The static array is sized for one decode query row per head and at most 32 splits.
+    if (L_q != 1 || num_queries != khq::HQ || num_splits > STATIC_MAX_SPLITS) return -106;
+    float* partials = nullptr;
+    const cudaError_t e = static_partials_address(&partials);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    return launch_khq_attn_fp16(q, k_payload, v_payload, v_shared_meta, k_mask, k_norms, k_r_norms, v_norms,
+                                v_r_norms, centroids_k, centroids_v, vq_centroids, k_rotor, v_rotor, d_vec_k,
+                                d_vec_v, out_attn, partials, num_queries, num_heads, L_q, c_len, c_len, n_rep,
+                                scale, alpha_k, alpha_v, rope_base, start_pos, num_splits, stream);
+}
+
 static void* g_khq_slots[3] = {nullptr, nullptr, nullptr};
 extern "C" void* khq_state_slot(int which) {
     if (which < 0 || which > 2) which = 0;

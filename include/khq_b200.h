@@ -173,6 +173,29 @@ int launch_khq_decode_batched_fp16(const void* descs, const void* tables, const 
                                    int n_slots_total, float scale, float rope_base, int ring_cap,
                                    int codebook_in_smem, khq_stream_t stream);
 
+/* No counterpart in the reference.  launch_khq_attn_fp16 for callers that cannot hand over a
+ * partial buffer: the split partials go to a fixed array inside the library's device image
+ * (24 heads x up to 32 splits x 258 floats = 792 576 bytes per GPU that loads the library)
+ * instead of `out_partial`.  Meant for hosts whose device memory is entirely owned by another
+ * runtime's pool, or that sit inside a decode loop where cudaMalloc (which synchronises the
+ * whole device) is not acceptable.  Same arguments and results as launch_khq_attn_fp16 without
+ * `out_partial` and `stride_s`; restricted to L_q == 1, num_queries == 24, num_splits <= 32,
+ * anything larger returns -106.  It calls no allocating routine.  The first call on a device
+ * looks up the array's device address (cudaGetSymbolAddress) and caches it, so make that first
+ * call outside any stream capture.  Every call on a device shares the one array: calls that may
+ * overlap on the GPU (different streams) race on it; calls on one stream do not.  Nothing in the
+ * array has to be cleared between calls: every split writes its whole record, empty splits
+ * included. */
+int launch_khq_attn_static_fp16(const void* q, const void* k_payload, const void* v_payload,
+                                const void* v_shared_meta, const void* k_mask, const void* k_norms,
+                                const void* k_r_norms, const void* v_norms, const void* v_r_norms,
+                                const void* centroids_k, const void* centroids_v,
+                                const void* vq_centroids, const void* k_rotor, const void* v_rotor,
+                                const void* d_vec_k, const void* d_vec_v, void* out_attn,
+                                int num_queries, int num_heads, int L_q, int c_len, int n_rep,
+                                float scale, float alpha_k, float alpha_v, float rope_base,
+                                int start_pos, int num_splits, khq_stream_t stream);
+
 /* Library identification: "khq-b200 <version> sm_100a". */
 const char* khq_b200_version(void);
 
