@@ -616,6 +616,26 @@ __global__ void khq_merge_gate_kernel(const float* __restrict__ attn_c, const fl
     out[i] = __float2half(val * (1.0f / (1.0f + __expf(-g))));
 }
 
+// LSE merge of n_slots slot-major partials (slot, H_q, 258) -> /(den+1e-8) -> sigmoid gate -> fp16.
+// Used to finish a context-parallel step from the partials gathered from every GPU.
+__global__ void __launch_bounds__(D)
+khq_merge_slots_gate_kernel(const float* __restrict__ partials, int n_slots, const __half* __restrict__ q_gate,
+                            __half* __restrict__ out) {
+    const int h = blockIdx.x, dd = threadIdx.x;
+    float M = NEG_BIG;
+    for (int s = 0; s < n_slots; ++s) M = fmaxf(M, partials[((size_t)s * HQ + h) * PART + D]);
+    float num = 0.0f, den = 0.0f;
+    for (int s = 0; s < n_slots; ++s) {
+        const float* p = partials + ((size_t)s * HQ + h) * PART;
+        const float w = __expf(p[D] - M);
+        num = fmaf(p[dd], w, num);
+        den = fmaf(p[D + 1], w, den);
+    }
+    const float val = num / (den + 1e-8f);
+    const float g = __half2float(q_gate[(size_t)h * 2 * D + D + dd]);
+    out[(size_t)h * D + dd] = __float2half(val * (1.0f / (1.0f + __expf(-g))));
+}
+
 __global__ void khq_gather_q_kernel(const __half* __restrict__ q_gate, __half* __restrict__ q_out, int H_q,
                                     int d_v) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -930,6 +950,17 @@ extern "C" int launch_khq_attn_static_fp16(const void* q, const void* k_payload,
                                 v_r_norms, centroids_k, centroids_v, vq_centroids, k_rotor, v_rotor, d_vec_k,
                                 d_vec_v, out_attn, partials, num_queries, num_heads, L_q, c_len, c_len, n_rep,
                                 scale, alpha_k, alpha_v, rope_base, start_pos, num_splits, stream);
+}
+
+extern "C" int launch_khq_merge_slots_gate_fp16(const void* partials, int n_slots, const void* q_gate,
+                                                void* out, int H_q, int d, cudaStream_t stream) {
+    if (n_slots <= 0 || !partials || !q_gate || !out) return -100;
+    if (H_q != HQ || d != D) return -103;
+    khq_merge_slots_gate_kernel<<<HQ, D, 0, stream>>>(static_cast<const float*>(partials), n_slots,
+                                                      static_cast<const __half*>(q_gate),
+                                                      static_cast<__half*>(out));
+    const cudaError_t err = cudaGetLastError();
+    return (err == cudaSuccess) ? 0 : static_cast<int>(err);
 }
 
 static void* g_khq_slots[3] = {nullptr, nullptr, nullptr};

@@ -33,6 +33,7 @@ SIGNATURES = {
         c_int, [_P, _P, _P, c_int, c_int, _P, c_size_t, c_int, c_float, c_float, c_int, c_int, _P]),
     "launch_khq_attn_static_fp16": (
         c_int, [_P] * 17 + [c_int] * 5 + [c_float, c_float, c_float, c_float, c_int, c_int, _P]),
+    "launch_khq_merge_slots_gate_fp16": (c_int, [_P, c_int, _P, _P, c_int, c_int, _P]),
     "khq_b200_version": (c_char_p, []),
     "khq_b200_device_status": (c_int, []),
 }

@@ -59,6 +59,12 @@ class CudaOps:
             1 if (has_w and has_c) else 0, current_stream())
         check("launch_khq_merge_gate_fp16", rc)
 
+    # -- launch_khq_merge_slots_gate_fp16: finish a context-parallel step ------------------------
+    def merge_slots_gate(self, partials, n_slots, q_gate, out, H_q, d):
+        rc = self.lib.launch_khq_merge_slots_gate_fp16(ptr(partials), int(n_slots), ptr(q_gate), ptr(out),
+                                                       int(H_q), int(d), current_stream())
+        check("launch_khq_merge_slots_gate_fp16", rc)
+
     # -- ring appends (khq_ring_dual_sm75_gpu / copy_vec_sm75_gpu,
     #    src/kernels/elementwise_sm75.mojo:277-312): device-to-device copies ------------------
     def ring_write(self, dst_row, src):

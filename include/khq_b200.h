@@ -173,6 +173,17 @@ int launch_khq_decode_batched_fp16(const void* descs, const void* tables, const 
                                    int n_slots_total, float scale, float rope_base, int ring_cap,
                                    int codebook_in_smem, khq_stream_t stream);
 
+/* ---- Context parallelism: one long sequence split by context range over several GPUs ------
+ * Each GPU calls launch_khq_attn_fp16 on its slice (start_pos = first absolute token of the
+ * slice) and obtains an unnormalised (24, 258) partial; the owner of the raw ring adds the
+ * window partial.  After the partials have been gathered slot-major, (n_slots, 24, 258) fp32,
+ * this launch LSE-merges them, divides by (den + 1e-8), applies the sigmoid gate and writes
+ * fp16 (24, 256): the math of khq_attn_reduce_kernel + khq_merge_gate_kernel
+ * (src/csrc/qmv_sm75_kernel.cu:1836-1877, 1983-2010) over n_slots regions.  Slots that hold
+ * (0, -1e20, 0) are neutral.  Returns -100 (bad arguments), -103 (shape). */
+int launch_khq_merge_slots_gate_fp16(const void* partials, int n_slots, const void* q_gate, void* out,
+                                     int H_q, int d, khq_stream_t stream);
+
 /* No counterpart in the reference.  launch_khq_attn_fp16 for callers that cannot hand over a
  * partial buffer: the split partials go to a fixed array inside the library's device image
  * (24 heads x up to 32 splits x 258 floats = 792 576 bytes per GPU that loads the library)

@@ -219,6 +219,17 @@ class OracleOps:
         if rc:
             raise OracleLaunchError("merge_gate", rc)
 
+    def merge_slots_gate(self, partials, n_slots, q_gate, out, H_q, d):
+        """(n_slots, H_q, 258) slot-major partials -> LSE merge -> gate -> fp16 (reduce + merge_gate)."""
+        import torch
+
+        p = partials if isinstance(partials, np.ndarray) else partials.numpy()
+        p = np.ascontiguousarray(p.reshape(n_slots, H_q, PART).transpose(1, 0, 2))
+        merged = attn_reduce(p, H_q, n_slots)
+        rc = merge_gate(merged, merged, q_gate, out, H_q, d, 0)
+        if rc:
+            raise OracleLaunchError("merge_slots_gate", rc)
+
     def ring_write(self, dst_row, src):
         dst_row.copy_(src.reshape(dst_row.shape))
 
