@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import POINTER, c_char_p, c_float, c_int, c_size_t, c_void_p
+from ctypes import POINTER, c_char_p, c_float, c_int, c_longlong, c_size_t, c_void_p
 from pathlib import Path
 
 _PKG_DIR = Path(__file__).resolve().parent
@@ -34,6 +34,8 @@ SIGNATURES = {
     "launch_khq_attn_static_fp16": (
         c_int, [_P] * 17 + [c_int] * 5 + [c_float, c_float, c_float, c_float, c_int, c_int, _P]),
     "launch_khq_merge_slots_gate_fp16": (c_int, [_P, c_int, _P, _P, c_int, c_int, _P]),
+    "launch_khq_gqa_prefill_fp16": (
+        c_int, [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_longlong, c_longlong, c_longlong, _P]),
     "khq_b200_version": (c_char_p, []),
     "khq_b200_device_status": (c_int, []),
 }

@@ -65,6 +65,14 @@ class CudaOps:
                                                        int(H_q), int(d), current_stream())
         check("launch_khq_merge_slots_gate_fp16", rc)
 
+    # -- launch_khq_gqa_prefill_fp16: causal GQA attention of whole prompts -----------------------
+    def gqa_prefill(self, q_gate, k, v, out, batch, T, H_q, H_kv, d, scale):
+        """q_gate (batch, T, H_q, 2d), k/v (batch, T, H_kv, d), out (batch, T, H_q, d): contiguous fp16."""
+        rc = self.lib.launch_khq_gqa_prefill_fp16(
+            ptr(q_gate), ptr(k), ptr(v), ptr(out), int(batch), int(T), int(H_q), int(H_kv), int(d), float(scale),
+            int(T) * H_q * 2 * d, int(T) * H_kv * d, int(T) * H_q * d, current_stream())
+        check("launch_khq_gqa_prefill_fp16", rc)
+
     # -- ring appends (khq_ring_dual_sm75_gpu / copy_vec_sm75_gpu,
     #    src/kernels/elementwise_sm75.mojo:277-312): device-to-device copies ------------------
     def ring_write(self, dst_row, src):

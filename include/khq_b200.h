@@ -173,6 +173,21 @@ int launch_khq_decode_batched_fp16(const void* descs, const void* tables, const 
                                    int n_slots_total, float scale, float rope_base, int ring_cap,
                                    int codebook_in_smem, khq_stream_t stream);
 
+/* ---- Prefill: causal GQA attention + sigmoid gate over a whole prompt --------------------
+ * The math of the reference's fp16-KV attention kernel (gqa_attention_sm75_gpu,
+ * src/kernels/elementwise_sm75.mojo:1091-1231), which the reference launches once per prompt
+ * token (src/models/qwen3_5/layer.mojo:630-641), for all T rows of `batch` prompts at once:
+ *   out[b,t,h,:] = softmax_{u<=t}(q[b,t,h] . K[b,u,h/6] * scale) V[b,u,h/6] * sigmoid(gate[b,t,h,:])
+ * with the kernel's 1/(Z + 1e-9) denominator.  q_gate (batch, T, H_q, 2*d) fp16 (query | gate
+ * per head, the reference's interleaved layout), k / v (batch, T, H_kv, d) fp16 token-major (the
+ * reference's KV-cache row layout), K already RoPE'd; out (batch, T, H_q, d) fp16.  Batch strides
+ * are in elements.  Returns -100 (empty), -103 (d != 256 or H_q % H_kv != 0), -104 (pointers not
+ * 16-byte aligned). */
+int launch_khq_gqa_prefill_fp16(const void* q_gate, const void* k, const void* v, void* out, int batch,
+                                int T, int H_q, int H_kv, int d, float scale, long long q_batch_stride,
+                                long long kv_batch_stride, long long out_batch_stride,
+                                khq_stream_t stream);
+
 /* ---- Context parallelism: one long sequence split by context range over several GPUs ------
  * Each GPU calls launch_khq_attn_fp16 on its slice (start_pos = first absolute token of the
  * slice) and obtains an unnormalised (24, 258) partial; the owner of the raw ring adds the
