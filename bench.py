@@ -51,6 +51,8 @@ def parse():
     ap.add_argument("--layers", type=int, default=N_LAYERS)
     ap.add_argument("--cpu-sample-mult", type=int, default=4, help="CPU sample = mult x host threads sequences")
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--kernel", default="auto", choices=["auto", "cuda-core", "mma"],
+                    help="generation of the batched decode kernel")
     return ap.parse_args()
 
 
@@ -271,7 +273,8 @@ def main():
     c_len, win = workload(args, rank)
     tables = make_tables(args.layers)
     t_setup = time.perf_counter()
-    eng = BatchEngine(tables, c_len, win, device=f"cuda:{local_rank}")
+    eng = BatchEngine(tables, c_len, win, device=f"cuda:{local_rank}",
+                      codebook_in_smem={"auto": -1, "cuda-core": 1, "mma": 2}[args.kernel])
     eng.fill_synthetic(20260914 + 1000 * 3 + rank)
     torch.cuda.synchronize()
     setup_s = time.perf_counter() - t_setup

@@ -573,6 +573,10 @@ khq_decode_batched_kernel(const KhqSeqDesc* __restrict__ descs, const KhqTablesD
     }
 }
 
+}  // namespace khq
+#include "khq_decode_mma.cuh"
+namespace khq {
+
 // Per problem and query head: LSE merge of the problem's partial slots, /(den+1e-8), sigmoid
 // gate, fp16 store.  grid = n_desc*HQ blocks of D threads.
 __global__ void __launch_bounds__(D)
@@ -678,6 +682,7 @@ static cudaError_t ensure_smem_attrs() {
     if ((e = cudaFuncSetAttribute(khq_attn_compressed_kernel<true>, attr, SM_TOTAL_VQ)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(khq_decode_batched_kernel<false>, attr, SM_TOTAL)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(khq_decode_batched_kernel<true>, attr, SM_TOTAL_VQ)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(khq_decode_batched_mma_kernel, attr, M2_SM_TOTAL)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(khq_window_attn_kernel, attr, 2 * HKV * MERGE_FLOATS * 4)) != cudaSuccess)
         return e;
     if (dev >= 0 && dev < 64) done[dev] = true;
@@ -887,7 +892,11 @@ extern "C" int launch_khq_decode_batched_fp16(const void* descs, const void* tab
     float* partials = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + 256);
     const int grid = n_items < sm_count() ? n_items : sm_count();
     const bool vqs = codebook_in_smem < 0 ? (n_items >= 1) : (codebook_in_smem != 0);
-    if (vqs)
+    if (codebook_in_smem == 2)
+        khq_decode_batched_mma_kernel<<<grid, M2_THREADS, M2_SM_TOTAL, stream>>>(
+            static_cast<const KhqSeqDesc*>(descs), static_cast<const KhqTablesDesc*>(tables),
+            static_cast<const KhqWorkItem*>(items), n_items, counter, partials, scale, rope_base, ring_cap);
+    else if (vqs)
         khq_decode_batched_kernel<true><<<grid, DEC_THREADS, SM_TOTAL_VQ, stream>>>(
             static_cast<const KhqSeqDesc*>(descs), static_cast<const KhqTablesDesc*>(tables),
             static_cast<const KhqWorkItem*>(items), n_items, counter, partials, scale, rope_base, ring_cap);

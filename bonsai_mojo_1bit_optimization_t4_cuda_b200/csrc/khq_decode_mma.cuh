@@ -1,0 +1,667 @@
+// khq_decode_mma.cuh -- second-generation compressed-region decode: the two contractions of
+// attention (q.K^T and p.V), the inverse K rotor + block sum, and the 64-dim rotary dot product
+// run on the tensor cores with the 16 tokens of a block as the M dimension and the GQA group's
+// six query heads (padded to 8) as N.  Included by khq_decode.cu (shares its helpers).
+//
+// Algebra.  K^ = RoPE_s( dinv * H256 * R * y ), y = alpha_k*k_norm*(mult*c*t + rs*sign*code).
+// Everything left of y is linear, so it moves to the query side once per (sequence, layer):
+//   * non-rotary output dims (>= 64):  q.K^ = y . q~,  q~ = R^T H256 (q * dinv * [dim >= 64])
+//     -> one GEMM  S_pass[token, head] = T[token, dim] Q1[dim, head] + C[token, dim] Q2[dim, head]
+//        with T = ternary symbols (exact in fp16), C = sign*code*(rs/mult), Q1 = q~*c, Q2 = q~;
+//   * rotary output dims (< 64): the first 64 outputs of H256 are H64 of the sum of the four
+//     64-dim blocks, so u[token, 64] = T * (R c)-blocks + C * R-blocks is a second GEMM with the
+//     same A operands; H64, /d, the rotation by the token's angle, and a 64-deep GEMM with the raw
+//     query finish it.
+// V is accumulated in the rotated domain exactly as the first-generation kernel does:
+//   O^T[dim, head] += V^T[dim, token] P^T[token, head], V^T = raw fp16 codebook entries (exact),
+//   the per-token scales (alpha_v*v_norm*energy etc.) folded into three variants of P.
+//
+// Thread mapping (mma.sync.m16n8k16 fragments): lane = 4*g + t.  K side: token rows g and g+8,
+// thread t owns the 64-dim quarter [64t, 64t+64) of both rows (mask words 4t..4t+3), k-step s
+// covers dims 64t'+4s..+3 of all four quarters, i.e. the four patches that the rotor block sum
+// adds up.  V side: thread (g, t) owns patch group g (patches 8g..8g+7) of tokens 2t, 2t+1,
+// 2t+8, 2t+9.
+#pragma once
+#include "khq_kdecode.cuh"
+
+namespace khq {
+
+constexpr int M2_THREADS = 256;
+constexpr int M2_TT = 32;      // tokens per tile: 2 warps per kv-head x 16 tokens
+constexpr int M2_NSTAGE = 2;
+constexpr int M2_ROWS = M2_TT * HKV;
+constexpr int M2_OFF_MASK = 0;
+constexpr int M2_OFF_KPAY = M2_OFF_MASK + M2_ROWS * 64;
+constexpr int M2_OFF_VPAY = M2_OFF_KPAY + M2_ROWS * K_PAY;
+constexpr int M2_OFF_KN = M2_OFF_VPAY + M2_ROWS * V_PAY;
+constexpr int M2_OFF_KRN = M2_OFF_KN + M2_ROWS * 2;
+constexpr int M2_OFF_VN = M2_OFF_KRN + M2_ROWS * 2;
+constexpr int M2_OFF_VRN = M2_OFF_VN + M2_ROWS * 2;
+constexpr int M2_OFF_VSM = M2_OFF_VRN + M2_ROWS * 2;
+constexpr int M2_STAGE_BYTES = M2_OFF_VSM + M2_ROWS * 4;  // 28160
+
+constexpr int M2_SM_STAGES = 0;
+constexpr int M2_SM_VQ = M2_SM_STAGES + M2_NSTAGE * M2_STAGE_BYTES;  // 256 x 64 x 8 B
+constexpr int M2_SM_ROPE = M2_SM_VQ + 256 * NP * 8;                  // 2 x 32 tokens x 32 float2
+constexpr int M2_SM_BROT = M2_SM_ROPE + 2 * M2_TT * 32 * 8;          // 2 kinds x 16 steps x 32 lanes x 8 B
+constexpr int M2_SM_LUT = M2_SM_BROT + 2 * 16 * 32 * 8;              // scatter table
+constexpr int M2_SM_FREQ = M2_SM_LUT + 448;
+constexpr int M2_SM_DINV = M2_SM_FREQ + 128;                         // 64 floats
+constexpr int M2_SM_BARS = M2_SM_DINV + 256;
+constexpr int M2_SM_TOTAL = M2_SM_BARS + 64;
+static_assert(M2_SM_TOTAL <= 227 * 1024, "shared memory budget");
+static_assert(8 * MERGE_FLOATS * 4 <= M2_NSTAGE * M2_STAGE_BYTES, "records alias the stages");
+static_assert(8 * NREP * D * 4 <= M2_NSTAGE * M2_STAGE_BYTES, "prologue scratch aliases the stages");
+static_assert(M2_STAGE_BYTES % 16 == 0 && M2_OFF_KPAY % 16 == 0 && M2_OFF_VPAY % 16 == 0 && M2_OFF_KN % 16 == 0 &&
+                  M2_OFF_VSM % 16 == 0, "bulk copy alignment");
+
+__device__ __forceinline__ void m2_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t m2_movmatrix_t(uint32_t x) {
+    uint32_t r;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(x));
+    return r;
+}
+__device__ __forceinline__ uint32_t m2_pack(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t m2_hfma2(uint32_t a, uint32_t b, uint32_t c) {
+    const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b),
+                              *reinterpret_cast<const __half2*>(&c));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t m2_hmul2(uint32_t a, uint32_t b) {
+    const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+// Stage `ntok` tokens starting at `tok0` (same contract as stage_tile of the first generation).
+__device__ __forceinline__ void m2_stage_tile(const CompressedKV& P, unsigned char* stage, uint64_t* bar, int tok0,
+                                              int ntok, int tid) {
+    const size_t r0 = (size_t)tok0 * HKV;
+    const int rows = ntok * HKV;
+    const unsigned char* src[8] = {reinterpret_cast<const unsigned char*>(P.k_mask) + r0 * 64,
+                                   P.k_payload + r0 * K_PAY,
+                                   P.v_payload + r0 * V_PAY,
+                                   reinterpret_cast<const unsigned char*>(P.k_norms) + r0 * 2,
+                                   reinterpret_cast<const unsigned char*>(P.k_r_norms) + r0 * 2,
+                                   reinterpret_cast<const unsigned char*>(P.v_norms) + r0 * 2,
+                                   reinterpret_cast<const unsigned char*>(P.v_r_norms) + r0 * 2,
+                                   P.v_shared_meta + r0 * 4};
+    const int dst[8] = {M2_OFF_MASK, M2_OFF_KPAY, M2_OFF_VPAY, M2_OFF_KN, M2_OFF_KRN, M2_OFF_VN, M2_OFF_VRN, M2_OFF_VSM};
+    const int bpr[8] = {64, K_PAY, V_PAY, 2, 2, 2, 2, 4};
+    const bool bulk = P.bulk_ok && ((tok0 & 1) == 0) && ((ntok & 1) == 0);
+    if (bulk) {
+        if (tid == 0) {
+            mbar_arrive_expect_tx(bar, (uint32_t)(rows * 220));
+#pragma unroll
+            for (int a = 0; a < 8; ++a) bulk_g2s(stage + dst[a], src[a], (uint32_t)(rows * bpr[a]), bar);
+        }
+    } else {
+#pragma unroll
+        for (int a = 0; a < 8; ++a) {
+            const int words = rows * bpr[a] / 4;
+            const unsigned int* s = reinterpret_cast<const unsigned int*>(src[a]);
+            unsigned int* d = reinterpret_cast<unsigned int*>(stage + dst[a]);
+            for (int i = tid; i < words; i += M2_THREADS) d[i] = s[i];
+        }
+        fence_proxy_async();
+        __syncthreads();
+        if (tid == 0) mbar_arrive(bar);
+    }
+}
+
+__device__ __forceinline__ void m2_fill_rope(float2* tab, const float* freq, int pos0, int tid) {
+    for (int e = tid; e < M2_TT * 32; e += M2_THREADS) {
+        const int t = e >> 5, m = e & 31;
+        double th = (double)(pos0 + t) * (double)freq[m];
+        th -= rint(th * 0.15915494309189535) * 6.283185307179586;
+        float s, c;
+        __sincosf((float)th, &s, &c);
+        tab[e] = make_float2(c, s);
+    }
+}
+
+// Per-layer constants in shared memory: RoPE frequencies, dinv of the 64 rotary dims, the scatter
+// table of the K decode, the rotor B fragments (with and without the centroid factor) and the V
+// codebook.  Must be followed by __syncthreads().
+__device__ __forceinline__ void m2_setup_tables(unsigned char* smem, const CompressedKV& P, int tid) {
+    float* freq_s = reinterpret_cast<float*>(smem + M2_SM_FREQ);
+    float* dinv_s = reinterpret_cast<float*>(smem + M2_SM_DINV);
+    KdLutEntry* lut = reinterpret_cast<KdLutEntry*>(smem + M2_SM_LUT);
+    uint2* brot = reinterpret_cast<uint2*>(smem + M2_SM_BROT);
+    unsigned short* vq_s = reinterpret_cast<unsigned short*>(smem + M2_SM_VQ);
+    if (tid < 32) freq_s[tid] = powf(P.rope_base, -2.0f * (float)tid / 64.0f);
+    if (tid < 64) dinv_s[tid] = (1.0f / 256.0f) / (__half2float(P.d_k[tid]) + 1e-8f);
+    if (tid >= 64 && tid < 64 + KD_LUT_ENTRIES) lut[tid - 64] = kd_make_lut_entry((uint32_t)(tid - 64));
+    for (int e = tid; e < 2 * 16 * 32; e += M2_THREADS) {
+        const int kind = e >> 9, s = (e >> 5) & 15, lane = e & 31;
+        const int g = lane >> 2, t = lane & 3;
+        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // dims 64t+4s + {0, 2, 1, 3}
+        if ((g >> 2) == (s & 1)) {
+            const int c = g & 3, patch = 16 * t + s;
+            const int kk[4] = {0, 2, 1, 3};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float r = __half2float(P.k_rotor[patch * 16 + c * 4 + kk[i]]);
+                if (kind == 0) r *= __half2float(P.cents_k[2 * D + 64 * t + 4 * s + kk[i]]);
+                v[i] = r;
+            }
+        }
+        brot[e] = make_uint2(m2_pack(v[0], v[1]), m2_pack(v[2], v[3]));
+    }
+    const unsigned int* src = reinterpret_cast<const unsigned int*>(P.vq);
+    for (int w = tid; w < NP * 256 * 3 / 2; w += M2_THREADS) {
+        const unsigned int two = __ldg(src + w);
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+            const int hidx = 2 * w + b;
+            const int entry = hidx / 3, k = hidx - entry * 3;
+            const int patch = entry >> 8, code = entry & 255;
+            vq_s[(code * 64 + patch) * 4 + k] = (unsigned short)(two >> (16 * b));
+        }
+    }
+}
+
+// Query-side operands of one (sequence, layer, kv-head): this warp's B fragments.
+struct M2Query {
+    uint32_t q1[16][2];  // q~ * c   (ternary part), per k-step
+    uint32_t q2[16][2];  // q~       (residual part)
+    uint32_t qr[4][2];   // raw rotary query dims 0..63
+};
+
+// q: (H_q, ..) with `q_head_stride` halfs between heads.  scratch: this warp's NREP*D floats.
+__device__ __forceinline__ void m2_build_query(M2Query& Q, const __half* __restrict__ q, size_t q_head_stride,
+                                               const CompressedKV& P, int kvh, int lane, float* scratch) {
+    const int g = lane >> 2, t = lane & 3;
+    // q~ in the lane-owns-8-dims layout: q~ = R^T H256 (q * dinv * [dim >= 64])
+    float dv[8], rr[2][16];
+    {
+        const uint4 dr = *reinterpret_cast<const uint4*>(P.d_k + lane * 8);
+        const __half* hd = reinterpret_cast<const __half*>(&dr);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dv[j] = (lane >= 8) ? (1.0f / 256.0f) / (__half2float(hd[j]) + 1e-8f) : 0.0f;
+#pragma unroll
+        for (int p = 0; p < 2; ++p)
+#pragma unroll
+            for (int i = 0; i < 16; ++i) rr[p][i] = __half2float(P.k_rotor[(lane * 2 + p) * 16 + i]);
+    }
+#pragma unroll 1
+    for (int h = 0; h < NREP; ++h) {
+        const uint4 qraw = *reinterpret_cast<const uint4*>(q + (size_t)(kvh * NREP + h) * q_head_stride + lane * 8);
+        const __half* hq = reinterpret_cast<const __half*>(&qraw);
+        float x[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] = __half2float(hq[j]) * dv[j];
+        fwht256_lane8(x, lane);
+#pragma unroll
+        for (int p = 0; p < 2; ++p)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float a = 0.0f;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) a = fmaf(rr[p][c * 4 + k], x[p * 4 + c], a);
+                scratch[h * D + lane * 8 + p * 4 + k] = a;
+            }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int s = 0; s < 16; ++s) {
+        const int d0 = 64 * t + 4 * s;
+        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f}, c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (g < NREP) {
+            const float4 qq = *reinterpret_cast<const float4*>(scratch + g * D + d0);
+            const uint2 cc = *reinterpret_cast<const uint2*>(P.cents_k + 2 * D + d0);
+            const __half* hc = reinterpret_cast<const __half*>(&cc);
+            v[0] = qq.x; v[1] = qq.z; v[2] = qq.y; v[3] = qq.w;  // dims d0 + {0, 2, 1, 3}
+            c[0] = __half2float(hc[0]); c[1] = __half2float(hc[2]); c[2] = __half2float(hc[1]); c[3] = __half2float(hc[3]);
+        }
+        Q.q1[s][0] = m2_pack(v[0] * c[0], v[1] * c[1]);
+        Q.q1[s][1] = m2_pack(v[2] * c[2], v[3] * c[3]);
+        Q.q2[s][0] = m2_pack(v[0], v[1]);
+        Q.q2[s][1] = m2_pack(v[2], v[3]);
+    }
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+        uint32_t b0 = 0, b1 = 0;
+        if (g < NREP) {
+            const __half* qh = q + (size_t)(kvh * NREP + g) * q_head_stride + 16 * kk + 2 * t;
+            b0 = *reinterpret_cast<const uint32_t*>(qh);
+            b1 = *reinterpret_cast<const uint32_t*>(qh + 8);
+        }
+        Q.qr[kk][0] = b0;
+        Q.qr[kk][1] = b1;
+    }
+    __syncwarp();
+}
+
+// Running attention state of a warp in fragment layout: thread (g, t) holds heads 2t, 2t+1.
+struct M2State {
+    float o[16][4];  // O^T tiles: [0..11] dims 0..2 of the patches, [12..15] dim 3 of the patches
+    float m[2], l[2];
+    __device__ __forceinline__ void init() {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+        m[0] = m[1] = NEG_BIG;
+        l[0] = l[1] = 0.0f;
+    }
+};
+
+// One block of 16 tokens (rows r0..r0+15 of the staged tile) of kv-head `kvh`.
+// valid_lo/valid_hi: block-relative range of tokens that belong to the caller's range.
+__device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, const unsigned char* __restrict__ smem,
+                                         const float2* __restrict__ rope, int r0, int kvh, int lane, int valid_lo,
+                                         int valid_hi, const M2Query& Q, const CompressedKV& P, float scale,
+                                         const float (&c3)[8][2], M2State& st) {
+    const int g = lane >> 2, t = lane & 3;
+    const KdLutEntry* lut = reinterpret_cast<const KdLutEntry*>(smem + M2_SM_LUT);
+    const uint2* brot = reinterpret_cast<const uint2*>(smem + M2_SM_BROT);
+    const float* dinv_s = reinterpret_cast<const float*>(smem + M2_SM_DINV);
+    const unsigned char* vq_s = smem + M2_SM_VQ;
+
+    // ================================ K side: scores ==========================================
+    const uint32_t* kp[2];
+    uint4 mw[2];
+    KdStream ks[2];
+    float sp[2];
+    uint32_t ratio2[2];
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        const int row = (r0 + g + 8 * x) * HKV + kvh;
+        kp[x] = reinterpret_cast<const uint32_t*>(S + M2_OFF_KPAY + row * K_PAY);
+        mw[x] = *reinterpret_cast<const uint4*>(S + M2_OFF_MASK + row * 64 + 16 * t);
+        // outliers of this thread's quarter, then the ordinal of its first one (scan over the quad)
+        int cnt = __popc(kd_word(mw[x].x).X3) + __popc(kd_word(mw[x].y).X3) + __popc(kd_word(mw[x].z).X3) +
+                  __popc(kd_word(mw[x].w).X3);
+        int incl = cnt;
+        int up = __shfl_up_sync(0xFFFFFFFFu, incl, 1);
+        if (t >= 1) incl += up;
+        up = __shfl_up_sync(0xFFFFFFFFu, incl, 2);
+        if (t >= 2) incl += up;
+        const uint32_t base = (uint32_t)(incl - cnt);
+        ks[x].pos4 = 4u * base;
+        kd_sign_window(kp[x], base, ks[x].sg_lo, ks[x].sg_hi);
+        float mult = (float)kp[x][0] / 1000.0f;
+        if (mult < 0.1f || mult > 10.0f || isnan(mult)) mult = 1.0f;
+        const float rs = hbits2f(reinterpret_cast<const uint16_t*>(S + M2_OFF_KRN)[row]);
+        const float kn = hbits2f(reinterpret_cast<const uint16_t*>(S + M2_OFF_KN)[row]);
+        sp[x] = P.alpha_k * kn * mult * scale;
+        const float ratio = rs / mult;
+        ratio2[x] = m2_pack(ratio, ratio);
+    }
+    const uint32_t neg1024 = 0xE400E400u;  // fp16x2 (-1024, -1024)
+    float cs[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // pass-part scores: rows g (0,1) and g+8 (2,3), heads 2t, 2t+1
+    float cu[8][4];                          // rotor block sums u[token, 8j + n]
+#pragma unroll
+    for (int j = 0; j < 8; ++j) cu[j][0] = cu[j][1] = cu[j][2] = cu[j][3] = 0.0f;
+#pragma unroll
+    for (int wi = 0; wi < 4; ++wi) {
+        const uint32_t wa = wi == 0 ? mw[0].x : wi == 1 ? mw[0].y : wi == 2 ? mw[0].z : mw[0].w;
+        const uint32_t wb = wi == 0 ? mw[1].x : wi == 1 ? mw[1].y : wi == 2 ? mw[1].z : mw[1].w;
+        const KdWord kwa = kd_word(wa), kwb = kd_word(wb);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int s = wi * 4 + q;
+            const KdStep a = kd_step(kwa, q, ks[0], kp[0], lut);
+            const KdStep b = kd_step(kwb, q, ks[1], kp[1], lut);
+            const uint32_t a1[4] = {a.t0, b.t0, a.t1, b.t1};
+            const uint32_t a2[4] = {m2_hmul2(m2_hfma2(a.t0, neg1024, a.h0), ratio2[0]),
+                                    m2_hmul2(m2_hfma2(b.t0, neg1024, b.h0), ratio2[1]),
+                                    m2_hmul2(m2_hfma2(a.t1, neg1024, a.h1), ratio2[0]),
+                                    m2_hmul2(m2_hfma2(b.t1, neg1024, b.h1), ratio2[1])};
+            const uint2 b1 = brot[s * 32 + lane], b2 = brot[512 + s * 32 + lane];
+            m2_mma(cs, a1, Q.q1[s][0], Q.q1[s][1]);
+            m2_mma(cs, a2, Q.q2[s][0], Q.q2[s][1]);
+            m2_mma(cu[s >> 1], a1, b1.x, b1.y);
+            m2_mma(cu[s >> 1], a2, b2.x, b2.y);
+        }
+    }
+    // ---- rotary part: H64 over idx = 8j + 2t + e, /d, rotation, dot with the raw query ----------
+    float cr[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    {
+        // bit 0 (e)
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+                const float a = cu[j][2 * x], b = cu[j][2 * x + 1];
+                cu[j][2 * x] = a + b;
+                cu[j][2 * x + 1] = a - b;
+            }
+        // bits 1, 2 (t): across the quad
+#pragma unroll
+        for (int m = 1; m <= 2; m <<= 1) {
+            const bool lower = (t & m) == 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float other = __shfl_xor_sync(0xFFFFFFFFu, cu[j][e], m);
+                    cu[j][e] = lower ? (cu[j][e] + other) : (other - cu[j][e]);
+                }
+        }
+        // bits 3, 4, 5 (j)
+#pragma unroll
+        for (int m = 1; m <= 4; m <<= 1)
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if ((j & m) == 0)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float a = cu[j][e], b = cu[j | m][e];
+                        cu[j][e] = a + b;
+                        cu[j | m][e] = a - b;
+                    }
+        // scale by dinv, rotate pairs (idx, idx + 32) = tiles (j, j + 4)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 dlo = *reinterpret_cast<const float2*>(dinv_s + 8 * j + 2 * t);
+            const float2 dhi = *reinterpret_cast<const float2*>(dinv_s + 32 + 8 * j + 2 * t);
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+                const float4 rc = *reinterpret_cast<const float4*>(rope + (r0 + g + 8 * x) * 32 + 8 * j + 2 * t);
+                const float z0 = cu[j][2 * x] * dlo.x, z1 = cu[j][2 * x + 1] * dlo.y;
+                const float w0 = cu[j + 4][2 * x] * dhi.x, w1 = cu[j + 4][2 * x + 1] * dhi.y;
+                cu[j][2 * x] = z0 * rc.x - w0 * rc.y;
+                cu[j + 4][2 * x] = z0 * rc.y + w0 * rc.x;
+                cu[j][2 * x + 1] = z1 * rc.z - w1 * rc.w;
+                cu[j + 4][2 * x + 1] = z1 * rc.w + w1 * rc.z;
+            }
+        }
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+            const uint32_t a[4] = {m2_pack(cu[2 * kk][0], cu[2 * kk][1]), m2_pack(cu[2 * kk][2], cu[2 * kk][3]),
+                                   m2_pack(cu[2 * kk + 1][0], cu[2 * kk + 1][1]),
+                                   m2_pack(cu[2 * kk + 1][2], cu[2 * kk + 1][3])};
+            m2_mma(cr, a, Q.qr[kk][0], Q.qr[kk][1]);
+        }
+    }
+    // ================================ softmax over the block ====================================
+    float sc[2][2], pw[2][2];  // [row x: g, g+8][head e: 2t, 2t+1]
+    bool valid[2];
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        valid[x] = (g + 8 * x) >= valid_lo && (g + 8 * x) < valid_hi;
+#pragma unroll
+        for (int e = 0; e < 2; ++e) sc[x][e] = valid[x] ? sp[x] * (cs[2 * x + e] + cr[2 * x + e]) : -1e30f;
+    }
+    float corr[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        float bm = fmaxf(sc[0][e], sc[1][e]);
+        bm = fmaxf(bm, __shfl_xor_sync(0xFFFFFFFFu, bm, 4));
+        bm = fmaxf(bm, __shfl_xor_sync(0xFFFFFFFFu, bm, 8));
+        bm = fmaxf(bm, __shfl_xor_sync(0xFFFFFFFFu, bm, 16));
+        const float mn = fmaxf(st.m[e], bm);
+        corr[e] = __expf(st.m[e] - mn);
+        st.m[e] = mn;
+        pw[0][e] = valid[0] ? __expf(sc[0][e] - mn) : 0.0f;
+        pw[1][e] = valid[1] ? __expf(sc[1][e] - mn) : 0.0f;
+        st.l[e] = st.l[e] * corr[e] + pw[0][e] + pw[1][e];
+    }
+    if (__any_sync(0xFFFFFFFFu, corr[0] != 1.0f || corr[1] != 1.0f)) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            st.o[i][0] *= corr[0];
+            st.o[i][1] *= corr[1];
+            st.o[i][2] *= corr[0];
+            st.o[i][3] *= corr[1];
+        }
+    }
+    // three scaled variants of P, transposed into B fragments (tokens = k, heads = n)
+    uint32_t pb[3][2];
+    {
+        float s1[2], s2[2], s3[2];
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+            const int row = (r0 + g + 8 * x) * HKV + kvh;
+            const float vn = hbits2f(reinterpret_cast<const uint16_t*>(S + M2_OFF_VN)[row]);
+            const float en = hbits2f(reinterpret_cast<const uint16_t*>(S + M2_OFF_VRN)[row]);
+            const float sm = reinterpret_cast<const float*>(S + M2_OFF_VSM)[row];
+            s1[x] = valid[x] ? P.alpha_v * vn * en : 0.0f;     // dims 0..2: codebook entry
+            s2[x] = valid[x] ? vn : 0.0f;                      // dim 3: centroid * alpha_v (folded in c3)
+            s3[x] = valid[x] ? sm * vn * (1.0f / 7.0f) : 0.0f;  // dim 3: (dump - 8)
+        }
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+            pb[0][x] = m2_movmatrix_t(m2_pack(pw[x][0] * s1[x], pw[x][1] * s1[x]));
+            pb[1][x] = m2_movmatrix_t(m2_pack(pw[x][0] * s2[x], pw[x][1] * s2[x]));
+            pb[2][x] = m2_movmatrix_t(m2_pack(pw[x][0] * s3[x], pw[x][1] * s3[x]));
+        }
+    }
+    // ================================ V side: O^T += V^T P^T ====================================
+    // thread (g, t): patch group g of tokens 2t, 2t+1, 2t+8, 2t+9
+    uint32_t vw[4][3], hb[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int tok = 2 * t + (i & 1) + 8 * (i >> 1);
+        const uint32_t* vp = reinterpret_cast<const uint32_t*>(S + M2_OFF_VPAY + ((r0 + tok) * HKV + kvh) * V_PAY);
+        vw[i][0] = vp[3 * g];
+        vw[i][1] = vp[3 * g + 1];
+        vw[i][2] = vp[3 * g + 2];
+        hb[i] = (vp[24 + (g >> 2)] >> (8 * (g & 3))) & 0xFFu;
+    }
+#pragma unroll
+    for (int pp = 0; pp < 4; ++pp) {  // patch pairs (2pp, 2pp+1) -> tiles 3pp .. 3pp+2
+        uint32_t ex[2][4], ey[2][4];  // [patch of the pair][token i]: (d0,d1), (d2,-)
+        uint32_t f3[2][4];            // 12-bit fields
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int pl = 2 * pp + u;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint32_t f;
+                switch (pl) {
+                    case 0: f = vw[i][0]; break;
+                    case 1: f = vw[i][0] >> 12; break;
+                    case 2: f = (vw[i][0] >> 24) | (vw[i][1] << 8); break;
+                    case 3: f = vw[i][1] >> 4; break;
+                    case 4: f = vw[i][1] >> 16; break;
+                    case 5: f = (vw[i][1] >> 28) | (vw[i][2] << 4); break;
+                    case 6: f = vw[i][2] >> 8; break;
+                    default: f = vw[i][2] >> 20; break;
+                }
+                f &= 0xFFFu;
+                f3[u][i] = f;
+                const uint32_t code = (f & 0x7Fu) | (((hb[i] >> pl) & 1u) << 7);
+                const uint2 e = *reinterpret_cast<const uint2*>(vq_s + (code * 64 + 8 * g + pl) * 8);
+                ex[u][i] = e.x;
+                ey[u][i] = e.y;
+            }
+        }
+        // rows: idx = 2j + r -> (patch idx/3, dim idx%3); the pair's six (patch, dim) rows in order
+        uint32_t lo[6], hi[6];  // token pairs (2t, 2t+1) and (2t+8, 2t+9)
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            lo[3 * u + 0] = __byte_perm(ex[u][0], ex[u][1], 0x5410);
+            lo[3 * u + 1] = __byte_perm(ex[u][0], ex[u][1], 0x7632);
+            lo[3 * u + 2] = __byte_perm(ey[u][0], ey[u][1], 0x5410);
+            hi[3 * u + 0] = __byte_perm(ex[u][2], ex[u][3], 0x5410);
+            hi[3 * u + 1] = __byte_perm(ex[u][2], ex[u][3], 0x7632);
+            hi[3 * u + 2] = __byte_perm(ey[u][2], ey[u][3], 0x5410);
+        }
+#pragma unroll
+        for (int jj = 0; jj < 3; ++jj) {
+            const uint32_t a[4] = {lo[2 * jj], lo[2 * jj + 1], hi[2 * jj], hi[2 * jj + 1]};
+            m2_mma(st.o[3 * pp + jj], a, pb[0][0], pb[0][1]);
+        }
+        // dim 3 of the two patches (rows 0, 1 of tile 12 + pp): centroid choice and (dump - 8)
+        uint32_t ca[4], da[4];  // a0..a3 of the two extra MMAs
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int pl = 2 * pp + u;
+            float cv[4];
+            uint32_t dv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                cv[i] = ((f3[u][i] >> 7) & 1u) ? c3[pl][1] : c3[pl][0];
+                dv[i] = 0x6400u | (f3[u][i] >> 8);  // fp16 bits of 1024 + dump
+            }
+            ca[u] = m2_pack(cv[0], cv[1]);
+            ca[2 + u] = m2_pack(cv[2], cv[3]);
+            const uint32_t bias = 0x64086408u;  // fp16x2 (1032, 1032): (1024 + dump) - 1032 = dump - 8
+            const uint32_t plo = dv[0] | (dv[1] << 16), phi = dv[2] | (dv[3] << 16);
+            const __half2 d_lo = __hsub2(*reinterpret_cast<const __half2*>(&plo), *reinterpret_cast<const __half2*>(&bias));
+            const __half2 d_hi = __hsub2(*reinterpret_cast<const __half2*>(&phi), *reinterpret_cast<const __half2*>(&bias));
+            da[u] = *reinterpret_cast<const uint32_t*>(&d_lo);
+            da[2 + u] = *reinterpret_cast<const uint32_t*>(&d_hi);
+        }
+        m2_mma(st.o[12 + pp], ca, pb[1][0], pb[1][1]);
+        m2_mma(st.o[12 + pp], da, pb[2][0], pb[2][1]);
+    }
+}
+
+// Attention of all 24 query heads over compressed tokens [my_lo, my_hi) of P; the CTA's 8 warps
+// are (kv-head = warp & 3) x (16-token half of each 32-token tile = warp >> 2).  On return,
+// warps 0..3 have written the merged, inverse-transformed partial of their kv-head's six heads
+// to ob[0..5] (each a (258,) record).  Tables must be set up; all 256 threads call it.
+__device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const __half* __restrict__ q,
+                                                    size_t q_head_stride, const CompressedKV& P, int my_lo, int my_hi,
+                                                    float scale, unsigned& tiles_done, float* const (&ob)[NREP]) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kvh = warp & 3, sub = warp >> 2, g = lane >> 2, t = lane & 3;
+    float2* rope_tab = reinterpret_cast<float2*>(smem + M2_SM_ROPE);
+    const float* freq_s = reinterpret_cast<const float*>(smem + M2_SM_FREQ);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + M2_SM_BARS);
+
+    M2Query Q;
+    m2_build_query(Q, q, q_head_stride, P, kvh, lane, reinterpret_cast<float*>(smem + M2_SM_STAGES) + warp * NREP * D);
+    float c3[8][2];
+#pragma unroll
+    for (int pl = 0; pl < 8; ++pl) {
+        c3[pl][0] = __half2float(P.cents_v[0 * D + (8 * g + pl) * 4 + 3]) * P.alpha_v;
+        c3[pl][1] = __half2float(P.cents_v[1 * D + (8 * g + pl) * 4 + 3]) * P.alpha_v;
+    }
+    __syncthreads();  // the query scratch aliases the stages
+
+    const int base = my_lo & ~1;
+    const int ntiles = (my_hi > my_lo) ? (my_hi - base + M2_TT - 1) / M2_TT : 0;
+    const unsigned t0 = tiles_done;
+    if (ntiles > 0) {
+        m2_fill_rope(rope_tab, freq_s, P.start_pos + base, tid);
+        m2_stage_tile(P, smem + M2_SM_STAGES + (t0 % M2_NSTAGE) * M2_STAGE_BYTES, &bars[t0 % M2_NSTAGE], base,
+                      min(M2_TT, P.c_len - base), tid);
+    }
+    __syncthreads();
+    M2State st;
+    st.init();
+#pragma unroll 1
+    for (int i = 0; i < ntiles; ++i) {
+        const unsigned gi = t0 + i;
+        const int stg = gi % M2_NSTAGE;
+        if (i + 1 < ntiles) {
+            const int tok0 = base + (i + 1) * M2_TT;
+            m2_stage_tile(P, smem + M2_SM_STAGES + ((gi + 1) % M2_NSTAGE) * M2_STAGE_BYTES, &bars[(gi + 1) % M2_NSTAGE],
+                          tok0, min(M2_TT, P.c_len - tok0), tid);
+            m2_fill_rope(rope_tab + ((i + 1) & 1) * M2_TT * 32, freq_s, P.start_pos + tok0, tid);
+        }
+        mbar_wait_bounded(&bars[stg], (uint32_t)((gi / M2_NSTAGE) & 1), &g_status);
+        const int blk0 = base + i * M2_TT + 16 * sub;
+        const int vlo = max(my_lo - blk0, 0), vhi = min(my_hi - blk0, 16);
+        if (vhi > vlo)
+            m2_block(smem + M2_SM_STAGES + stg * M2_STAGE_BYTES, smem, rope_tab + (i & 1) * M2_TT * 32, 16 * sub, kvh,
+                     lane, vlo, vhi, Q, P, scale, c3, st);
+        __syncthreads();  // stage and rope buffer free for the tile after next
+    }
+    tiles_done = t0 + (unsigned)ntiles;
+
+    // ---- per-warp record in the first generation's layout, then merge + inverse V transform --------
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        st.l[e] += __shfl_xor_sync(0xFFFFFFFFu, st.l[e], 4);
+        st.l[e] += __shfl_xor_sync(0xFFFFFFFFu, st.l[e], 8);
+        st.l[e] += __shfl_xor_sync(0xFFFFFFFFu, st.l[e], 16);
+    }
+    float* rec = reinterpret_cast<float*>(smem + M2_SM_STAGES) + warp * MERGE_FLOATS;
+    if (t < 3) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const int idx = 2 * j + r;
+                const int dim = j < 12 ? 4 * (8 * g + idx / 3) + idx % 3 : 4 * (8 * g + 2 * (j - 12) + r) + 3;
+                rec[(2 * t) * D + dim] = st.o[j][2 * r];
+                rec[(2 * t + 1) * D + dim] = st.o[j][2 * r + 1];
+            }
+        if (g == 0) {
+            rec[NREP * D + 2 * t] = st.m[0];
+            rec[NREP * D + 2 * t + 1] = st.m[1];
+            rec[NREP * D + NREP + 2 * t] = st.l[0];
+            rec[NREP * D + NREP + 2 * t + 1] = st.l[1];
+        }
+    }
+    __syncthreads();
+    if (warp < 4) {
+        WarpState ws;
+        ws.init();
+        merge_from(ws, reinterpret_cast<const float*>(smem + M2_SM_STAGES) + warp * MERGE_FLOATS, lane);
+        merge_from(ws, reinterpret_cast<const float*>(smem + M2_SM_STAGES) + (warp + 4) * MERGE_FLOATS, lane);
+        v_epilogue_store(ws, P, lane, ob);
+    }
+}
+
+// Persistent batched kernel, second generation (same contract as khq_decode_batched_kernel).
+__global__ void __launch_bounds__(M2_THREADS, 1)
+khq_decode_batched_mma_kernel(const KhqSeqDesc* __restrict__ descs, const KhqTablesDesc* __restrict__ tables,
+                              const KhqWorkItem* __restrict__ items, int n_items, int* __restrict__ counter,
+                              float* __restrict__ partials, float scale, float rope_base, int ring_cap) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ int s_next;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kvh = warp & 3, sub = warp >> 2;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + M2_SM_BARS);
+    if (tid == 0) {
+        for (int s = 0; s < M2_NSTAGE; ++s) mbar_init(&bars[s], 1);
+        fence_barrier_init();
+    }
+    int cur_table = -1;
+    unsigned tiles_done = 0;
+#pragma unroll 1
+    while (true) {
+        __syncthreads();
+        if (tid == 0) s_next = atomicAdd(counter, 1);
+        __syncthreads();
+        const int it = s_next;
+        if (it >= n_items) break;
+        const KhqWorkItem w = items[it];
+        const KhqSeqDesc d = descs[w.desc];
+        float* ob[NREP];
+#pragma unroll
+        for (int h = 0; h < NREP; ++h) ob[h] = partials + ((size_t)w.slot * HQ + kvh * NREP + h) * PART;
+        if (w.kind == 0) {
+            const KhqTablesDesc tb = tables[d.table_id];
+            CompressedKV P;
+            P.k_payload = d.k_payload; P.v_payload = d.v_payload; P.v_shared_meta = d.v_shared_meta;
+            P.k_mask = d.k_mask; P.k_norms = d.k_norms; P.k_r_norms = d.k_r_norms;
+            P.v_norms = d.v_norms; P.v_r_norms = d.v_r_norms;
+            P.cents_k = tb.cents_k; P.cents_v = tb.cents_v; P.vq = tb.vq; P.k_rotor = tb.k_rotor;
+            P.v_rotor = tb.v_rotor; P.d_k = tb.d_k; P.d_v = tb.d_v;
+            P.alpha_k = tb.alpha_k; P.alpha_v = tb.alpha_v; P.rope_base = rope_base;
+            P.start_pos = d.start_pos; P.c_len = d.c_len; P.bulk_ok = 1;
+            if (d.table_id != cur_table) {
+                m2_setup_tables(smem, P, tid);
+                cur_table = d.table_id;
+                __syncthreads();
+            }
+            m2_compressed_range(smem, d.q_gate, (size_t)2 * D, P, w.lo, w.hi, scale, tiles_done, ob);
+        } else {
+            WarpState ws;
+            ws.init();
+            window_range(d.q_gate, d.ring_k, d.ring_v, d.win_start, w.lo + sub, 2, w.hi, ring_cap, scale, kvh, lane, ws);
+            float* rec = reinterpret_cast<float*>(smem + M2_SM_STAGES) + kvh * MERGE_FLOATS;
+            if (sub == 1) store_record(ws, rec, lane);
+            __syncthreads();
+            if (sub == 0) {
+                merge_from(ws, rec, lane);
+                raw_store(ws, lane, ob);
+            }
+        }
+    }
+}
+
+}  // namespace khq

@@ -1,0 +1,22 @@
+"""Compiles and runs tests/host/test_kdecode.cpp: the register-level K code-word decode used by
+the tensor-core decode kernel (byte-permute look-ups, outlier stream scatter, sign handling,
+rows with more than 50 outlier symbols) against a plain per-dim decode, on the CPU."""
+import shutil
+import subprocess
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_register_level_k_decode_matches_plain_decode(tmp_path):
+    cxx = shutil.which("g++")
+    if cxx is None:
+        pytest.skip("no host C++ compiler")
+    exe = tmp_path / "test_kdecode"
+    subprocess.run([cxx, "-O2", "-std=c++17", "-I", str(ROOT / "bonsai_mojo_1bit_optimization_t4_cuda_b200" / "csrc"),
+                    "-o", str(exe), str(ROOT / "tests" / "host" / "test_kdecode.cpp")], check=True)
+    res = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert res.stdout.startswith("ok")
