@@ -654,10 +654,10 @@ static inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<u
 
 template <typename Kernel, typename... Args>
 static cudaError_t launch_cluster(Kernel kernel, unsigned grid, unsigned cluster, size_t smem_bytes,
-                                  cudaStream_t stream, Args... args) {
+                                  cudaStream_t stream, unsigned threads, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);
-    cfg.blockDim = dim3(DEC_THREADS, 1, 1);
+    cfg.blockDim = dim3(threads, 1, 1);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -683,6 +683,7 @@ static cudaError_t ensure_smem_attrs() {
     if ((e = cudaFuncSetAttribute(khq_decode_batched_kernel<false>, attr, SM_TOTAL)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(khq_decode_batched_kernel<true>, attr, SM_TOTAL_VQ)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(khq_decode_batched_mma_kernel, attr, M2_SM_TOTAL)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(khq_attn_compressed_mma_kernel, attr, M2_SM_TOTAL)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(khq_window_attn_kernel, attr, 2 * HKV * MERGE_FLOATS * 4)) != cudaSuccess)
         return e;
     if (dev >= 0 && dev < 64) done[dev] = true;
@@ -764,14 +765,15 @@ extern "C" int launch_khq_attn_fp16(const void* q, const void* k_payload, const 
         if (cluster > 8) cluster = 8;
         // Staging the 128 KB V codebook in shared memory pays once a CTA decodes a few hundred tokens.
         const int tok_per_cta = (per + cluster - 1) / cluster;
-        if (tok_per_cta >= 192)
-            err = launch_cluster(khq_attn_compressed_kernel<true>, (unsigned)(num_splits * cluster),
-                                 (unsigned)cluster, (size_t)SM_TOTAL_VQ, stream, static_cast<const __half*>(q), P,
+        if (tok_per_cta >= 192)  // tensor-core generation: its per-CTA table set-up pays from here on
+            err = launch_cluster(khq_attn_compressed_mma_kernel, (unsigned)(num_splits * cluster), (unsigned)cluster,
+                                 (size_t)M2_SM_TOTAL, stream, (unsigned)M2_THREADS, static_cast<const __half*>(q), P,
                                  static_cast<float*>(out_attn), static_cast<float*>(out_partial), num_splits, L_q,
                                  l, s_limit, scale);
         else
             err = launch_cluster(khq_attn_compressed_kernel<false>, (unsigned)(num_splits * cluster),
-                                 (unsigned)cluster, (size_t)SM_TOTAL, stream, static_cast<const __half*>(q), P,
+                                 (unsigned)cluster, (size_t)SM_TOTAL, stream, (unsigned)DEC_THREADS,
+                                 static_cast<const __half*>(q), P,
                                  static_cast<float*>(out_attn), static_cast<float*>(out_partial), num_splits, L_q,
                                  l, s_limit, scale);
         if (err != cudaSuccess) return static_cast<int>(err);
@@ -797,8 +799,8 @@ extern "C" int launch_khq_window_attn_fp16(const void* q, const void* ring_k, co
     if (cluster < 1) cluster = 1;
     if (cluster > 8) cluster = 8;
     err = launch_cluster(khq_window_attn_kernel, (unsigned)cluster, (unsigned)cluster,
-                         (size_t)(2 * HKV * MERGE_FLOATS * 4), stream, static_cast<const __half*>(q),
-                         static_cast<const __half*>(ring_k), static_cast<const __half*>(ring_v),
+                         (size_t)(2 * HKV * MERGE_FLOATS * 4), stream, (unsigned)DEC_THREADS,
+                         static_cast<const __half*>(q), static_cast<const __half*>(ring_k), static_cast<const __half*>(ring_v),
                          static_cast<float*>(out_attn), win_start, win_len, ring_cap, scale);
     return (err == cudaSuccess) ? 0 : static_cast<int>(err);
 }
@@ -891,8 +893,8 @@ extern "C" int launch_khq_decode_batched_fp16(const void* descs, const void* tab
     int* counter = static_cast<int*>(workspace);
     float* partials = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + 256);
     const int grid = n_items < sm_count() ? n_items : sm_count();
-    const bool vqs = codebook_in_smem < 0 ? (n_items >= 1) : (codebook_in_smem != 0);
-    if (codebook_in_smem == 2)
+    const bool vqs = codebook_in_smem != 0;
+    if (codebook_in_smem == 2 || codebook_in_smem < 0)
         khq_decode_batched_mma_kernel<<<grid, M2_THREADS, M2_SM_TOTAL, stream>>>(
             static_cast<const KhqSeqDesc*>(descs), static_cast<const KhqTablesDesc*>(tables),
             static_cast<const KhqWorkItem*>(items), n_items, counter, partials, scale, rope_base, ring_cap);

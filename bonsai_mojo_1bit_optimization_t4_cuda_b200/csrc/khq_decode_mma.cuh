@@ -41,15 +41,25 @@ constexpr int M2_OFF_VSM = M2_OFF_VRN + M2_ROWS * 2;
 constexpr int M2_STAGE_BYTES = M2_OFF_VSM + M2_ROWS * 4;  // 28160
 
 constexpr int M2_SM_STAGES = 0;
-constexpr int M2_SM_VQ = M2_SM_STAGES + M2_NSTAGE * M2_STAGE_BYTES;  // 256 x 64 x 8 B
-constexpr int M2_SM_ROPE = M2_SM_VQ + 256 * NP * 8;                  // 2 x 32 tokens x 32 float2
-constexpr int M2_SM_BROT = M2_SM_ROPE + 2 * M2_TT * 32 * 8;          // 2 kinds x 16 steps x 32 lanes x 8 B
-constexpr int M2_SM_LUT = M2_SM_BROT + 2 * 16 * 32 * 8;              // scatter table
+// V codebook, split so that it fits beside everything else: (d0, d1) as one 32-bit word per
+// (code, patch) and d2 as one half.  Rows of 65 words / 65 halfs instead of 64: the bank of a
+// look-up then depends on the code as well as on the patch, which spreads the warp's 32
+// look-ups (8 patches x 4 tokens per instruction) over the banks.
+constexpr int M2_VQA_STRIDE = 65;                                    // words per code row
+constexpr int M2_VQB_STRIDE = 130;                                   // bytes per code row
+constexpr int M2_SM_VQ = M2_SM_STAGES + M2_NSTAGE * M2_STAGE_BYTES;  // (d0, d1): 256 x 65 x 4 B
+constexpr int M2_SM_VQB = M2_SM_VQ + 256 * M2_VQA_STRIDE * 4;        // d2: 256 x 130 B
+constexpr int M2_SM_ROPE = M2_SM_VQB + 256 * M2_VQB_STRIDE;          // 2 x 32 tokens x 32 float2
+constexpr int M2_SM_BROT = M2_SM_ROPE + 2 * M2_TT * 32 * 8;          // 3 kinds x 16 steps x 32 lanes x 8 B
+constexpr int M2_SM_LUT = M2_SM_BROT + 3 * 16 * 32 * 8;              // scatter table
 constexpr int M2_SM_FREQ = M2_SM_LUT + 448;
 constexpr int M2_SM_DINV = M2_SM_FREQ + 128;                         // 64 floats
 constexpr int M2_SM_BARS = M2_SM_DINV + 256;
-constexpr int M2_SM_TOTAL = M2_SM_BARS + 64;
-static_assert(M2_SM_TOTAL <= 227 * 1024, "shared memory budget");
+constexpr int M2_SM_QLO = M2_SM_BARS + 64;                           // 2 kinds x 4 kv-heads x 16 steps x 32 lanes x 8 B
+constexpr int M2_SM_TOTAL = M2_SM_QLO + 2 * HKV * 16 * 32 * 8;
+static_assert(M2_SM_TOTAL <= 227 * 1024 && M2_SM_QLO % 16 == 0 && M2_SM_ROPE % 16 == 0 && M2_SM_VQB % 16 == 0,
+              "shared memory budget");
+static_assert(HKV * MERGE_FLOATS * 4 <= 256 * M2_VQA_STRIDE * 4, "cluster export records alias the codebook");
 static_assert(8 * MERGE_FLOATS * 4 <= M2_NSTAGE * M2_STAGE_BYTES, "records alias the stages");
 static_assert(8 * NREP * D * 4 <= M2_NSTAGE * M2_STAGE_BYTES, "prologue scratch aliases the stages");
 static_assert(M2_STAGE_BYTES % 16 == 0 && M2_OFF_KPAY % 16 == 0 && M2_OFF_VPAY % 16 == 0 && M2_OFF_KN % 16 == 0 &&
@@ -69,6 +79,12 @@ __device__ __forceinline__ uint32_t m2_movmatrix_t(uint32_t x) {
 __device__ __forceinline__ uint32_t m2_pack(float lo, float hi) {
     const __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&h);
+}
+// fp16x2 of (a, b) and fp16x2 of what that rounding lost: hi + lo carries ~22 mantissa bits.
+__device__ __forceinline__ void m2_pack_hilo(float a, float b, uint32_t& hi, uint32_t& lo) {
+    const __half2 h = __floats2half2_rn(a, b);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    lo = m2_pack(a - __low2float(h), b - __high2float(h));
 }
 __device__ __forceinline__ uint32_t m2_hfma2(uint32_t a, uint32_t b, uint32_t c) {
     const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b),
@@ -135,25 +151,30 @@ __device__ __forceinline__ void m2_setup_tables(unsigned char* smem, const Compr
     float* dinv_s = reinterpret_cast<float*>(smem + M2_SM_DINV);
     KdLutEntry* lut = reinterpret_cast<KdLutEntry*>(smem + M2_SM_LUT);
     uint2* brot = reinterpret_cast<uint2*>(smem + M2_SM_BROT);
-    unsigned short* vq_s = reinterpret_cast<unsigned short*>(smem + M2_SM_VQ);
+    unsigned short* vqa = reinterpret_cast<unsigned short*>(smem + M2_SM_VQ);
+    unsigned short* vqb = reinterpret_cast<unsigned short*>(smem + M2_SM_VQB);
     if (tid < 32) freq_s[tid] = powf(P.rope_base, -2.0f * (float)tid / 64.0f);
     if (tid < 64) dinv_s[tid] = (1.0f / 256.0f) / (__half2float(P.d_k[tid]) + 1e-8f);
     if (tid >= 64 && tid < 64 + KD_LUT_ENTRIES) lut[tid - 64] = kd_make_lut_entry((uint32_t)(tid - 64));
-    for (int e = tid; e < 2 * 16 * 32; e += M2_THREADS) {
-        const int kind = e >> 9, s = (e >> 5) & 15, lane = e & 31;
+    for (int e = tid; e < 16 * 32; e += M2_THREADS) {
+        const int s = e >> 5, lane = e & 31;
         const int g = lane >> 2, t = lane & 3;
-        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // dims 64t+4s + {0, 2, 1, 3}
+        float rc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, r1[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // dims 64t+4s + {0, 2, 1, 3}
         if ((g >> 2) == (s & 1)) {
             const int c = g & 3, patch = 16 * t + s;
             const int kk[4] = {0, 2, 1, 3};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                float r = __half2float(P.k_rotor[patch * 16 + c * 4 + kk[i]]);
-                if (kind == 0) r *= __half2float(P.cents_k[2 * D + 64 * t + 4 * s + kk[i]]);
-                v[i] = r;
+                r1[i] = __half2float(P.k_rotor[patch * 16 + c * 4 + kk[i]]);
+                rc[i] = r1[i] * __half2float(P.cents_k[2 * D + 64 * t + 4 * s + kk[i]]);
             }
         }
-        brot[e] = make_uint2(m2_pack(v[0], v[1]), m2_pack(v[2], v[3]));
+        uint2 hi, lo;
+        m2_pack_hilo(rc[0], rc[1], hi.x, lo.x);
+        m2_pack_hilo(rc[2], rc[3], hi.y, lo.y);
+        brot[e] = hi;                                                     // rotor * centroid (ternary operand)
+        brot[512 + e] = make_uint2(m2_pack(r1[0], r1[1]), m2_pack(r1[2], r1[3]));  // rotor (residual operand), exact
+        brot[1024 + e] = lo;                                              // what fp16 lost of rotor * centroid
     }
     const unsigned int* src = reinterpret_cast<const unsigned int*>(P.vq);
     for (int w = tid; w < NP * 256 * 3 / 2; w += M2_THREADS) {
@@ -163,7 +184,9 @@ __device__ __forceinline__ void m2_setup_tables(unsigned char* smem, const Compr
             const int hidx = 2 * w + b;
             const int entry = hidx / 3, k = hidx - entry * 3;
             const int patch = entry >> 8, code = entry & 255;
-            vq_s[(code * 64 + patch) * 4 + k] = (unsigned short)(two >> (16 * b));
+            const unsigned short val = (unsigned short)(two >> (16 * b));
+            if (k < 2) vqa[(code * M2_VQA_STRIDE + patch) * 2 + k] = val;
+            else vqb[code * (M2_VQB_STRIDE / 2) + patch] = val;
         }
     }
 }
@@ -177,7 +200,9 @@ struct M2Query {
 
 // q: (H_q, ..) with `q_head_stride` halfs between heads.  scratch: this warp's NREP*D floats.
 __device__ __forceinline__ void m2_build_query(M2Query& Q, const __half* __restrict__ q, size_t q_head_stride,
-                                               const CompressedKV& P, int kvh, int lane, float* scratch) {
+                                               const CompressedKV& P, int kvh, int lane, float* scratch,
+                                               uint2* qlo /* this kv-head's [16][32] low-order q1 fragments; the
+                                                             q2 ones sit HKV*16*32 entries further */) {
     const int g = lane >> 2, t = lane & 3;
     // q~ in the lane-owns-8-dims layout: q~ = R^T H256 (q * dinv * [dim >= 64])
     float dv[8], rr[2][16];
@@ -221,10 +246,14 @@ __device__ __forceinline__ void m2_build_query(M2Query& Q, const __half* __restr
             v[0] = qq.x; v[1] = qq.z; v[2] = qq.y; v[3] = qq.w;  // dims d0 + {0, 2, 1, 3}
             c[0] = __half2float(hc[0]); c[1] = __half2float(hc[2]); c[2] = __half2float(hc[1]); c[3] = __half2float(hc[3]);
         }
-        Q.q1[s][0] = m2_pack(v[0] * c[0], v[1] * c[1]);
-        Q.q1[s][1] = m2_pack(v[2] * c[2], v[3] * c[3]);
-        Q.q2[s][0] = m2_pack(v[0], v[1]);
-        Q.q2[s][1] = m2_pack(v[2], v[3]);
+        uint2 lo;
+        m2_pack_hilo(v[0] * c[0], v[1] * c[1], Q.q1[s][0], lo.x);
+        m2_pack_hilo(v[2] * c[2], v[3] * c[3], Q.q1[s][1], lo.y);
+        qlo[s * 32 + lane] = lo;  // both warps of a kv-head write the same values
+        uint2 lo2;
+        m2_pack_hilo(v[0], v[1], Q.q2[s][0], lo2.x);
+        m2_pack_hilo(v[2], v[3], Q.q2[s][1], lo2.y);
+        qlo[HKV * 16 * 32 + s * 32 + lane] = lo2;
     }
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
@@ -261,41 +290,48 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
     const int g = lane >> 2, t = lane & 3;
     const KdLutEntry* lut = reinterpret_cast<const KdLutEntry*>(smem + M2_SM_LUT);
     const uint2* brot = reinterpret_cast<const uint2*>(smem + M2_SM_BROT);
+    const uint2* qlo = reinterpret_cast<const uint2*>(smem + M2_SM_QLO) + kvh * 16 * 32;
     const float* dinv_s = reinterpret_cast<const float*>(smem + M2_SM_DINV);
-    const unsigned char* vq_s = smem + M2_SM_VQ;
+    const unsigned char* vqa = smem + M2_SM_VQ;
+    const unsigned char* vqb = smem + M2_SM_VQB;
 
     // ================================ K side: scores ==========================================
     const uint32_t* kp[2];
     uint4 mw[2];
-    KdStream ks[2];
-    float sp[2];
-    uint32_t ratio2[2];
+    KdSigns sg[2];
+    uint32_t wbase[2];
+    float sp[2], sp2[2];
+    uint32_t ratio_hi[2], ratio_lo[2];  // rs/mult as two 7-bit pieces: code (4 bits) * piece is exact in fp16
 #pragma unroll
     for (int x = 0; x < 2; ++x) {
         const int row = (r0 + g + 8 * x) * HKV + kvh;
         kp[x] = reinterpret_cast<const uint32_t*>(S + M2_OFF_KPAY + row * K_PAY);
         mw[x] = *reinterpret_cast<const uint4*>(S + M2_OFF_MASK + row * 64 + 16 * t);
         // outliers of this thread's quarter, then the ordinal of its first one (scan over the quad)
-        int cnt = __popc(kd_word(mw[x].x).X3) + __popc(kd_word(mw[x].y).X3) + __popc(kd_word(mw[x].z).X3) +
-                  __popc(kd_word(mw[x].w).X3);
+        int cnt = (int)(kd_count(kd_word(mw[x].x)) + kd_count(kd_word(mw[x].y)) + kd_count(kd_word(mw[x].z)) +
+                        kd_count(kd_word(mw[x].w)));
         int incl = cnt;
         int up = __shfl_up_sync(0xFFFFFFFFu, incl, 1);
         if (t >= 1) incl += up;
         up = __shfl_up_sync(0xFFFFFFFFu, incl, 2);
         if (t >= 2) incl += up;
-        const uint32_t base = (uint32_t)(incl - cnt);
-        ks[x].pos4 = 4u * base;
-        kd_sign_window(kp[x], base, ks[x].sg_lo, ks[x].sg_hi);
+        wbase[x] = (uint32_t)(incl - cnt);
+        sg[x] = kd_signs(kp[x]);
         float mult = (float)kp[x][0] / 1000.0f;
         if (mult < 0.1f || mult > 10.0f || isnan(mult)) mult = 1.0f;
         const float rs = hbits2f(reinterpret_cast<const uint16_t*>(S + M2_OFF_KRN)[row]);
         const float kn = hbits2f(reinterpret_cast<const uint16_t*>(S + M2_OFF_KN)[row]);
         sp[x] = P.alpha_k * kn * mult * scale;
+        sp2[x] = P.alpha_k * kn * rs * scale;
         const float ratio = rs / mult;
-        ratio2[x] = m2_pack(ratio, ratio);
+        const uint32_t rh = m2_pack(ratio, ratio) & 0xFFF0FFF0u;
+        const float rhf = __half2float(__ushort_as_half((unsigned short)(rh & 0xFFFFu)));
+        ratio_hi[x] = rh;
+        ratio_lo[x] = m2_pack(ratio - rhf, ratio - rhf) & 0xFFF0FFF0u;
     }
     const uint32_t neg1024 = 0xE400E400u;  // fp16x2 (-1024, -1024)
-    float cs[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // pass-part scores: rows g (0,1) and g+8 (2,3), heads 2t, 2t+1
+    float cs[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // pass-part scores, ternary part: rows g (0,1), g+8 (2,3); heads 2t, 2t+1
+    float cs2[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // pass-part scores, residual part (exact integer operand)
     float cu[8][4];                          // rotor block sums u[token, 8j + n]
 #pragma unroll
     for (int j = 0; j < 8; ++j) cu[j][0] = cu[j][1] = cu[j][2] = cu[j][3] = 0.0f;
@@ -307,19 +343,29 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const int s = wi * 4 + q;
-            const KdStep a = kd_step(kwa, q, ks[0], kp[0], lut);
-            const KdStep b = kd_step(kwb, q, ks[1], kp[1], lut);
+            const KdStep a = kd_step(kwa, q, wbase[0] + kd_prefix(kwa, q), kp[0], sg[0], lut);
+            const KdStep b = kd_step(kwb, q, wbase[1] + kd_prefix(kwb, q), kp[1], sg[1], lut);
             const uint32_t a1[4] = {a.t0, b.t0, a.t1, b.t1};
-            const uint32_t a2[4] = {m2_hmul2(m2_hfma2(a.t0, neg1024, a.h0), ratio2[0]),
-                                    m2_hmul2(m2_hfma2(b.t0, neg1024, b.h0), ratio2[1]),
-                                    m2_hmul2(m2_hfma2(a.t1, neg1024, a.h1), ratio2[0]),
-                                    m2_hmul2(m2_hfma2(b.t1, neg1024, b.h1), ratio2[1])};
-            const uint2 b1 = brot[s * 32 + lane], b2 = brot[512 + s * 32 + lane];
+            const uint32_t ax[4] = {m2_hfma2(a.t0, neg1024, a.h0), m2_hfma2(b.t0, neg1024, b.h0),
+                                    m2_hfma2(a.t1, neg1024, a.h1), m2_hfma2(b.t1, neg1024, b.h1)};  // sign*code, exact
+            // * rs/mult in two exact pieces: only the rotary GEMM uses them
+            const uint32_t a2[4] = {m2_hmul2(ax[0], ratio_hi[0]), m2_hmul2(ax[1], ratio_hi[1]),
+                                    m2_hmul2(ax[2], ratio_hi[0]), m2_hmul2(ax[3], ratio_hi[1])};
+            const uint32_t a3[4] = {m2_hmul2(ax[0], ratio_lo[0]), m2_hmul2(ax[1], ratio_lo[1]),
+                                    m2_hmul2(ax[2], ratio_lo[0]), m2_hmul2(ax[3], ratio_lo[1])};
+            const uint2 b1 = brot[s * 32 + lane], b2 = brot[512 + s * 32 + lane], b1l = brot[1024 + s * 32 + lane];
+            const uint2 ql = qlo[s * 32 + lane], ql2 = qlo[HKV * 16 * 32 + s * 32 + lane];
             m2_mma(cs, a1, Q.q1[s][0], Q.q1[s][1]);
-            m2_mma(cs, a2, Q.q2[s][0], Q.q2[s][1]);
+            m2_mma(cs, a1, ql.x, ql.y);  // low-order halves of the query operands: the code operands are exact
+            m2_mma(cs2, ax, Q.q2[s][0], Q.q2[s][1]);
+            m2_mma(cs2, ax, ql2.x, ql2.y);
             m2_mma(cu[s >> 1], a1, b1.x, b1.y);
+            m2_mma(cu[s >> 1], a1, b1l.x, b1l.y);
             m2_mma(cu[s >> 1], a2, b2.x, b2.y);
+            m2_mma(cu[s >> 1], a3, b2.x, b2.y);
         }
+        wbase[0] += kd_count(kwa);
+        wbase[1] += kd_count(kwb);
     }
     // ---- rotary part: H64 over idx = 8j + 2t + e, /d, rotation, dot with the raw query ----------
     float cr[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -375,10 +421,13 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
         }
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
-            const uint32_t a[4] = {m2_pack(cu[2 * kk][0], cu[2 * kk][1]), m2_pack(cu[2 * kk][2], cu[2 * kk][3]),
-                                   m2_pack(cu[2 * kk + 1][0], cu[2 * kk + 1][1]),
-                                   m2_pack(cu[2 * kk + 1][2], cu[2 * kk + 1][3])};
+            uint32_t a[4], al[4];  // rotated K^ dims as fp16 hi + lo: the raw query operand is exact
+            m2_pack_hilo(cu[2 * kk][0], cu[2 * kk][1], a[0], al[0]);
+            m2_pack_hilo(cu[2 * kk][2], cu[2 * kk][3], a[1], al[1]);
+            m2_pack_hilo(cu[2 * kk + 1][0], cu[2 * kk + 1][1], a[2], al[2]);
+            m2_pack_hilo(cu[2 * kk + 1][2], cu[2 * kk + 1][3], a[3], al[3]);
             m2_mma(cr, a, Q.qr[kk][0], Q.qr[kk][1]);
+            m2_mma(cr, al, Q.qr[kk][0], Q.qr[kk][1]);
         }
     }
     // ================================ softmax over the block ====================================
@@ -388,7 +437,8 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
     for (int x = 0; x < 2; ++x) {
         valid[x] = (g + 8 * x) >= valid_lo && (g + 8 * x) < valid_hi;
 #pragma unroll
-        for (int e = 0; e < 2; ++e) sc[x][e] = valid[x] ? sp[x] * (cs[2 * x + e] + cr[2 * x + e]) : -1e30f;
+        for (int e = 0; e < 2; ++e)
+            sc[x][e] = valid[x] ? fmaf(sp[x], cs[2 * x + e] + cr[2 * x + e], sp2[x] * cs2[2 * x + e]) : -1e30f;
     }
     float corr[2];
 #pragma unroll
@@ -414,7 +464,7 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
         }
     }
     // three scaled variants of P, transposed into B fragments (tokens = k, heads = n)
-    uint32_t pb[3][2];
+    uint32_t pb[3][2], pl_[3][2];  // fp16 hi and the fp16 of what hi lost
     {
         float s1[2], s2[2], s3[2];
 #pragma unroll
@@ -429,9 +479,16 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
         }
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
-            pb[0][x] = m2_movmatrix_t(m2_pack(pw[x][0] * s1[x], pw[x][1] * s1[x]));
-            pb[1][x] = m2_movmatrix_t(m2_pack(pw[x][0] * s2[x], pw[x][1] * s2[x]));
-            pb[2][x] = m2_movmatrix_t(m2_pack(pw[x][0] * s3[x], pw[x][1] * s3[x]));
+            uint32_t hi, lo;
+            m2_pack_hilo(pw[x][0] * s1[x], pw[x][1] * s1[x], hi, lo);
+            pb[0][x] = m2_movmatrix_t(hi);
+            pl_[0][x] = m2_movmatrix_t(lo);
+            m2_pack_hilo(pw[x][0] * s2[x], pw[x][1] * s2[x], hi, lo);
+            pb[1][x] = m2_movmatrix_t(hi);
+            pl_[1][x] = m2_movmatrix_t(lo);
+            m2_pack_hilo(pw[x][0] * s3[x], pw[x][1] * s3[x], hi, lo);
+            pb[2][x] = m2_movmatrix_t(hi);
+            pl_[2][x] = m2_movmatrix_t(lo);
         }
     }
     // ================================ V side: O^T += V^T P^T ====================================
@@ -469,9 +526,8 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
                 f &= 0xFFFu;
                 f3[u][i] = f;
                 const uint32_t code = (f & 0x7Fu) | (((hb[i] >> pl) & 1u) << 7);
-                const uint2 e = *reinterpret_cast<const uint2*>(vq_s + (code * 64 + 8 * g + pl) * 8);
-                ex[u][i] = e.x;
-                ey[u][i] = e.y;
+                ex[u][i] = *reinterpret_cast<const uint32_t*>(vqa + (code * M2_VQA_STRIDE + 8 * g + pl) * 4);
+                ey[u][i] = *reinterpret_cast<const unsigned short*>(vqb + code * M2_VQB_STRIDE + (8 * g + pl) * 2);
             }
         }
         // rows: idx = 2j + r -> (patch idx/3, dim idx%3); the pair's six (patch, dim) rows in order
@@ -489,6 +545,7 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
         for (int jj = 0; jj < 3; ++jj) {
             const uint32_t a[4] = {lo[2 * jj], lo[2 * jj + 1], hi[2 * jj], hi[2 * jj + 1]};
             m2_mma(st.o[3 * pp + jj], a, pb[0][0], pb[0][1]);
+            m2_mma(st.o[3 * pp + jj], a, pl_[0][0], pl_[0][1]);
         }
         // dim 3 of the two patches (rows 0, 1 of tile 12 + pp): centroid choice and (dump - 8)
         uint32_t ca[4], da[4];  // a0..a3 of the two extra MMAs
@@ -512,17 +569,20 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
             da[2 + u] = *reinterpret_cast<const uint32_t*>(&d_hi);
         }
         m2_mma(st.o[12 + pp], ca, pb[1][0], pb[1][1]);
+        m2_mma(st.o[12 + pp], ca, pl_[1][0], pl_[1][1]);
         m2_mma(st.o[12 + pp], da, pb[2][0], pb[2][1]);
+        m2_mma(st.o[12 + pp], da, pl_[2][0], pl_[2][1]);
     }
 }
 
 // Attention of all 24 query heads over compressed tokens [my_lo, my_hi) of P; the CTA's 8 warps
 // are (kv-head = warp & 3) x (16-token half of each 32-token tile = warp >> 2).  On return,
-// warps 0..3 have written the merged, inverse-transformed partial of their kv-head's six heads
-// to ob[0..5] (each a (258,) record).  Tables must be set up; all 256 threads call it.
+// warps 0..3 hold in `ws` the merged state of their kv-head's six heads in the first generation's
+// layout (lane = 8 dims, rotated V domain), ready for merge_from / v_epilogue_store.  Tables must
+// be set up; all 256 threads call it.
 __device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const __half* __restrict__ q,
                                                     size_t q_head_stride, const CompressedKV& P, int my_lo, int my_hi,
-                                                    float scale, unsigned& tiles_done, float* const (&ob)[NREP]) {
+                                                    float scale, unsigned& tiles_done, WarpState& ws) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kvh = warp & 3, sub = warp >> 2, g = lane >> 2, t = lane & 3;
     float2* rope_tab = reinterpret_cast<float2*>(smem + M2_SM_ROPE);
@@ -530,7 +590,8 @@ __device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const _
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + M2_SM_BARS);
 
     M2Query Q;
-    m2_build_query(Q, q, q_head_stride, P, kvh, lane, reinterpret_cast<float*>(smem + M2_SM_STAGES) + warp * NREP * D);
+    m2_build_query(Q, q, q_head_stride, P, kvh, lane, reinterpret_cast<float*>(smem + M2_SM_STAGES) + warp * NREP * D,
+                   reinterpret_cast<uint2*>(smem + M2_SM_QLO) + kvh * 16 * 32);
     float c3[8][2];
 #pragma unroll
     for (int pl = 0; pl < 8; ++pl) {
@@ -596,12 +657,10 @@ __device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const _
         }
     }
     __syncthreads();
+    ws.init();
     if (warp < 4) {
-        WarpState ws;
-        ws.init();
         merge_from(ws, reinterpret_cast<const float*>(smem + M2_SM_STAGES) + warp * MERGE_FLOATS, lane);
         merge_from(ws, reinterpret_cast<const float*>(smem + M2_SM_STAGES) + (warp + 4) * MERGE_FLOATS, lane);
-        v_epilogue_store(ws, P, lane, ob);
     }
 }
 
@@ -648,7 +707,9 @@ khq_decode_batched_mma_kernel(const KhqSeqDesc* __restrict__ descs, const KhqTab
                 cur_table = d.table_id;
                 __syncthreads();
             }
-            m2_compressed_range(smem, d.q_gate, (size_t)2 * D, P, w.lo, w.hi, scale, tiles_done, ob);
+            WarpState ws;
+            m2_compressed_range(smem, d.q_gate, (size_t)2 * D, P, w.lo, w.hi, scale, tiles_done, ws);
+            if (warp < 4) v_epilogue_store(ws, P, lane, ob);
         } else {
             WarpState ws;
             ws.init();
@@ -661,6 +722,61 @@ khq_decode_batched_mma_kernel(const KhqSeqDesc* __restrict__ descs, const KhqTab
                 raw_store(ws, lane, ob);
             }
         }
+    }
+}
+
+// Drop-in (single sequence-layer) variant: grid = num_splits * cluster_size CTAs; the CTAs of a
+// cluster share one of the caller's splits and merge through distributed shared memory.
+__global__ void __launch_bounds__(M2_THREADS, 1)
+khq_attn_compressed_mma_kernel(const __half* __restrict__ q, CompressedKV P, float* __restrict__ out_attn,
+                               float* __restrict__ out_partial, int num_splits, int L_q, int l_idx, int s_limit,
+                               float scale) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int csize = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
+    const int split_id = blockIdx.x / csize;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + M2_SM_BARS);
+    int s_lo = 0, s_hi = s_limit;
+    if (num_splits > 1) {
+        const int per = (s_limit + num_splits - 1) / num_splits;
+        s_lo = min(split_id * per, s_limit);
+        s_hi = min(s_lo + per, s_limit);
+    }
+    const int len = s_hi - s_lo;
+    const int chunk = (((len + csize - 1) / csize) + 1) & ~1;
+    const int my_lo = min(s_lo + crank * chunk, s_hi);
+    const int my_hi = min(my_lo + chunk, s_hi);
+    if (tid == 0) {
+        for (int s = 0; s < M2_NSTAGE; ++s) mbar_init(&bars[s], 1);
+        fence_barrier_init();
+    }
+    m2_setup_tables(smem, P, tid);
+    __syncthreads();
+    unsigned tiles_done = 0;
+    WarpState ws;
+    m2_compressed_range(smem, q + (size_t)l_idx * 2 * D, (size_t)L_q * 2 * D, P, my_lo, my_hi, scale, tiles_done, ws);
+    // cluster merge: records exported over the (no longer needed) codebook area
+    float* exp_rec = reinterpret_cast<float*>(smem + M2_SM_VQ) + (warp & 3) * MERGE_FLOATS;
+    if (csize > 1) {
+        __syncthreads();  // every warp is done with the codebook
+        if (warp < 4) store_record(ws, exp_rec, lane);
+        cluster.sync();
+        if (crank == 0 && warp < 4) {
+#pragma unroll 1
+            for (int r = 1; r < csize; ++r) merge_from(ws, cluster.map_shared_rank(exp_rec, r), lane);
+        }
+        cluster.sync();
+    }
+    if (crank == 0 && warp < 4) {
+        float* ob[NREP];
+#pragma unroll
+        for (int h = 0; h < NREP; ++h) {
+            const int total_id = (warp * NREP + h) * L_q + l_idx;
+            ob[h] = (num_splits > 1) ? out_partial + ((size_t)total_id * num_splits + split_id) * PART
+                                     : out_attn + (size_t)total_id * PART;
+        }
+        v_epilogue_store(ws, P, lane, ob);
     }
 }
 

@@ -90,30 +90,54 @@ KHQ_HD KdWord kd_word(uint32_t w) {
     return r;
 }
 
-// Running position in one row's outlier streams (per thread: its own quarter of the row).
-struct KdStream {
-    uint32_t pos4;          // 4 * ordinal of the next outlier
-    uint32_t sg_lo, sg_hi;  // sign bits, next outlier's sign at bit 0
+// The sign-bit stream of a row: bits 0..49 = payload bytes 29..35.
+struct KdSigns {
+    uint32_t lo, hi;
 };
+KHQ_HD KdSigns kd_signs(const uint32_t* kp) {
+    KdSigns r;
+    r.lo = kd_funnel_r(kp[7], kp[8], 8);
+    r.hi = kd_funnel_r(kp[8], kp[9], 8) & 0x00FFFFFFu;
+    return r;
+}
+
+// Number of outliers of a word before its step q (q = 0..3).
+KHQ_HD uint32_t kd_prefix(const KdWord& w, int q) {
+#if defined(__CUDA_ARCH__)
+    return (uint32_t)__popc(w.X3 & ((1u << (8 * q)) - 1u));
+#else
+    return (uint32_t)__builtin_popcount(w.X3 & ((1u << (8 * q)) - 1u));
+#endif
+}
+KHQ_HD uint32_t kd_count(const KdWord& w) {
+#if defined(__CUDA_ARCH__)
+    return (uint32_t)__popc(w.X3);
+#else
+    return (uint32_t)__builtin_popcount(w.X3);
+#endif
+}
 
 struct KdStep {
     uint32_t t0, t1;  // fp16x2 ternary values: dims (4q, 4q+2), (4q+1, 4q+3)
     uint32_t h0, h1;  // fp16x2 of sign-matched (1024 + code); residual = t * -1024 + h
 };
 
-// Decode step q (0..3) of a mask word.  `kp` = the row's 10 payload words, `lut` = scatter table.
-KHQ_HD KdStep kd_step(const KdWord& w, int q, KdStream& st, const uint32_t* kp, const KdLutEntry* lut) {
+// Decode step q (0..3) of a mask word.  `pos` = ordinal (in the row) of the step's first outlier,
+// `kp` = the row's 10 payload words, `sg` = its sign stream, `lut` = the scatter table.  Nothing
+// is carried from one step to the next, so the steps of a row are independent instruction streams.
+KHQ_HD KdStep kd_step(const KdWord& w, int q, uint32_t pos, const uint32_t* kp, const KdSigns& sg,
+                      const KdLutEntry* lut) {
     const uint32_t f = (w.X3 >> (8 * q)) & 0xFFu;
     const KdLutEntry e = lut[f];
     // next four residual nibbles -> bytes [n0, n1, n2, n3]
-    const uint32_t p4 = st.pos4 < 200u ? st.pos4 : 200u;  // never read past the 50-entry stream
-    const uint32_t bit = 32u + p4;
+    const uint32_t p = pos < 50u ? pos : 50u;  // never read past the 50-entry stream
+    const uint32_t bit = 32u + 4u * p;
     const uint32_t cw = kd_funnel_r(kp[bit >> 5], kp[(bit >> 5) + 1], bit & 31u);
     const uint32_t cb = kd_prmt(cw & 0x0F0Fu, (cw >> 4) & 0x0F0Fu, 0x5140u);
     // next four sign bits -> 0x80 in bytes 0..3
-    uint32_t sb = (((st.sg_lo & 0xFu) * 0x10204080u) & 0x80808080u) | cb;
-    if (st.pos4 > 184u) {  // entries with ordinal >= 50 do not exist: code 0, negative sign
-        const uint32_t pos = st.pos4 >> 2;
+    const uint32_t s4 = kd_funnel_r(p < 32u ? sg.lo : sg.hi, p < 32u ? sg.hi : 0u, p & 31u);
+    uint32_t sb = (((s4 & 0xFu) * 0x10204080u) & 0x80808080u) | cb;
+    if (pos > 46u) {  // entries with ordinal >= 50 do not exist: code 0, negative sign
         const uint32_t nv = pos >= 50u ? 0u : (50u - pos);
         if (nv < 4u) sb &= (1u << (8u * nv)) - 1u;
     }
@@ -129,27 +153,7 @@ KHQ_HD KdStep kd_step(const KdWord& w, int q, KdStream& st, const uint32_t* kp, 
     r.t1 = kd_prmt(H, 0u, 0x3424u);
     r.h0 = kd_prmt(H2, pdc, 0x1504u);
     r.h1 = kd_prmt(H2, pdc, 0x3726u);
-    // advance the streams by the number of outliers of this step
-    const uint32_t n = e.x >> 24;
-    st.pos4 += (e.x >> 16) & 0xFFu;
-    st.sg_lo = kd_funnel_r(st.sg_lo, st.sg_hi, n);
-    st.sg_hi >>= n;
     return r;
-}
-
-// Sign-bit stream of a row (bits 0..49 = payload bytes 29..35) starting at outlier `ord`.
-KHQ_HD void kd_sign_window(const uint32_t* kp, uint32_t ord, uint32_t& lo, uint32_t& hi) {
-    const uint32_t s_lo = kd_funnel_r(kp[7], kp[8], 8), s_hi = kd_funnel_r(kp[8], kp[9], 8) & 0x00FFFFFFu;
-    if (ord >= 64u) {
-        lo = 0;
-        hi = 0;
-    } else if (ord >= 32u) {
-        lo = s_hi >> (ord - 32u);
-        hi = 0;
-    } else {
-        lo = kd_funnel_r(s_lo, s_hi, ord);
-        hi = ord ? (s_hi >> ord) : s_hi;
-    }
 }
 
 }  // namespace khq

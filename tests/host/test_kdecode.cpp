@@ -50,13 +50,12 @@ int main() {
         // register-level decode, one "thread" per 64-dim quarter
         uint32_t base = 0;
         for (int t = 0; t < 4; ++t) {
-            KdStream st;
-            st.pos4 = 4 * base;
-            kd_sign_window(kp, base, st.sg_lo, st.sg_hi);
+            const KdSigns sg = kd_signs(kp);
+            uint32_t wbase = base;
             for (int wi = 0; wi < 4; ++wi) {
                 const KdWord w = kd_word(mask[4 * t + wi]);
                 for (int q = 0; q < 4; ++q) {
-                    const KdStep r = kd_step(w, q, st, kp, lut);
+                    const KdStep r = kd_step(w, q, wbase + kd_prefix(w, q), kp, sg, lut);
                     const int d0 = 64 * t + 16 * wi + 4 * q;
                     const int dims[4] = {d0, d0 + 2, d0 + 1, d0 + 3};
                     const uint16_t th[4] = {(uint16_t)r.t0, (uint16_t)(r.t0 >> 16), (uint16_t)r.t1, (uint16_t)(r.t1 >> 16)};
@@ -72,9 +71,10 @@ int main() {
                         ++checked;
                     }
                 }
+                wbase += kd_count(w);
             }
             for (int i = 64 * t; i < 64 * t + 64; ++i) base += sym[i] == 3;
-            if (st.pos4 != 4 * base) { std::printf("stream position drifted\n"); return 1; }
+            if (wbase != base) { std::printf("stream position drifted\n"); return 1; }
         }
     }
     std::printf("ok %ld dims\n", checked);

@@ -146,7 +146,7 @@ def check_partial(got, ref, what):
 
 @pytest.mark.parametrize("variant", list(cases.VARIANTS))
 @pytest.mark.parametrize("c_len,splits", [(1, 1), (7, 1), (8, 8), (127, 4), (128, 16), (129, 32), (384, 1),
-                                          (384, 8), (50, 32), (1000, 3)])
+                                          (384, 8), (50, 32), (1000, 3), (4096, 2), (2501, 1)])  # the last two take the tensor-core path
 def test_attn_compressed_vs_oracle(cuda_ops, oracle, variant, c_len, splits):
     case = cases.make_case(900 + c_len, c_len + 1, variant)
     kv = cases.compress_with(oracle.compress, case, c_len)
