@@ -24,6 +24,10 @@
 #pragma once
 #include "khq_kdecode.cuh"
 
+#ifndef KHQ_ABLATE
+#define KHQ_ABLATE 0  // timing experiments only: 1 skip V side, 2 skip rotary part, 4 fake K decode, 8 skip rope table
+#endif
+
 namespace khq {
 
 constexpr int M2_THREADS = 256;
@@ -50,8 +54,8 @@ constexpr int M2_VQB_STRIDE = 130;                                   // bytes pe
 constexpr int M2_SM_VQ = M2_SM_STAGES + M2_NSTAGE * M2_STAGE_BYTES;  // (d0, d1): 256 x 65 x 4 B
 constexpr int M2_SM_VQB = M2_SM_VQ + 256 * M2_VQA_STRIDE * 4;        // d2: 256 x 130 B
 constexpr int M2_SM_ROPE = M2_SM_VQB + 256 * M2_VQB_STRIDE;          // 2 x 32 tokens x 32 float2
-constexpr int M2_SM_BROT = M2_SM_ROPE + 2 * M2_TT * 32 * 8;          // 3 kinds x 16 steps x 32 lanes x 8 B
-constexpr int M2_SM_LUT = M2_SM_BROT + 3 * 16 * 32 * 8;              // scatter table
+constexpr int M2_SM_BROT = M2_SM_ROPE + 2 * M2_TT * 32 * 8;          // 4 kinds x 16 steps x 32 lanes x 8 B
+constexpr int M2_SM_LUT = M2_SM_BROT + 4 * 16 * 32 * 8;              // scatter table
 constexpr int M2_SM_FREQ = M2_SM_LUT + 448;
 constexpr int M2_SM_DINV = M2_SM_FREQ + 128;                         // 64 floats
 constexpr int M2_SM_BARS = M2_SM_DINV + 256;
@@ -65,6 +69,12 @@ static_assert(8 * NREP * D * 4 <= M2_NSTAGE * M2_STAGE_BYTES, "prologue scratch 
 static_assert(M2_STAGE_BYTES % 16 == 0 && M2_OFF_KPAY % 16 == 0 && M2_OFF_VPAY % 16 == 0 && M2_OFF_KN % 16 == 0 &&
                   M2_OFF_VSM % 16 == 0, "bulk copy alignment");
 
+// low-order ("what fp16 lost") products; compiled out only in timing experiments
+#if KHQ_ABLATE & 16
+#define m2_mma_lo(c, a, b0, b1) ((void)0)
+#else
+#define m2_mma_lo(c, a, b0, b1) m2_mma(c, a, b0, b1)
+#endif
 __device__ __forceinline__ void m2_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -133,6 +143,9 @@ __device__ __forceinline__ void m2_stage_tile(const CompressedKV& P, unsigned ch
 }
 
 __device__ __forceinline__ void m2_fill_rope(float2* tab, const float* freq, int pos0, int tid) {
+#if KHQ_ABLATE & 8
+    return;
+#endif
     for (int e = tid; e < M2_TT * 32; e += M2_THREADS) {
         const int t = e >> 5, m = e & 31;
         double th = (double)(pos0 + t) * (double)freq[m];
@@ -156,25 +169,37 @@ __device__ __forceinline__ void m2_setup_tables(unsigned char* smem, const Compr
     if (tid < 32) freq_s[tid] = powf(P.rope_base, -2.0f * (float)tid / 64.0f);
     if (tid < 64) dinv_s[tid] = (1.0f / 256.0f) / (__half2float(P.d_k[tid]) + 1e-8f);
     if (tid >= 64 && tid < 64 + KD_LUT_ENTRIES) lut[tid - 64] = kd_make_lut_entry((uint32_t)(tid - 64));
+    // Rotor B fragments with the three low index bits of the 64-point Hadamard transform folded
+    // in: u[8j + n] is produced by step s = 2j + (n >> 2) as rotor output c = n & 3, and
+    // H64 = H8 (bits 0..2, inside a tile) x H8 (bits 3..5, across tiles), so column n' of the
+    // folded operand is sum_n H8[n][n'] * (column n of the plain one).
     for (int e = tid; e < 16 * 32; e += M2_THREADS) {
         const int s = e >> 5, lane = e & 31;
         const int g = lane >> 2, t = lane & 3;
-        float rc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, r1[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // dims 64t+4s + {0, 2, 1, 3}
-        if ((g >> 2) == (s & 1)) {
-            const int c = g & 3, patch = 16 * t + s;
-            const int kk[4] = {0, 2, 1, 3};
+        const int patch = 16 * t + s;
+        const int kk[4] = {0, 2, 1, 3};  // dims 64t+4s + {0, 2, 1, 3}
+        float rc[4], r1[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                r1[i] = __half2float(P.k_rotor[patch * 16 + c * 4 + kk[i]]);
-                rc[i] = r1[i] * __half2float(P.cents_k[2 * D + 64 * t + 4 * s + kk[i]]);
+        for (int i = 0; i < 4; ++i) {
+            float acc = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int n = 4 * (s & 1) + c;
+                const float sgn = (__popc(n & g) & 1) ? -1.0f : 1.0f;
+                acc += sgn * __half2float(P.k_rotor[patch * 16 + c * 4 + kk[i]]);
             }
+            r1[i] = acc;
+            rc[i] = acc * __half2float(P.cents_k[2 * D + 64 * t + 4 * s + kk[i]]);
         }
         uint2 hi, lo;
         m2_pack_hilo(rc[0], rc[1], hi.x, lo.x);
         m2_pack_hilo(rc[2], rc[3], hi.y, lo.y);
-        brot[e] = hi;                                                     // rotor * centroid (ternary operand)
-        brot[512 + e] = make_uint2(m2_pack(r1[0], r1[1]), m2_pack(r1[2], r1[3]));  // rotor (residual operand), exact
-        brot[1024 + e] = lo;                                              // what fp16 lost of rotor * centroid
+        brot[e] = hi;          // rotor * centroid (ternary operand), fp16 hi
+        brot[1024 + e] = lo;   //   and what fp16 lost
+        m2_pack_hilo(r1[0], r1[1], hi.x, lo.x);
+        m2_pack_hilo(r1[2], r1[3], hi.y, lo.y);
+        brot[512 + e] = hi;    // rotor (residual operand), fp16 hi
+        brot[1536 + e] = lo;   //   and what fp16 lost
     }
     const unsigned int* src = reinterpret_cast<const unsigned int*>(P.vq);
     for (int w = tid; w < NP * 256 * 3 / 2; w += M2_THREADS) {
@@ -343,8 +368,12 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const int s = wi * 4 + q;
+#if KHQ_ABLATE & 4
+            const KdStep a = {kwa.E, kwa.O, kwa.X3, kwa.E ^ (uint32_t)q}, b = {kwb.E, kwb.O, kwb.X3, kwb.O ^ (uint32_t)q};
+#else
             const KdStep a = kd_step(kwa, q, wbase[0] + kd_prefix(kwa, q), kp[0], sg[0], lut);
             const KdStep b = kd_step(kwb, q, wbase[1] + kd_prefix(kwb, q), kp[1], sg[1], lut);
+#endif
             const uint32_t a1[4] = {a.t0, b.t0, a.t1, b.t1};
             const uint32_t ax[4] = {m2_hfma2(a.t0, neg1024, a.h0), m2_hfma2(b.t0, neg1024, b.h0),
                                     m2_hfma2(a.t1, neg1024, a.h1), m2_hfma2(b.t1, neg1024, b.h1)};  // sign*code, exact
@@ -353,44 +382,29 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
                                     m2_hmul2(ax[2], ratio_hi[0]), m2_hmul2(ax[3], ratio_hi[1])};
             const uint32_t a3[4] = {m2_hmul2(ax[0], ratio_lo[0]), m2_hmul2(ax[1], ratio_lo[1]),
                                     m2_hmul2(ax[2], ratio_lo[0]), m2_hmul2(ax[3], ratio_lo[1])};
-            const uint2 b1 = brot[s * 32 + lane], b2 = brot[512 + s * 32 + lane], b1l = brot[1024 + s * 32 + lane];
+            const uint2 b1 = brot[s * 32 + lane], b2 = brot[512 + s * 32 + lane], b1l = brot[1024 + s * 32 + lane],
+                        b2l = brot[1536 + s * 32 + lane];
             const uint2 ql = qlo[s * 32 + lane], ql2 = qlo[HKV * 16 * 32 + s * 32 + lane];
             m2_mma(cs, a1, Q.q1[s][0], Q.q1[s][1]);
-            m2_mma(cs, a1, ql.x, ql.y);  // low-order halves of the query operands: the code operands are exact
+            m2_mma_lo(cs, a1, ql.x, ql.y);  // low-order halves of the query operands: the code operands are exact
             m2_mma(cs2, ax, Q.q2[s][0], Q.q2[s][1]);
-            m2_mma(cs2, ax, ql2.x, ql2.y);
+            m2_mma_lo(cs2, ax, ql2.x, ql2.y);
             m2_mma(cu[s >> 1], a1, b1.x, b1.y);
-            m2_mma(cu[s >> 1], a1, b1l.x, b1l.y);
+            m2_mma_lo(cu[s >> 1], a1, b1l.x, b1l.y);
             m2_mma(cu[s >> 1], a2, b2.x, b2.y);
-            m2_mma(cu[s >> 1], a3, b2.x, b2.y);
+            m2_mma_lo(cu[s >> 1], a2, b2l.x, b2l.y);
+            m2_mma_lo(cu[s >> 1], a3, b2.x, b2.y);
         }
         wbase[0] += kd_count(kwa);
         wbase[1] += kd_count(kwb);
     }
-    // ---- rotary part: H64 over idx = 8j + 2t + e, /d, rotation, dot with the raw query ----------
+    // ---- rotary part: rest of H64 over idx = 8j + 2t + e, /d, rotation, dot with the raw query ----
     float cr[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#if KHQ_ABLATE & 2
+    cr[0] = cu[0][0] + cu[7][3];
+#else
     {
-        // bit 0 (e)
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-#pragma unroll
-            for (int x = 0; x < 2; ++x) {
-                const float a = cu[j][2 * x], b = cu[j][2 * x + 1];
-                cu[j][2 * x] = a + b;
-                cu[j][2 * x + 1] = a - b;
-            }
-        // bits 1, 2 (t): across the quad
-#pragma unroll
-        for (int m = 1; m <= 2; m <<= 1) {
-            const bool lower = (t & m) == 0;
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float other = __shfl_xor_sync(0xFFFFFFFFu, cu[j][e], m);
-                    cu[j][e] = lower ? (cu[j][e] + other) : (other - cu[j][e]);
-                }
-        }
+        // index bits 0..2 were transformed inside the GEMM (folded into the rotor operand)
         // bits 3, 4, 5 (j)
 #pragma unroll
         for (int m = 1; m <= 4; m <<= 1)
@@ -427,9 +441,10 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
             m2_pack_hilo(cu[2 * kk + 1][0], cu[2 * kk + 1][1], a[2], al[2]);
             m2_pack_hilo(cu[2 * kk + 1][2], cu[2 * kk + 1][3], a[3], al[3]);
             m2_mma(cr, a, Q.qr[kk][0], Q.qr[kk][1]);
-            m2_mma(cr, al, Q.qr[kk][0], Q.qr[kk][1]);
+            m2_mma_lo(cr, al, Q.qr[kk][0], Q.qr[kk][1]);
         }
     }
+#endif
     // ================================ softmax over the block ====================================
     float sc[2][2], pw[2][2];  // [row x: g, g+8][head e: 2t, 2t+1]
     bool valid[2];
@@ -491,6 +506,10 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
             pl_[2][x] = m2_movmatrix_t(lo);
         }
     }
+#if KHQ_ABLATE & 1
+    st.o[0][0] += __uint_as_float(pb[0][0] ^ pb[1][1] ^ pb[2][0] ^ pl_[0][0] ^ pl_[1][0] ^ pl_[2][1]);
+    return;
+#endif
     // ================================ V side: O^T += V^T P^T ====================================
     // thread (g, t): patch group g of tokens 2t, 2t+1, 2t+8, 2t+9
     uint32_t vw[4][3], hb[4];
@@ -545,7 +564,7 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
         for (int jj = 0; jj < 3; ++jj) {
             const uint32_t a[4] = {lo[2 * jj], lo[2 * jj + 1], hi[2 * jj], hi[2 * jj + 1]};
             m2_mma(st.o[3 * pp + jj], a, pb[0][0], pb[0][1]);
-            m2_mma(st.o[3 * pp + jj], a, pl_[0][0], pl_[0][1]);
+            m2_mma_lo(st.o[3 * pp + jj], a, pl_[0][0], pl_[0][1]);
         }
         // dim 3 of the two patches (rows 0, 1 of tile 12 + pp): centroid choice and (dump - 8)
         uint32_t ca[4], da[4];  // a0..a3 of the two extra MMAs
@@ -569,9 +588,9 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
             da[2 + u] = *reinterpret_cast<const uint32_t*>(&d_hi);
         }
         m2_mma(st.o[12 + pp], ca, pb[1][0], pb[1][1]);
-        m2_mma(st.o[12 + pp], ca, pl_[1][0], pl_[1][1]);
+        m2_mma_lo(st.o[12 + pp], ca, pl_[1][0], pl_[1][1]);
         m2_mma(st.o[12 + pp], da, pb[2][0], pb[2][1]);
-        m2_mma(st.o[12 + pp], da, pl_[2][0], pl_[2][1]);
+        m2_mma_lo(st.o[12 + pp], da, pl_[2][0], pl_[2][1]);
     }
 }
 
