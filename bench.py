@@ -51,6 +51,11 @@ def parse():
     ap.add_argument("--layers", type=int, default=N_LAYERS)
     ap.add_argument("--cpu-sample-mult", type=int, default=4, help="CPU sample = mult x host threads sequences")
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--workload", default="batched", choices=["batched", "long"],
+                    help="batched = BASELINE configs[3] (default); long = configs[2], one 131072-token sequence "
+                         "split by context range over the ranks")
+    ap.add_argument("--long-ctx", type=int, default=131072)
+    ap.add_argument("--splits", type=int, default=32)
     ap.add_argument("--kernel", default="auto", choices=["auto", "cuda-core", "mma"],
                     help="generation of the batched decode kernel")
     return ap.parse_args()
@@ -251,6 +256,86 @@ def config_dict(args, world):
 
 
 # ------------------------------------------------------------------------------------------------
+def run_long(args, rank, world, local_rank):
+    """BASELINE configs[2]: one sequence, --long-ctx compressed tokens + 256 raw ring tokens, one
+    layer, the compressed region partitioned by context range over the ranks; per step every rank
+    computes its (24, 258) partial, one NCCL all-gather exchanges them, every rank merges + gates.
+    Value: microseconds per layer-step (max over ranks)."""
+    import torch
+    import torch.distributed as dist
+
+    from bonsai_mojo_1bit_optimization_t4_cuda_b200 import lib as khqlib
+    from bonsai_mojo_1bit_optimization_t4_cuda_b200.context_parallel import ContextParallelDecode, partition_context
+    from bonsai_mojo_1bit_optimization_t4_cuda_b200.ops import CudaOps
+
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), init_method=None if world > 1 or
+                            "MASTER_ADDR" in os.environ else "tcp://127.0.0.1:29533", rank=rank, world_size=world)
+    dev = torch.device("cuda", local_rank)
+    ops = CudaOps()
+    tb = make_tables(1)[0]
+    f = tb.as_f16()
+    tab = {k: torch.from_numpy(v).to(dev) for k, v in dict(cents_k=f["cents_k"], cents_v=f["cents_v"], vq=f["vq"],
+                                                            rotor_k=f["rotor_k"], rotor_v=f["rotor_v"], d_k=f["d_k"],
+                                                            d_v=f["d_v"]).items()}
+    lo, hi = partition_context(args.long_ctx, world)[rank]
+    n = hi - lo
+    rows = max(n, 1) * 4
+    g = torch.Generator(device=dev).manual_seed(20260914 + 2000 + rank)
+    kv = dict(k_mask=torch.zeros(rows * 16, dtype=torch.int32, device=dev),
+              k_payload=torch.zeros(rows * 40, dtype=torch.uint8, device=dev),
+              v_payload=torch.zeros(rows * 104, dtype=torch.uint8, device=dev),
+              v_shared_meta=torch.zeros(rows * 4, dtype=torch.uint8, device=dev),
+              k_norms=torch.zeros(rows, dtype=torch.float16, device=dev), k_r_norms=torch.zeros(rows, dtype=torch.float16, device=dev),
+              v_norms=torch.zeros(rows, dtype=torch.float16, device=dev), v_r_norms=torch.zeros(rows, dtype=torch.float16, device=dev))
+    if n > 0:
+        k = torch.randn(n, 4, 256, generator=g, device=dev).half()
+        v = torch.randn(n, 4, 256, generator=g, device=dev).half()
+        ops.compress(k, tab["d_k"], tab["rotor_k"], tab["cents_k"], tab["cents_k"], kv["k_mask"], kv["k_norms"], kv["k_r_norms"],
+                     kv["k_payload"], kv["v_shared_meta"], n * 4, 256, tb.ts_k, tb.alpha_k, False)
+        ops.compress(v, tab["d_v"], tab["rotor_v"], tab["cents_v"], tab["vq"], kv["k_mask"], kv["v_norms"], kv["v_r_norms"],
+                     kv["v_payload"], kv["v_shared_meta"], n * 4, 256, tb.ts_v, tb.alpha_v, True)
+    ring_k = torch.randn(256 * 1024, generator=g, device=dev).half()
+    ring_v = torch.randn(256 * 1024, generator=g, device=dev).half()
+    owner = world - 1
+    cp = ContextParallelDecode(ops, dist.group.WORLD, kv, tab, lo, hi, tb.alpha_k, tb.alpha_v, ring_k, ring_v, owner=owner,
+                               splits=args.splits, device=dev)
+    qg = torch.randn(24 * 512, generator=g, device=dev).half()
+    win_start, win_len = args.long_ctx % 256, 256
+    for _ in range(max(args.warmup, 3)):
+        cp.step(qg, win_start, win_len)
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        cp.step(qg, win_start, win_len)
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    us = float(t[0]) * 1e3 / args.steps
+    if rank == 0:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        b_alg = 4 * (220 * args.long_ctx + 1024 * win_len)
+        ach = b_alg / (us * 1e-6) / 1e9
+        print(json.dumps({
+            "metric": "KHQ long-context decode attention latency", "value": us, "unit": "us/layer-step", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": us / 1e3, "higher_is_better": False,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "BASELINE configs[2]: one sequence, %d compressed + %d raw tokens, 1 layer, splits %d, "
+                                   "context-partitioned over %d GPU(s), partials merged after one NCCL all-gather"
+                                   % (args.long_ctx, win_len, args.splits, world), "l2": "payload 115 MB per step, "
+                       "larger than L2 only in aggregate at 1 GPU"},
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peak * world, "unit": "GB/s", "frac": ach / (peak * world),
+                         "traffic": None, "algorithmic_bytes_per_step": b_alg},
+            "gpu_launches": 5 * args.steps, "device_status": khqlib.load().khq_b200_device_status()}), flush=True)
+    dist.destroy_process_group()
+
+
 def main():
     args = parse()
     rank = int(os.environ.get("RANK", "0"))
@@ -258,6 +343,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.workload == "long":
+        run_long(args, rank, world, local_rank)
         return
 
     import torch
