@@ -73,6 +73,15 @@ class CudaOps:
             int(T) * H_q * 2 * d, int(T) * H_kv * d, int(T) * H_q * d, current_stream())
         check("launch_khq_gqa_prefill_fp16", rc)
 
+    # -- launch_khq_prestep_fp16: q/k head RMSNorm + K capture + partial RoPE + ring appends --------
+    def prestep(self, q_gate, k, v, q_norm_w, k_norm_w, ring_k_slot, ring_v_slot, ring_u_slot, H_q, H_kv, d,
+                rotary_dim, pos, rope_theta, rms_eps, has_norms):
+        rc = self.lib.launch_khq_prestep_fp16(
+            ptr(q_gate), ptr(k), ptr(v), ptr(q_norm_w), ptr(k_norm_w), ptr(ring_k_slot), ptr(ring_v_slot),
+            ptr(ring_u_slot), int(H_q), int(H_kv), int(d), int(rotary_dim), int(pos), float(rope_theta),
+            float(rms_eps), 1 if has_norms else 0, current_stream())
+        check("launch_khq_prestep_fp16", rc)
+
     # -- ring appends (khq_ring_dual_sm75_gpu / copy_vec_sm75_gpu,
     #    src/kernels/elementwise_sm75.mojo:277-312): device-to-device copies ------------------
     def ring_write(self, dst_row, src):

@@ -180,6 +180,27 @@ class KhqRuntime:
         slot = L.write_pos % KHQ_RING
         self.ops.ring_write(L.t["ring_u"][slot * kv:(slot + 1) * kv], k_dev)
 
+    # ------------------------------------------------------------------ fused pre-step (addition)
+    def khq_prestep(self, layer_idx: int, q_gate_dev, k_dev, v_dev, pos: int, q_norm_w=None, k_norm_w=None,
+                    has_norms: bool = True, rms_eps: float = 1e-6, rope_theta: float = ROPE_BASE,
+                    rotary_dim: int = 64) -> bool:
+        """One launch for what the reference does in five before ``khq_step``
+        (``attention.mojo:329-353`` + ``khq_capture_unroped`` + the ring append of ``khq_step``):
+        q/k head RMSNorm, K un-RoPE'd -> ring_u, partial RoPE of q and k, K RoPE'd and V -> rings.
+        Follow it with ``khq_step(..., rings_written=True)``."""
+        if not self.active or not self.ready or layer_idx < 0 or layer_idx >= KHQ_MAX_LAYERS:
+            return False
+        L = self.layers[layer_idx]
+        if not L.ready:
+            return False
+        kv = L.H_kv * L.D
+        slot = L.write_pos % KHQ_RING
+        T = L.t
+        self.ops.prestep(q_gate_dev, k_dev, v_dev, q_norm_w, k_norm_w, T["ring_k"][slot * kv:(slot + 1) * kv],
+                         T["ring_v"][slot * kv:(slot + 1) * kv], T["ring_u"][slot * kv:(slot + 1) * kv], L.H_q, L.H_kv,
+                         L.D, rotary_dim, pos, rope_theta, rms_eps, has_norms)
+        return True
+
     # ------------------------------------------------------------------ khq_step
     def _tick(self):
         if self.prof:
@@ -194,7 +215,8 @@ class KhqRuntime:
             import time
             self.prof_ns[phase] += time.monotonic_ns() - t0
 
-    def khq_step(self, layer_idx: int, q_gate_dev, k_roped_dev, v_dev, out_dev, scale: float) -> bool:
+    def khq_step(self, layer_idx: int, q_gate_dev, k_roped_dev, v_dev, out_dev, scale: float,
+                 rings_written: bool = False) -> bool:
         """One KHQ attention step of one layer.  False = the KHQ path is not active/ready
         (the caller then raises, as ``attention.mojo:359-365`` does)."""
         if not self.active or not self.ready or layer_idx < 0 or layer_idx >= KHQ_MAX_LAYERS:
@@ -209,8 +231,9 @@ class KhqRuntime:
 
         # 1. ring append: K RoPE'd + V (K un-RoPE'd was written by khq_capture_unroped)
         t0 = self._tick()
-        ops.ring_write(T["ring_k"][slot * kv:(slot + 1) * kv], k_roped_dev)
-        ops.ring_write(T["ring_v"][slot * kv:(slot + 1) * kv], v_dev)
+        if not rings_written:  # khq_prestep already appended this token
+            ops.ring_write(T["ring_k"][slot * kv:(slot + 1) * kv], k_roped_dev)
+            ops.ring_write(T["ring_v"][slot * kv:(slot + 1) * kv], v_dev)
         self._tock(KHQ_P_RING, t0)
         L.write_pos += 1
 

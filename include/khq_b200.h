@@ -173,6 +173,22 @@ int launch_khq_decode_batched_fp16(const void* descs, const void* tables, const 
                                    int n_slots_total, float scale, float rope_base, int ring_cap,
                                    int codebook_in_smem, khq_stream_t stream);
 
+/* ---- Pre-step: everything between the q/k/v projections and khq_step, in one launch --------
+ * Replaces five launches of the reference host: head_rmsnorm_sm75_gpu on q and k
+ * (src/models/qwen3_5/attention.mojo:329-336), khq_capture_unroped (src/khq/runtime.mojo:432-451),
+ * partial_rope_sm75_gpu on q and k (attention.mojo:348-353) and the ring append of khq_step
+ * (runtime.mojo:486).  In place: q_gate (H_q, 2*d) fp16 (query half normed + RoPE'd, gate half
+ * untouched), k (H_kv, d) fp16 (normed + RoPE'd).  The three ring slot pointers address this
+ * token's row of ring_u (K normed, un-RoPE'd), ring_k (K RoPE'd) and ring_v (V); any of them may
+ * be NULL.  q_norm_w / k_norm_w: fp32 (d) or NULL; has_norms == 0 skips the norm as the
+ * reference does.  Half-split RoPE pairs (i, i + rotary_dim/2), freq = exp(log(theta) *
+ * (-2i/rotary_dim)), fp32 angle pos*freq.  Returns -100 (bad arguments), -103 (shape), -104
+ * (pointers not 16-byte aligned). */
+int launch_khq_prestep_fp16(void* q_gate, void* k, const void* v, const void* q_norm_w,
+                            const void* k_norm_w, void* ring_k_slot, void* ring_v_slot, void* ring_u_slot,
+                            int H_q, int H_kv, int d, int rotary_dim, int pos, float rope_theta,
+                            float rms_eps, int has_norms, khq_stream_t stream);
+
 /* ---- Prefill: causal GQA attention + sigmoid gate over a whole prompt --------------------
  * The math of the reference's fp16-KV attention kernel (gqa_attention_sm75_gpu,
  * src/kernels/elementwise_sm75.mojo:1091-1231), which the reference launches once per prompt

@@ -720,3 +720,35 @@ void khq_oracle_partial_rope(uint16_t* vec, int num_heads, int head_dim, int rot
             vec[(size_t)h * st + i + half] = f2h(x0 * s + x1 * c);
         }
 }
+
+/* ============================================================ head RMSNorm ==== */
+/* Per-head RMSNorm in place on fp16 (src/kernels/elementwise_sm75.mojo:362-423): one warp per
+ * head; lane t sums the squares of dims t, t+32, ... in fp32, the 32 partial sums go through a
+ * shuffle-down tree (offsets 16, 8, 4, 2, 1; lane 0 holds the total), scale =
+ * 1/sqrt(sum/dim + eps), out = fp16(x*scale [* weight]).  The tree is reproduced so that the
+ * result is bit-identical. */
+void khq_oracle_head_rmsnorm(uint16_t* x, int num_heads, int head_dim, int stride, const float* weight,
+                             float eps) {
+    int st = stride > 0 ? stride : head_dim;
+    for (int h = 0; h < num_heads; ++h) {
+        uint16_t* p = x + (size_t)h * st;
+        float part[64];
+        for (int t = 0; t < 64; ++t) part[t] = 0.0f;
+        for (int t = 0; t < 32; ++t)
+            for (int d = t; d < head_dim; d += 32) {
+                float v = h2f(p[d]);
+                part[t] += v * v;
+            }
+        for (int off = 16; off > 0; off >>= 1) {
+            float nxt[32];
+            for (int t = 0; t < 32; ++t) nxt[t] = part[t] + ((t + off < 32) ? part[t + off] : part[t]);
+            for (int t = 0; t < 32; ++t) part[t] = nxt[t];
+        }
+        float scale = 1.0f / sqrtf(part[0] / (float)head_dim + eps);
+        for (int d = 0; d < head_dim; ++d) {
+            float n = h2f(p[d]) * scale;
+            if (weight) n *= weight[d];
+            p[d] = f2h(n);
+        }
+    }
+}

@@ -177,6 +177,13 @@ def partial_rope(vec, num_heads, head_dim, rotary_dim, pos, theta, stride):
     return vec
 
 
+def head_rmsnorm(x, num_heads, head_dim, stride, weight, eps):
+    """In place on a fp16 numpy array / CPU tensor."""
+    lib = load()
+    lib.khq_oracle_head_rmsnorm(_p(x), c_int(num_heads), c_int(head_dim), c_int(stride), _p(weight), c_float(eps))
+    return x
+
+
 # ---------------------------------------------------------------------------- launch backend
 class OracleLaunchError(RuntimeError):
     def __init__(self, name, code):
@@ -229,6 +236,24 @@ class OracleOps:
         rc = merge_gate(merged, merged, q_gate, out, H_q, d, 0)
         if rc:
             raise OracleLaunchError("merge_slots_gate", rc)
+
+    def prestep(self, q_gate, k, v, q_norm_w, k_norm_w, ring_k_slot, ring_v_slot, ring_u_slot, H_q, H_kv, d,
+                rotary_dim, pos, rope_theta, rms_eps, has_norms):
+        """q/k head RMSNorm, K capture, partial RoPE, ring appends (CPU torch tensors, in place)."""
+        if has_norms:
+            head_rmsnorm(q_gate, H_q, d, 2 * d, q_norm_w, rms_eps)
+            head_rmsnorm(k, H_kv, d, d, k_norm_w, rms_eps)
+        if ring_u_slot is not None:
+            ring_u_slot.copy_(k.reshape(ring_u_slot.shape))
+        lib = load()
+        lib.khq_oracle_partial_rope(_p(q_gate), c_int(H_q), c_int(d), c_int(rotary_dim), c_int(pos),
+                                    c_float(rope_theta), c_int(2 * d))
+        lib.khq_oracle_partial_rope(_p(k), c_int(H_kv), c_int(d), c_int(rotary_dim), c_int(pos),
+                                    c_float(rope_theta), c_int(d))
+        if ring_k_slot is not None:
+            ring_k_slot.copy_(k.reshape(ring_k_slot.shape))
+        if ring_v_slot is not None:
+            ring_v_slot.copy_(v.reshape(ring_v_slot.shape))
 
     def ring_write(self, dst_row, src):
         dst_row.copy_(src.reshape(dst_row.shape))

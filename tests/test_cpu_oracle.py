@@ -240,3 +240,14 @@ def test_oracle_far_position_vs_reference_kernel_golden(oracle):
                               float(g["alpha_v"]), 1e7, 100000, 0, 64)
     ok, mx, exc = cases.attention_close(cases.normalised(got), cases.normalised(g["attn_c_s1"]), atol=2e-2, rtol=5e-2)
     assert ok, (mx, exc)
+
+
+def test_head_rmsnorm_matches_float64_formula(oracle):
+    rng = np.random.default_rng(3)
+    x = (rng.standard_normal((24, 512)) * 2).astype(np.float16)
+    w = (1 + 0.1 * rng.standard_normal(256)).astype(np.float32)
+    got = oracle.head_rmsnorm(x.copy(), 24, 256, 512, w, 1e-6)
+    q = x[:, :256].astype(np.float64)
+    want = q / np.sqrt((q * q).mean(1, keepdims=True) + 1e-6) * w
+    assert np.abs(got[:, :256].astype(np.float64) - want).max() <= 2e-3 * np.abs(want).max()
+    assert np.array_equal(got[:, 256:].view(np.uint16), x[:, 256:].view(np.uint16))  # gate half untouched

@@ -56,3 +56,44 @@ def test_decode_loop_matches_oracle_backend(cuda_ops, oracle, monkeypatch):
     for k in sorted(g_out):
         ok, mx, exc = cases.attention_close(g_out[k], c_out[k])
         assert ok, f"step {k}: max abs {mx:.3e} excess {exc:.3e}"
+
+
+def test_decode_loop_with_fused_prestep(cuda_ops, oracle, monkeypatch):
+    """Same loop, but q/k arrive un-normed and un-RoPE'd and go through khq_prestep (one launch
+    for norm + capture + RoPE + ring appends) followed by khq_step(rings_written=True)."""
+    import torch
+
+    from bonsai_mojo_1bit_optimization_t4_cuda_b200.runtime import KhqRuntime
+
+    monkeypatch.setenv("BONSAI_KHQ_SPLITS", "8")
+    n_steps = 300
+    case = cases.make_case(cases.synth.seed_for(1, 7), n_steps, "n01_idrot", layer_id=7)
+    rng = np.random.default_rng(5)
+    qw = (1 + 0.1 * rng.standard_normal(D)).astype(np.float32)
+    kw = (1 + 0.1 * rng.standard_normal(D)).astype(np.float32)
+    q_raw = [(np.random.default_rng(100 + t).standard_normal((H_Q, 2 * D))).astype(np.float16) for t in range(n_steps)]
+    collect = {0, 100, 255, 256, 299}
+    res = {}
+    for name, ops, device in (("gpu", cuda_ops, "cuda"), ("cpu", oracle.OracleOps(), "cpu")):
+        rt = KhqRuntime(ops, device=device)
+        assert rt.khq_activate([case["tables"]], max_seq=1024)
+        rt.khq_init_layer(7, H_Q, H_KV, D)
+        outs = {}
+        for t in range(n_steps):
+            qg = torch.from_numpy(q_raw[t].copy()).to(device).reshape(-1)
+            k = torch.from_numpy(case["k_unroped"][t].copy()).to(device).reshape(-1)
+            v = torch.from_numpy(case["v"][t].copy()).to(device).reshape(-1)
+            out = torch.zeros(H_Q * D, dtype=torch.float16, device=device)
+            assert rt.khq_prestep(7, qg, k, v, t, torch.from_numpy(qw).to(device), torch.from_numpy(kw).to(device))
+            assert rt.khq_step(7, qg, k, v, out, SCALE, rings_written=True)
+            if t in collect:
+                outs[t] = out.float().cpu().numpy()
+        res[name] = (outs, rt)
+    (g_out, g_rt), (c_out, c_rt) = res["gpu"], res["cpu"]
+    assert [e.boundary for e in g_rt.events] == [e.boundary for e in c_rt.events] == [128]
+    for key in ("kmask", "kpay", "knorm", "krn", "vpay", "vnorm", "vrn", "vsm"):
+        n = 128 * H_KV * {"kmask": 16, "kpay": 40, "vpay": 104, "vsm": 4}.get(key, 1)
+        assert torch.equal(g_rt.layers[7].t[key].cpu()[:n].view(torch.uint8), c_rt.layers[7].t[key][:n].view(torch.uint8)), key
+    for t in sorted(g_out):
+        ok, mx, exc = cases.attention_close(g_out[t], c_out[t])
+        assert ok, f"step {t}: max abs {mx:.3e} excess {exc:.3e}"
