@@ -297,6 +297,59 @@ class KhqRuntime:
         self._tock(KHQ_P_MERGE, t0)
         return True
 
+    # ------------------------------------------------------------------ prompt prefill (addition)
+    def khq_prefill(self, layer_idx: int, q_gate_dev, k_unroped_dev, k_roped_dev, v_dev, out_dev, scale: float) -> bool:
+        """Whole-prompt path for one layer: causal GQA attention of all T prompt rows at once
+        (``ops.gqa_prefill``; the reference loops its decode kernel over the prompt,
+        ``src/models/qwen3_5/layer.mojo:630-641``), then the KHQ state that the per-token path would
+        have left behind: every full 128-token chunk except the last one is compressed (K from the
+        un-RoPE'd rows, V as is), the remaining 128..255 newest tokens sit in the rings at slots
+        ``token % 256``, ``boundary``/``write_pos`` are advanced accordingly.
+
+        q_gate (T, H_q, 2d), k_unroped / k_roped (T, H_kv, d), v (T, H_kv, d), out (T, H_q, d): fp16.
+        The code words are bit-identical to the per-token path's (same inputs to the same compress
+        launches); the attention outputs of prompt rows are exact fp16-KV attention, whereas the
+        per-token path attends older tokens through their lossy decompression.
+        Only valid on a fresh layer (write_pos == 0)."""
+        if not self.active or not self.ready or layer_idx < 0 or layer_idx >= KHQ_MAX_LAYERS:
+            return False
+        L = self.layers[layer_idx]
+        if not L.ready or L.write_pos != 0:
+            return False
+        ops, Tn = self.ops, L.t
+        H_q, H_kv, d = L.H_q, L.H_kv, L.D
+        kv = H_kv * d
+        T = int(k_roped_dev.shape[0])
+        ops.gqa_prefill(q_gate_dev, k_roped_dev, v_dev, out_dev, 1, T, H_q, H_kv, d, scale)
+        # the per-token path compresses chunk c when write_pos reaches 128*(c+2), capped by `cap`
+        n_chunks = 0
+        while (n_chunks + 2) * KHQ_CHUNK <= T and (n_chunks + 1) * KHQ_CHUNK <= L.cap:
+            n_chunks += 1
+        if n_chunks > 0:
+            rows = n_chunks * KHQ_CHUNK * H_kv
+            ku = k_unroped_dev.reshape(-1)
+            vv = v_dev.reshape(-1)
+            ops.compress(ku, Tn["dk"], Tn["rk"], Tn["ck"], Tn["ck"], Tn["kmask"], Tn["knorm"], Tn["krn"], Tn["kpay"],
+                         Tn["vsm"], rows, d, L.ts_k, L.alpha_k, False)
+            ops.compress(vv, Tn["dv"], Tn["rv"], Tn["cv"], Tn["vq"], Tn["kmask"], Tn["vnorm"], Tn["vrn"], Tn["vpay"],
+                         Tn["vsm"], rows, d, L.ts_v, L.alpha_v, True)
+        L.boundary = n_chunks * KHQ_CHUNK
+        L.write_pos = T
+        # newest min(T, 256) tokens into the rings at slot = token % 256
+        first = max(0, T - KHQ_RING)
+        for name, src in (("ring_k", k_roped_dev), ("ring_v", v_dev), ("ring_u", k_unroped_dev)):
+            ring = Tn[name].view(KHQ_RING, kv)
+            s2 = src.reshape(T, kv)
+            a = first % KHQ_RING
+            n = T - first
+            head = min(n, KHQ_RING - a)
+            ring[a:a + head].copy_(s2[first:first + head])
+            if n > head:
+                ring[0:n - head].copy_(s2[first + head:T])
+        for c in range(n_chunks):
+            self.events.append(KhqCompressEvent(layer_idx, c + 1, (c + 1) * KHQ_CHUNK, (c + 2) * KHQ_CHUNK, KHQ_CHUNK))
+        return True
+
     # ------------------------------------------------------------------ khq_prof_report
     def khq_prof_report(self, n_tokens: int) -> Optional[str]:
         if not self.prof or n_tokens <= 0:

@@ -237,6 +237,14 @@ class OracleOps:
         if rc:
             raise OracleLaunchError("merge_slots_gate", rc)
 
+    def gqa_prefill(self, q_gate, k, v, out, batch, T, H_q, H_kv, d, scale):
+        import torch
+
+        for b in range(batch):
+            o = gqa_prefill(q_gate.reshape(batch, -1)[b].numpy(), k.reshape(batch, -1)[b].numpy(),
+                            v.reshape(batch, -1)[b].numpy(), T, H_q, H_kv, d, scale)
+            out.reshape(batch, -1)[b].copy_(torch.from_numpy(o.reshape(-1)).to(out.dtype))
+
     def prestep(self, q_gate, k, v, q_norm_w, k_norm_w, ring_k_slot, ring_v_slot, ring_u_slot, H_q, H_kv, d,
                 rotary_dim, pos, rope_theta, rms_eps, has_norms):
         """q/k head RMSNorm, K capture, partial RoPE, ring appends (CPU torch tensors, in place)."""

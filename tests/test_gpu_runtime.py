@@ -97,3 +97,56 @@ def test_decode_loop_with_fused_prestep(cuda_ops, oracle, monkeypatch):
     for t in sorted(g_out):
         ok, mx, exc = cases.attention_close(g_out[t], c_out[t])
         assert ok, f"step {t}: max abs {mx:.3e} excess {exc:.3e}"
+
+
+@pytest.mark.parametrize("T", [300, 511, 640])
+def test_prefill_leaves_the_per_token_state(cuda_ops, oracle, T, monkeypatch):
+    """khq_prefill (one attention launch + two compress launches) must leave the KHQ state that T
+    per-token khq_step calls leave: same boundary/write_pos, bit-identical code words, identical
+    rings; then one more decode step on top of either state gives the same output."""
+    import torch
+
+    from bonsai_mojo_1bit_optimization_t4_cuda_b200.runtime import KhqRuntime
+
+    monkeypatch.setenv("BONSAI_KHQ_SPLITS", "8")
+    case = cases.make_case(8800 + T, T + 1, "calib", layer_id=3)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    ku, kr, v = dev(case["k_unroped"]), dev(case["k_roped"]), dev(case["v"])
+    rng = np.random.default_rng(1)
+    qg_all = dev(rng.standard_normal((T, H_Q, 2 * D)).astype(np.float16))
+    # per-token path
+    a = KhqRuntime(cuda_ops, device="cuda")
+    assert a.khq_activate([case["tables"]], max_seq=1024)
+    a.khq_init_layer(3, H_Q, H_KV, D)
+    out = torch.zeros(H_Q * D, dtype=torch.float16, device="cuda")
+    for t in range(T):
+        a.khq_capture_unroped(3, ku[t])
+        assert a.khq_step(3, qg_all[t].reshape(-1), kr[t], v[t], out, SCALE)
+    # prompt path
+    b = KhqRuntime(cuda_ops, device="cuda")
+    assert b.khq_activate([case["tables"]], max_seq=1024)
+    b.khq_init_layer(3, H_Q, H_KV, D)
+    out_p = torch.zeros(T, H_Q, D, dtype=torch.float16, device="cuda")
+    assert b.khq_prefill(3, qg_all, ku[:T], kr[:T], v[:T], out_p, SCALE)
+    La, Lb = a.layers[3], b.layers[3]
+    assert (La.boundary, La.write_pos) == (Lb.boundary, Lb.write_pos)
+    assert [(e.boundary, e.write_pos) for e in a.events] == [(e.boundary, e.write_pos) for e in b.events]
+    rows = La.boundary * H_KV
+    for key, w in (("kmask", 16), ("kpay", 40), ("knorm", 1), ("krn", 1), ("vpay", 104), ("vnorm", 1), ("vrn", 1), ("vsm", 4)):
+        assert torch.equal(La.t[key][:rows * w].view(torch.uint8), Lb.t[key][:rows * w].view(torch.uint8)), key
+    live = [(t % 256) for t in range(La.boundary, T)]
+    for ring in ("ring_k", "ring_v", "ring_u"):
+        assert torch.equal(La.t[ring].view(256, -1)[live], Lb.t[ring].view(256, -1)[live]), ring
+    # prompt rows: exact causal attention == oracle
+    ref = oracle.gqa_prefill(qg_all.cpu().numpy(), case["k_roped"][:T], case["v"][:T], T, H_Q, H_KV, D, SCALE)
+    ok, mx, exc = cases.attention_close(out_p.float().cpu().numpy()[-5:], ref[-5:])
+    assert ok, (mx, exc)
+    # one more token on both states
+    qn = dev(cases.synth.make_q_gate(rng, T)).reshape(-1)
+    oa = torch.zeros(H_Q * D, dtype=torch.float16, device="cuda")
+    ob = torch.zeros(H_Q * D, dtype=torch.float16, device="cuda")
+    for rt, o in ((a, oa), (b, ob)):
+        rt.khq_capture_unroped(3, ku[T])
+        assert rt.khq_step(3, qn, kr[T], v[T], o, SCALE)
+    torch.cuda.synchronize()
+    assert torch.equal(oa, ob)
