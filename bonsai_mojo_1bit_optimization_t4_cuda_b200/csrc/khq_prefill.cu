@@ -222,10 +222,10 @@ khq_gqa_prefill_kernel(const __half* __restrict__ q_gate, const __half* __restri
 
 }  // namespace khq_prefill
 
-extern "C" int launch_khq_gqa_prefill_fp16(const void* q_gate, const void* k, const void* v, void* out,
-                                           int batch, int T, int H_q, int H_kv, int d, float scale,
-                                           long long q_batch_stride, long long kv_batch_stride,
-                                           long long out_batch_stride, cudaStream_t stream) {
+extern "C" int launch_khq_gqa_prefill_mma_fp16(const void* q_gate, const void* k, const void* v, void* out,
+                                               int batch, int T, int H_q, int H_kv, int d, float scale,
+                                               long long q_batch_stride, long long kv_batch_stride,
+                                               long long out_batch_stride, cudaStream_t stream) {
     using namespace khq_prefill;
     if (batch <= 0 || T <= 0 || H_q <= 0 || H_kv <= 0) return -100;
     if (d != D || H_q % H_kv != 0) return -103;
@@ -248,4 +248,26 @@ extern "C" int launch_khq_gqa_prefill_fp16(const void* q_gate, const void* k, co
         out_batch_stride);
     err = cudaGetLastError();
     return (err == cudaSuccess) ? 0 : static_cast<int>(err);
+}
+
+// ---- kernel selection -----------------------------------------------------------------------------
+extern "C" int launch_khq_gqa_prefill_tc5_fp16(const void* q_gate, const void* k, const void* v, void* out,
+                                               int batch, int T, int H_q, int H_kv, int d, float scale,
+                                               long long q_batch_stride, long long kv_batch_stride,
+                                               long long out_batch_stride, cudaStream_t stream);
+
+static int g_prefill_kernel = 0;  // 0: tcgen05 / tensor-memory kernel, 1: warp-level mma.sync kernel
+
+extern "C" int khq_b200_prefill_select(int which) {
+    if (which != 0 && which != 1) return -100;
+    g_prefill_kernel = which;
+    return 0;
+}
+
+extern "C" int launch_khq_gqa_prefill_fp16(const void* q_gate, const void* k, const void* v, void* out,
+                                           int batch, int T, int H_q, int H_kv, int d, float scale,
+                                           long long q_batch_stride, long long kv_batch_stride,
+                                           long long out_batch_stride, cudaStream_t stream) {
+    return (g_prefill_kernel == 0 ? launch_khq_gqa_prefill_tc5_fp16 : launch_khq_gqa_prefill_mma_fp16)(
+        q_gate, k, v, out, batch, T, H_q, H_kv, d, scale, q_batch_stride, kv_batch_stride, out_batch_stride, stream);
 }

@@ -1,0 +1,439 @@
+// khq_prefill_tc5.cu -- causal GQA prefill attention with sigmoid output gate on the fifth
+// generation tensor cores (tcgen05.mma, accumulators in tensor memory, operands staged by TMA).
+//
+// Same math and the same tensors as the warp-level kernel in khq_prefill.cu (the reference's
+// fp16-KV attention, src/kernels/elementwise_sm75.mojo:1140-1231, applied to all prompt rows at
+// once): out[t,h,:] = softmax_{u<=t}(q[t,h].K[u,h/6]*scale) V[u,h/6] * sigmoid(gate[t,h,:]).
+//
+// One CTA = 128 query rows of one query head; key tiles of 64.  Six warps, three roles:
+//   warps 0-3  softmax: thread i owns query row i -- its S row and its O row are tensor-memory
+//              lane i, so row max / row sum need no shuffles.  Reads S (64 fp32 columns) with
+//              tcgen05.ld, writes P (fp16) to shared memory, rescales O lazily (only when the
+//              running max grew by more than 2^8), and runs the epilogue.
+//   warp 4     producer: one thread issues the TMA loads of Q and of the K/V tiles (2 stages).
+//   warp 5     MMA: one thread issues S = Q K^T (M128 N64 K256) for tile j+1, then O += P V
+//              (M128 N256 K64) for tile j; tcgen05.commit signals the mbarriers.
+// Tensor memory columns: S ping [0,64), S pong [64,128), O [256,512).
+//
+// Shared-memory operand layout: no swizzle, 8x8 "core matrices" of 128 contiguous bytes.  A
+// 5-D tensor map {8 halfs, row, 16-byte chunk, head, batch} makes TMA write a (rows x 256) tile
+// as [chunk][row][8 halfs] = chunk*rows*16 + row*16 bytes, which is that layout with
+//   K-major  (Q, K, P): leading-dim byte offset (between 8-element K groups)  = rows*16,
+//                       stride-dim byte offset (between 8-row groups)         = 128;
+//   MN-major (V as the B operand of P V, keys are the contraction dim):
+//                       leading (between 8-key groups) = 128, stride (between 8-dim groups) = rows*16.
+// Every wait is bounded; a wait that runs out sets a status word the host can read and the CTA
+// falls through to the teardown (tensor memory is always released).
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "khq_common.cuh"
+
+namespace khq_prefill5 {
+
+using khq::smem_u32;
+
+constexpr int D = 256;
+constexpr int BR = 128;  // query rows per CTA
+constexpr int BC = 64;   // keys per tile
+constexpr int NTHREADS = 192;
+constexpr int Q_BYTES = BR * D * 2;   // 64 KB
+constexpr int KV_BYTES = BC * D * 2;  // 32 KB
+constexpr int P_BYTES = BR * BC * 2;  // 16 KB
+constexpr int OFF_Q = 0;
+constexpr int OFF_K0 = OFF_Q + Q_BYTES;
+constexpr int OFF_V0 = OFF_K0 + KV_BYTES;
+constexpr int OFF_K1 = OFF_V0 + KV_BYTES;
+constexpr int OFF_V1 = OFF_K1 + KV_BYTES;
+constexpr int OFF_P = OFF_V1 + KV_BYTES;
+constexpr int OFF_BARS = OFF_P + P_BYTES;
+constexpr int SMEM_BYTES = OFF_BARS + 256;
+constexpr uint32_t TM_COLS = 512, TM_S = 0, TM_O = 256;
+constexpr float RESCALE_LOG2 = 8.0f;
+
+enum Bar { B_QFULL = 0, B_KFULL = 1, B_VFULL = 3, B_EMPTY = 5, B_SFULL = 7, B_PREADY = 9, B_PVDONE = 10, B_COUNT = 11 };
+
+__device__ int g_prefill_status = 0;
+
+// ---- descriptors ---------------------------------------------------------------------------------
+// Shared-memory matrix descriptor, no swizzle: start address, leading and stride byte offsets
+// (all in 16-byte units), descriptor version 1 in bits 46-47.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)((lbo >> 4) & 0x3FFFu) << 16) |
+           ((uint64_t)((sbo >> 4) & 0x3FFFu) << 32) | ((uint64_t)1 << 46);
+}
+// Instruction descriptor for kind::f16: fp32 accumulate, fp16 A and B, A K-major, M = 128.
+__host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
+    return (1u << 4) | (b_mn_major ? (1u << 16) : 0u) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+
+// ---- tcgen05 / TMA wrappers ----------------------------------------------------------------------
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+        "%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+        "%29,%30,%31};" ::"r"(r[0]),
+        "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+        "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]),
+        "r"(r[29]), "r"(r[30]), "r"(r[31]), "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// One 5-D tiled TMA load (no multicast); coordinate 0 is always 0, so the 16-byte rule holds.
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int c1, int c3,
+                                            int c4) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, "
+        "%6, %7}], [%2];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(0), "r"(c1), "r"(0), "r"(c3), "r"(c4)
+        : "memory");
+}
+
+// ---- the kernel ----------------------------------------------------------------------------------
+// grid = (ceil(T/128), H_q, batch).  q_gate (B, T, H_q, 2D), out (B, T, H_q, D); K and V only
+// through their tensor maps.
+__global__ void __launch_bounds__(NTHREADS, 1)
+khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                           const __grid_constant__ CUtensorMap tm_v, const __half* __restrict__ q_gate,
+                           __half* __restrict__ out, int T, int H_q, int H_kv, float scale_log2e, long long q_bs,
+                           long long o_bs) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BARS);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_BARS + 128);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;  // heaviest row blocks first
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int kvh = h / (H_q / H_kv);
+    const int q0 = qb * BR;
+    const int n_tiles = min((T + BC - 1) / BC, (q0 + BR) / BC);
+    int* status = &g_prefill_status;
+
+    if (tid == 0) {
+        khq::mbar_init(&bars[B_QFULL], 1);
+        for (int s = 0; s < 2; ++s) {
+            khq::mbar_init(&bars[B_KFULL + s], 1);
+            khq::mbar_init(&bars[B_VFULL + s], 1);
+            khq::mbar_init(&bars[B_EMPTY + s], 1);
+            khq::mbar_init(&bars[B_SFULL + s], 1);
+        }
+        khq::mbar_init(&bars[B_PREADY], 128);
+        khq::mbar_init(&bars[B_PVDONE], 1);
+        khq::fence_barrier_init();
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "n"(TM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t sbase = smem_u32(smem);
+
+    if (warp == 4) {
+        // ================================ producer ================================================
+        if (lane == 0) {
+            khq::mbar_arrive_expect_tx(&bars[B_QFULL], Q_BYTES);
+            tma_load_5d(sbase + OFF_Q, &tm_q, &bars[B_QFULL], q0, h, b);
+            int issued = 0;
+            for (int j = 0; j < n_tiles; ++j) {
+                const int s = j & 1;
+                if (j >= 2 && !khq::mbar_wait_bounded(&bars[B_EMPTY + s], (uint32_t)(((j >> 1) - 1) & 1), status)) break;
+                khq::mbar_arrive_expect_tx(&bars[B_KFULL + s], KV_BYTES);
+                tma_load_5d(sbase + (s ? OFF_K1 : OFF_K0), &tm_k, &bars[B_KFULL + s], j * BC, kvh, b);
+                khq::mbar_arrive_expect_tx(&bars[B_VFULL + s], KV_BYTES);
+                tma_load_5d(sbase + (s ? OFF_V1 : OFF_V0), &tm_v, &bars[B_VFULL + s], j * BC, kvh, b);
+                issued = j + 1;
+            }
+            // nothing this thread started may still be in flight when the CTA leaves
+            khq::mbar_wait_bounded(&bars[B_QFULL], 0u, status);
+            for (int j = max(0, issued - 2); j < issued; ++j) {
+                khq::mbar_wait_bounded(&bars[B_KFULL + (j & 1)], (uint32_t)((j >> 1) & 1), status);
+                khq::mbar_wait_bounded(&bars[B_VFULL + (j & 1)], (uint32_t)((j >> 1) & 1), status);
+            }
+        }
+    } else if (warp == 5) {
+        // ================================ MMA issuer ==============================================
+        if (lane == 0) {
+            constexpr uint32_t IDESC_S = instr_desc(BC, false);
+            constexpr uint32_t IDESC_O = instr_desc(D, true);
+            auto issue_qk = [&](int j) {
+                const uint32_t kaddr = sbase + ((j & 1) ? OFF_K1 : OFF_K0);
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint64_t da = smem_desc(sbase + OFF_Q + ks * 2 * (BR * 16), BR * 16, 128);
+                    const uint64_t db = smem_desc(kaddr + ks * 2 * (BC * 16), BC * 16, 128);
+                    umma_f16(tmem + TM_S + (uint32_t)(j & 1) * BC, da, db, IDESC_S, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(&bars[B_SFULL + (j & 1)]);
+            };
+            bool ok = khq::mbar_wait_bounded(&bars[B_QFULL], 0u, status) &&
+                      khq::mbar_wait_bounded(&bars[B_KFULL], 0u, status);
+            if (ok) {
+                tc_fence_after();
+                issue_qk(0);
+            }
+            for (int j = 0; ok && j < n_tiles; ++j) {
+                if (j + 1 < n_tiles) {
+                    ok = khq::mbar_wait_bounded(&bars[B_KFULL + ((j + 1) & 1)], (uint32_t)(((j + 1) >> 1) & 1), status);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_qk(j + 1);
+                }
+                ok = khq::mbar_wait_bounded(&bars[B_PREADY], (uint32_t)(j & 1), status) &&
+                     khq::mbar_wait_bounded(&bars[B_VFULL + (j & 1)], (uint32_t)((j >> 1) & 1), status);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t vaddr = sbase + ((j & 1) ? OFF_V1 : OFF_V0);
+#pragma unroll
+                for (int ks = 0; ks < BC / 16; ++ks) {
+                    const uint64_t da = smem_desc(sbase + OFF_P + ks * 2 * (BR * 16), BR * 16, 128);
+                    const uint64_t db = smem_desc(vaddr + ks * 2 * 128, 128, BC * 16);
+                    umma_f16(tmem + TM_O, da, db, IDESC_O, (j > 0 || ks > 0) ? 1u : 0u);
+                }
+                umma_commit(&bars[B_PVDONE]);
+                umma_commit(&bars[B_EMPTY + (j & 1)]);
+            }
+        }
+    } else {
+        // ================================ softmax + epilogue ======================================
+        const int row = q0 + tid;
+        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+        float m_used = -1e30f, l_run = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            ok = __all_sync(0xFFFFFFFFu, khq::mbar_wait_bounded(&bars[B_SFULL + (j & 1)], (uint32_t)((j >> 1) & 1), status));
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t sr[2][32];
+            tmem_ld32(lane_base + TM_S + (uint32_t)(j & 1) * BC, sr[0]);
+            tmem_ld32(lane_base + TM_S + (uint32_t)(j & 1) * BC + 32, sr[1]);
+            tmem_ld_wait();
+            const int k0 = j * BC;
+            const bool need_mask = (k0 + BC - 1 > q0) || (k0 + BC > T);
+            float mx = -1e30f;
+#pragma unroll
+            for (int c = 0; c < BC; ++c) {
+                float x = __uint_as_float(sr[c >> 5][c & 31]) * scale_log2e;
+                if (need_mask && (k0 + c > row || k0 + c >= T)) x = -1e30f;
+                sr[c >> 5][c & 31] = __float_as_uint(x);
+                mx = fmaxf(mx, x);
+            }
+            float factor = 1.0f;
+            bool grow = false;
+            if (j == 0) {
+                m_used = mx;
+            } else if (mx > m_used + RESCALE_LOG2) {
+                factor = exp2f(m_used - mx);
+                m_used = mx;
+                grow = true;
+            }
+            float rs = 0.0f;
+            uint32_t pk[BC / 2];
+#pragma unroll
+            for (int c = 0; c < BC; c += 2) {
+                const float p0 = exp2f(__uint_as_float(sr[c >> 5][c & 31]) - m_used);
+                const float p1 = exp2f(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]) - m_used);
+                rs += p0 + p1;
+                const __half2 hh = __floats2half2_rn(p0, p1);
+                pk[c >> 1] = *reinterpret_cast<const uint32_t*>(&hh);
+            }
+            l_run = l_run * factor + rs;
+            if (j > 0) {
+                // P's buffer and the O accumulator are free once P V of the previous tile is done
+                ok = __all_sync(0xFFFFFFFFu, khq::mbar_wait_bounded(&bars[B_PVDONE], (uint32_t)((j - 1) & 1), status));
+                if (!ok) break;
+                tc_fence_after();
+                if (__any_sync(0xFFFFFFFFu, grow)) {
+#pragma unroll 1
+                    for (int c0 = 0; c0 < D; c0 += 32) {
+                        uint32_t orr[32];
+                        tmem_ld32(lane_base + TM_O + c0, orr);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * factor);
+                        tmem_st32(lane_base + TM_O + c0, orr);
+                    }
+                    tmem_st_wait();
+                }
+            }
+            // P row -> shared memory, K-major core-matrix layout: chunk c8 (8 keys) at c8*2048 + row*16
+#pragma unroll
+            for (int c8 = 0; c8 < BC / 8; ++c8) {
+                const uint32_t dst = sbase + OFF_P + c8 * (BR * 16) + tid * 16;
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[c8 * 4]), "r"(pk[c8 * 4 + 1]),
+                             "r"(pk[c8 * 4 + 2]), "r"(pk[c8 * 4 + 3])
+                             : "memory");
+            }
+            khq::fence_proxy_async();
+            tc_fence_before();
+            khq::mbar_arrive(&bars[B_PREADY]);
+        }
+        if (ok) ok = khq::mbar_wait_bounded(&bars[B_PVDONE], (uint32_t)((n_tiles - 1) & 1), status);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        if (ok) {
+            tc_fence_after();
+            const float inv = 1.0f / (l_run + 1e-9f);
+            const long long q_row = (long long)H_q * 2 * D, o_row = (long long)H_q * D;
+            const bool live = row < T;
+            const __half* gate = q_gate + b * q_bs + (long long)(live ? row : 0) * q_row + (long long)h * 2 * D + D;
+            __half* op = out + b * o_bs + (long long)(live ? row : 0) * o_row + (long long)h * D;
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t orr[32];
+                tmem_ld32(lane_base + TM_O + c0, orr);
+                tmem_ld_wait();
+                if (live) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        const uint4 g4 = *reinterpret_cast<const uint4*>(gate + c0 + i);
+                        const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w};
+                        uint32_t ow[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const __half2 gg = *reinterpret_cast<const __half2*>(&gw[e]);
+                            const float g0 = __half2float(__low2half(gg)), g1 = __half2float(__high2half(gg));
+                            const float x0 = __uint_as_float(orr[i + 2 * e]) * inv * (1.0f / (1.0f + __expf(-g0)));
+                            const float x1 = __uint_as_float(orr[i + 2 * e + 1]) * inv * (1.0f / (1.0f + __expf(-g1)));
+                            const __half2 oo = __floats2half2_rn(x0, x1);
+                            ow[e] = *reinterpret_cast<const uint32_t*>(&oo);
+                        }
+                        *reinterpret_cast<uint4*>(op + c0 + i) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                    }
+                }
+            }
+        }
+    }
+    // ---- teardown: every thread arrives here, with or without a failed wait ----------------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(TM_COLS) : "memory");
+    }
+}
+
+}  // namespace khq_prefill5
+
+// ---- host side -----------------------------------------------------------------------------------
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// Tensor map over a (batch, T, heads, row_halfs) fp16 tensor that exposes, per (head, batch), a
+// T x 256 matrix as {8 halfs, T rows, 32 chunks}; a box is `box_rows` rows of one head.
+int make_map(CUtensorMap* map, const void* base, int T, int heads, int batch, long long row_halfs,
+             long long head_halfs, long long batch_halfs, int box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return -107;
+    if (batch == 1) batch_halfs = (long long)T * row_halfs;
+    const cuuint64_t dims[5] = {8, (cuuint64_t)T, 32, (cuuint64_t)heads, (cuuint64_t)batch};
+    const cuuint64_t strides[4] = {(cuuint64_t)row_halfs * 2, 16, (cuuint64_t)head_halfs * 2, (cuuint64_t)batch_halfs * 2};
+    const cuuint32_t box[5] = {8, (cuuint32_t)box_rows, 32, 1, 1};
+    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    for (cuuint64_t st : strides)
+        if (st % 16 != 0) return -104;
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -108;
+}
+
+}  // namespace
+
+// Same arguments as launch_khq_gqa_prefill_fp16.  Returns -107 when the driver offers no tensor-map
+// encoder and -108 when it refuses these shapes.
+extern "C" int launch_khq_gqa_prefill_tc5_fp16(const void* q_gate, const void* k, const void* v, void* out, int batch,
+                                               int T, int H_q, int H_kv, int d, float scale,
+                                               long long q_batch_stride, long long kv_batch_stride,
+                                               long long out_batch_stride, cudaStream_t stream) {
+    using namespace khq_prefill5;
+    if (batch <= 0 || T <= 0 || H_q <= 0 || H_kv <= 0) return -100;
+    if (d != D || H_q % H_kv != 0) return -103;
+    const void* ptrs[] = {q_gate, k, v, out};
+    for (const void* p : ptrs)
+        if ((reinterpret_cast<uintptr_t>(p) & 15) != 0) return -104;
+    if (batch > 1 && ((q_batch_stride | kv_batch_stride | out_batch_stride) & 7) != 0) return -104;
+    CUtensorMap mq, mk, mv;
+    int rc = make_map(&mq, q_gate, T, H_q, batch, (long long)H_q * 2 * D, 2 * D, q_batch_stride, BR);
+    if (rc == 0) rc = make_map(&mk, k, T, H_kv, batch, (long long)H_kv * D, D, kv_batch_stride, BC);
+    if (rc == 0) rc = make_map(&mv, v, T, H_kv, batch, (long long)H_kv * D, D, kv_batch_stride, BC);
+    if (rc != 0) return rc;
+    static bool attr_done[64] = {};
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return static_cast<int>(err);
+    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+        err = cudaFuncSetAttribute(khq_gqa_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (err != cudaSuccess) return static_cast<int>(err);
+        if (dev >= 0 && dev < 64) attr_done[dev] = true;
+    }
+    const dim3 grid((unsigned)((T + BR - 1) / BR), (unsigned)H_q, (unsigned)batch);
+    khq_gqa_prefill_tc5_kernel<<<grid, NTHREADS, SMEM_BYTES, stream>>>(
+        mq, mk, mv, static_cast<const __half*>(q_gate), static_cast<__half*>(out), T, H_q, H_kv,
+        scale * 1.4426950408889634f, q_batch_stride, out_batch_stride);
+    err = cudaGetLastError();
+    return (err == cudaSuccess) ? 0 : static_cast<int>(err);
+}
+
+// Reads and clears the status word of the tcgen05 prefill kernel on the current device
+// (synchronises the device): 0 = clean, 1 = a bounded wait ran out.
+extern "C" int khq_b200_prefill_status(void) {
+    int st = 0;
+    if (cudaMemcpyFromSymbol(&st, khq_prefill5::g_prefill_status, sizeof(int)) != cudaSuccess) return -1;
+    if (st != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(khq_prefill5::g_prefill_status, &zero, sizeof(int));
+    }
+    return st;
+}

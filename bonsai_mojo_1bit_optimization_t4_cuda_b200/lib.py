@@ -36,6 +36,12 @@ SIGNATURES = {
     "launch_khq_merge_slots_gate_fp16": (c_int, [_P, c_int, _P, _P, c_int, c_int, _P]),
     "launch_khq_gqa_prefill_fp16": (
         c_int, [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_longlong, c_longlong, c_longlong, _P]),
+    "launch_khq_gqa_prefill_tc5_fp16": (
+        c_int, [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_longlong, c_longlong, c_longlong, _P]),
+    "launch_khq_gqa_prefill_mma_fp16": (
+        c_int, [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_longlong, c_longlong, c_longlong, _P]),
+    "khq_b200_prefill_select": (c_int, [c_int]),
+    "khq_b200_prefill_status": (c_int, []),
     "launch_khq_prestep_fp16": (c_int, [_P] * 8 + [c_int] * 5 + [c_float, c_float, c_int, _P]),
     "khq_b200_version": (c_char_p, []),
     "khq_b200_device_status": (c_int, []),

@@ -204,6 +204,27 @@ int launch_khq_gqa_prefill_fp16(const void* q_gate, const void* k, const void* v
                                 long long kv_batch_stride, long long out_batch_stride,
                                 khq_stream_t stream);
 
+/* The two kernels behind launch_khq_gqa_prefill_fp16, with its arguments and error codes.  No
+ * reference counterpart (the reference has one attention kernel, launched per token).
+ *   _tc5_: tcgen05.mma with accumulators in tensor memory, operands staged by TMA tensor maps
+ *          built per call; also returns -107 (the driver exposes no tensor-map encoder) or -108
+ *          (the encoder refused the shapes; batch strides must be multiples of 8 elements).
+ *   _mma_: warp-level mma.sync kernel.
+ * khq_b200_prefill_select(0) routes launch_khq_gqa_prefill_fp16 to _tc5_ (the default), (1) to
+ * _mma_; returns -100 for any other value.  khq_b200_prefill_status() synchronises the device,
+ * returns and clears the _tc5_ kernel's status word: 0 clean, 1 a bounded wait ran out (the
+ * output of that launch is then meaningless), -1 the read failed. */
+int launch_khq_gqa_prefill_tc5_fp16(const void* q_gate, const void* k, const void* v, void* out, int batch,
+                                    int T, int H_q, int H_kv, int d, float scale, long long q_batch_stride,
+                                    long long kv_batch_stride, long long out_batch_stride,
+                                    khq_stream_t stream);
+int launch_khq_gqa_prefill_mma_fp16(const void* q_gate, const void* k, const void* v, void* out, int batch,
+                                    int T, int H_q, int H_kv, int d, float scale, long long q_batch_stride,
+                                    long long kv_batch_stride, long long out_batch_stride,
+                                    khq_stream_t stream);
+int khq_b200_prefill_select(int which);
+int khq_b200_prefill_status(void);
+
 /* ---- Context parallelism: one long sequence split by context range over several GPUs ------
  * Each GPU calls launch_khq_attn_fp16 on its slice (start_pos = first absolute token of the
  * slice) and obtains an unnormalised (24, 258) partial; the owner of the raw ring adds the

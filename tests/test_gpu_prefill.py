@@ -8,18 +8,27 @@ from cases import D, H_KV, H_Q, SCALE
 pytestmark = pytest.mark.gpu
 
 
-def _run(cuda_ops, qg, k, v, B, T, H_q=H_Q, H_kv=H_KV):
+KERNELS = ["tc5", "mma"]  # tcgen05 / tensor-memory kernel (the default) and the warp-level mma.sync kernel
+
+
+def _run(cuda_ops, qg, k, v, B, T, H_q=H_Q, H_kv=H_KV, kernel="tc5"):
     import torch
 
     dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
     out = torch.full((B, T, H_q, D), float("nan"), dtype=torch.float16, device="cuda")
-    cuda_ops.gqa_prefill(dev(qg), dev(k), dev(v), out, B, T, H_q, H_kv, D, SCALE)
-    torch.cuda.synchronize()
+    assert cuda_ops.lib.khq_b200_prefill_select(KERNELS.index(kernel)) == 0
+    try:
+        cuda_ops.gqa_prefill(dev(qg), dev(k), dev(v), out, B, T, H_q, H_kv, D, SCALE)
+        torch.cuda.synchronize()
+    finally:
+        cuda_ops.lib.khq_b200_prefill_select(0)
+    assert cuda_ops.lib.khq_b200_prefill_status() == 0
     return out.float().cpu().numpy()
 
 
-@pytest.mark.parametrize("T", [1, 64, 65, 200, 321])
-def test_prefill_vs_oracle(cuda_ops, oracle, T):
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("T", [1, 64, 65, 200, 321, 1000])
+def test_prefill_vs_oracle(cuda_ops, oracle, T, kernel):
     B = 2
     rng = np.random.default_rng(50 + T)
     qg = rng.standard_normal((B, T, H_Q, 2 * D)).astype(np.float16)
@@ -27,15 +36,16 @@ def test_prefill_vs_oracle(cuda_ops, oracle, T):
     k = np.stack([cases.synth.make_kv(rng, T, sk, sv)[0] for _ in range(B)])
     v = np.stack([cases.synth.make_kv(rng, T, sk, sv)[1] for _ in range(B)])
     k = (k.astype(np.float32) * 0.25).astype(np.float16)  # keep the scores in a softmax-friendly range
-    got = _run(cuda_ops, qg, k, v, B, T)
+    got = _run(cuda_ops, qg, k, v, B, T, kernel=kernel)
     for b in range(B):
         ref = oracle.gqa_prefill(qg[b], k[b], v[b], T, H_Q, H_KV, D, SCALE)
         ok, mx, exc = cases.attention_close(got[b], ref)
         assert ok, f"T={T} batch {b}: max abs {mx:.3e}, excess {exc:.3e}"
 
 
+@pytest.mark.parametrize("kernel", KERNELS)
 @pytest.mark.parametrize("H_q,H_kv,seq", [(24, 4, 8), (4, 2, 16), (4, 2, 1)])
-def test_prefill_on_reference_fixture_fills(cuda_ops, oracle, H_q, H_kv, seq):
+def test_prefill_on_reference_fixture_fills(cuda_ops, oracle, H_q, H_kv, seq, kernel):
     """The reference's deterministic fills (tests/test_gqa_attention_gpu.mojo:105-109) and cases
     (:188-194): every prompt row carries the fixture query, so row seq-1 of the prefill is the
     reference test's single decode row over `seq` cache rows; bar 2e-3 of the largest output."""
@@ -46,7 +56,8 @@ def test_prefill_on_reference_fixture_fills(cuda_ops, oracle, H_q, H_kv, seq):
     k = ((((j * 6271 + 5003) % 2000).astype(np.float32) * np.float32(0.001)) - np.float32(1.0)).astype(np.float16)
     v = ((((j * 4931 + 7919) % 2000).astype(np.float32) * np.float32(0.002)) - np.float32(2.0)).astype(np.float16)
     qg = np.tile(qg1.reshape(1, 1, H_q, 2 * d), (1, seq, 1, 1))
-    got = _run(cuda_ops, qg, k.reshape(1, seq, H_kv, d), v.reshape(1, seq, H_kv, d), 1, seq, H_q, H_kv)[0, seq - 1]
+    got = _run(cuda_ops, qg, k.reshape(1, seq, H_kv, d), v.reshape(1, seq, H_kv, d), 1, seq, H_q, H_kv,
+               kernel=kernel)[0, seq - 1]
     want = oracle.gqa_attention_f32(qg1.astype(np.float32), k.astype(np.float32), v.astype(np.float32), seq, H_q, H_kv,
                                     d, 1.0 / np.sqrt(d))
     rel = np.abs(got - want).max() / (np.abs(want).max() + 1e-12)
@@ -55,6 +66,8 @@ def test_prefill_on_reference_fixture_fills(cuda_ops, oracle, H_q, H_kv, seq):
 
 def test_prefill_error_codes(cuda_ops):
     lib = cuda_ops.lib
-    assert lib.launch_khq_gqa_prefill_fp16(0, 0, 0, 0, 0, 8, 24, 4, 256, 0.0625, 0, 0, 0, 0) == -100
-    assert lib.launch_khq_gqa_prefill_fp16(0, 0, 0, 0, 1, 8, 24, 4, 128, 0.0625, 0, 0, 0, 0) == -103
-    assert lib.launch_khq_gqa_prefill_fp16(8, 0, 0, 0, 1, 8, 24, 4, 256, 0.0625, 0, 0, 0, 0) == -104
+    for fn in (lib.launch_khq_gqa_prefill_fp16, lib.launch_khq_gqa_prefill_tc5_fp16, lib.launch_khq_gqa_prefill_mma_fp16):
+        assert fn(0, 0, 0, 0, 0, 8, 24, 4, 256, 0.0625, 0, 0, 0, 0) == -100
+        assert fn(0, 0, 0, 0, 1, 8, 24, 4, 128, 0.0625, 0, 0, 0, 0) == -103
+        assert fn(8, 0, 0, 0, 1, 8, 24, 4, 256, 0.0625, 0, 0, 0, 0) == -104
+    assert lib.khq_b200_prefill_select(2) == -100
