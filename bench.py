@@ -51,7 +51,11 @@ def parse():
     ap.add_argument("--layers", type=int, default=N_LAYERS)
     ap.add_argument("--cpu-sample-mult", type=int, default=4, help="CPU sample = mult x host threads sequences")
     ap.add_argument("--no-extras", action="store_true")
-    ap.add_argument("--workload", default="batched", choices=["batched", "long"],
+    ap.add_argument("--prefill-batch", type=int, default=4, help="prompts per GPU (--workload prefill)")
+    ap.add_argument("--prefill-len", type=int, default=8192, help="prompt length (--workload prefill)")
+    ap.add_argument("--prefill-kernel", default="tc5", choices=["tc5", "mma"],
+                    help="tc5: tcgen05 / tensor-memory kernel; mma: warp-level mma.sync kernel")
+    ap.add_argument("--workload", default="batched", choices=["batched", "long", "prefill"],
                     help="batched = BASELINE configs[3] (default); long = configs[2], one 131072-token sequence "
                          "split by context range over the ranks")
     ap.add_argument("--long-ctx", type=int, default=131072)
@@ -336,6 +340,78 @@ def run_long(args, rank, world, local_rank):
     dist.destroy_process_group()
 
 
+def run_prefill(args, rank, world, local_rank):
+    """Causal GQA prefill attention + sigmoid gate of --prefill-batch prompts of --prefill-len
+    tokens per GPU (sharded by prompt, no collective).  Value: prompt tokens per second through one
+    attention layer; roofline: causal-attention FLOPs (4 * d * H_q * T(T+1)/2 per prompt) against
+    the measured dense bf16 GEMM burst peak."""
+    import torch
+    import torch.distributed as dist
+
+    from bonsai_mojo_1bit_optimization_t4_cuda_b200 import lib as khqlib
+    from bonsai_mojo_1bit_optimization_t4_cuda_b200.ops import CudaOps
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    ops = CudaOps()
+    lib = khqlib.load()
+    assert lib.khq_b200_prefill_select(0 if args.prefill_kernel == "tc5" else 1) == 0
+    B, T = args.prefill_batch, args.prefill_len
+    g = torch.Generator(device=dev).manual_seed(20260914 + 3000 + rank)
+    qg = torch.randn(B, T, 24, 512, generator=g, device=dev).half()
+    k = (torch.randn(B, T, 4, 256, generator=g, device=dev) * 0.25).half()
+    v = torch.randn(B, T, 4, 256, generator=g, device=dev).half()
+    out = torch.zeros(B, T, 24, 256, device=dev, dtype=torch.float16)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # larger than the 126 MB L2
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        ops.gqa_prefill(qg, k, v, out, B, T, 24, 4, 256, 1.0 / 16.0)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for e0, e1 in evs:
+        flush.fill_(1)
+        e0.record()
+        ops.gqa_prefill(qg, k, v, out, B, T, 24, 4, 256, 1.0 / 16.0)
+        e1.record()
+    barrier()
+    clocks = sampler.stop()
+    ms = sum(e0.elapsed_time(e1) for e0, e1 in evs) / args.steps
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t[0])
+    status = lib.khq_b200_prefill_status()
+    if rank == 0:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+        peak = float(peaks.get("bf16_tflops", 1590.0))
+        flops = 4.0 * 256 * 24 * (T * (T + 1) / 2.0) * B
+        ach = flops / (ms * 1e-3) / 1e12
+        print(json.dumps({
+            "metric": "causal GQA prefill attention throughput", "value": B * T * world / (ms * 1e-3), "unit": "prompt tok/s/layer",
+            "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
+            "config": {"workload": "causal GQA prefill attention + gate, %d prompts x %d tokens per GPU, H_q 24 / H_kv 4 / "
+                                   "d 256, kernel %s" % (B, T, args.prefill_kernel),
+                       "l2": "a 256 MB buffer is rewritten between timed launches", "world": world},
+            "roofline": {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
+                         "traffic": None, "algorithmic_flops_per_launch": flops,
+                         "peak_source": "MEASURED_PEAKS.json bf16_tflops (burst)" if peaks else "fallback"},
+            "gpu_launches": args.steps, "clocks": clocks, "device_status": status}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     args = parse()
     rank = int(os.environ.get("RANK", "0"))
@@ -346,6 +422,9 @@ def main():
         return
     if args.workload == "long":
         run_long(args, rank, world, local_rank)
+        return
+    if args.workload == "prefill":
+        run_prefill(args, rank, world, local_rank)
         return
 
     import torch

@@ -5,23 +5,27 @@
 // fp16-KV attention, src/kernels/elementwise_sm75.mojo:1140-1231, applied to all prompt rows at
 // once): out[t,h,:] = softmax_{u<=t}(q[t,h].K[u,h/6]*scale) V[u,h/6] * sigmoid(gate[t,h,:]).
 //
-// One CTA = 128 query rows of one query head; key tiles of 64.  Six warps, three roles:
+// One CTA = 128 query rows of one query head; key tiles of 64.  Seven warps, three roles:
 //   warps 0-3  softmax: thread i owns query row i -- its S row and its O row are tensor-memory
 //              lane i, so row max / row sum need no shuffles.  Reads S (64 fp32 columns) with
 //              tcgen05.ld, writes P (fp16) to shared memory, rescales O lazily (only when the
 //              running max grew by more than 2^8), and runs the epilogue.
-//   warp 4     producer: one thread issues the TMA loads of Q and of the K/V tiles (2 stages).
+//   warps 4, 6 producers: one thread each issues the TMA loads of Q and the K tiles (warp 4) and of
+//              the V tiles (warp 6), two stages each; a K stage is released as soon as its
+//              Q K^T has completed, a V stage when its P V has.
 //   warp 5     MMA: one thread issues S = Q K^T (M128 N64 K256) for tile j+1, then O += P V
 //              (M128 N256 K64) for tile j; tcgen05.commit signals the mbarriers.
 // Tensor memory columns: S ping [0,64), S pong [64,128), O [256,512).
 //
-// Shared-memory operand layout: no swizzle, 8x8 "core matrices" of 128 contiguous bytes.  A
-// 5-D tensor map {8 halfs, row, 16-byte chunk, head, batch} makes TMA write a (rows x 256) tile
-// as [chunk][row][8 halfs] = chunk*rows*16 + row*16 bytes, which is that layout with
-//   K-major  (Q, K, P): leading-dim byte offset (between 8-element K groups)  = rows*16,
-//                       stride-dim byte offset (between 8-row groups)         = 128;
-//   MN-major (V as the B operand of P V, keys are the contraction dim):
-//                       leading (between 8-key groups) = 128, stride (between 8-dim groups) = rows*16.
+// Shared-memory operand layout: the 128-byte-swizzle canonical layouts.  A 5-D tensor map
+// {64 halfs, row, 64-column group, head, batch} with 128-byte swizzle makes TMA write a
+// (rows x 256) tile as four sub-tiles [group][row][128 bytes], 16-byte chunk c of row r at
+// r*128 + ((c ^ (r & 7)) << 4).  Descriptors over it:
+//   K-major  (Q, K, P): stride-dim byte offset (between 8-row groups) = 1024; a K step of 16 halfs
+//                       advances the start address by 32 bytes inside a group, then to the next group;
+//   MN-major (V as the B operand of P V, keys are the contraction dim): leading-dim byte offset
+//                       (between 64-column groups) = rows*128, stride-dim byte offset (between 8-key
+//                       groups) = 1024; a K step of 16 keys advances the start address by 2048 bytes.
 // Every wait is bounded; a wait that runs out sets a status word the host can read and the CTA
 // falls through to the teardown (tensor memory is always released).
 #include <cuda.h>
@@ -38,7 +42,7 @@ using khq::smem_u32;
 constexpr int D = 256;
 constexpr int BR = 128;  // query rows per CTA
 constexpr int BC = 64;   // keys per tile
-constexpr int NTHREADS = 192;
+constexpr int NTHREADS = 224;
 constexpr int Q_BYTES = BR * D * 2;   // 64 KB
 constexpr int KV_BYTES = BC * D * 2;  // 32 KB
 constexpr int P_BYTES = BR * BC * 2;  // 16 KB
@@ -53,16 +57,16 @@ constexpr int SMEM_BYTES = OFF_BARS + 256;
 constexpr uint32_t TM_COLS = 512, TM_S = 0, TM_O = 256;
 constexpr float RESCALE_LOG2 = 8.0f;
 
-enum Bar { B_QFULL = 0, B_KFULL = 1, B_VFULL = 3, B_EMPTY = 5, B_SFULL = 7, B_PREADY = 9, B_PVDONE = 10, B_COUNT = 11 };
+enum Bar { B_QFULL = 0, B_KFULL = 1, B_VFULL = 3, B_KEMPTY = 5, B_SFULL = 7, B_PREADY = 9, B_PVDONE = 10, B_VEMPTY = 11, B_COUNT = 13 };
 
 __device__ int g_prefill_status = 0;
 
 // ---- descriptors ---------------------------------------------------------------------------------
-// Shared-memory matrix descriptor, no swizzle: start address, leading and stride byte offsets
-// (all in 16-byte units), descriptor version 1 in bits 46-47.
+// Shared-memory matrix descriptor: start address, leading and stride byte offsets (all in 16-byte
+// units), descriptor version 1 in bits 46-47, layout type 2 (128-byte swizzle) in bits 61-63.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
     return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)((lbo >> 4) & 0x3FFFu) << 16) |
-           ((uint64_t)((sbo >> 4) & 0x3FFFu) << 32) | ((uint64_t)1 << 46);
+           ((uint64_t)((sbo >> 4) & 0x3FFFu) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 // Instruction descriptor for kind::f16: fp32 accumulate, fp16 A and B, A K-major, M = 128.
 __host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
@@ -97,6 +101,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile(
@@ -111,7 +120,7 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// One 5-D tiled TMA load (no multicast); coordinate 0 is always 0, so the 16-byte rule holds.
+// One 5-D tiled TMA load of a single CTA; coordinate 0 is always 0, so the 16-byte rule holds.
 __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int c1, int c3,
                                             int c4) {
     asm volatile(
@@ -139,13 +148,18 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
     const int q0 = qb * BR;
     const int n_tiles = min((T + BC - 1) / BC, (q0 + BR) / BC);
     int* status = &g_prefill_status;
+    if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled layouts need a 1024-byte aligned base
+        if (tid == 0) atomicExch(status, 2);
+        return;
+    }
 
     if (tid == 0) {
         khq::mbar_init(&bars[B_QFULL], 1);
         for (int s = 0; s < 2; ++s) {
             khq::mbar_init(&bars[B_KFULL + s], 1);
             khq::mbar_init(&bars[B_VFULL + s], 1);
-            khq::mbar_init(&bars[B_EMPTY + s], 1);
+            khq::mbar_init(&bars[B_KEMPTY + s], 1);
+            khq::mbar_init(&bars[B_VEMPTY + s], 1);
             khq::mbar_init(&bars[B_SFULL + s], 1);
         }
         khq::mbar_init(&bars[B_PREADY], 128);
@@ -165,26 +179,38 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
     const uint32_t sbase = smem_u32(smem);
 
     if (warp == 4) {
-        // ================================ producer ================================================
+        // ================================ producer of Q and K ======================================
+        // A K stage is free again as soon as Q K^T of its tile has completed.
         if (lane == 0) {
             khq::mbar_arrive_expect_tx(&bars[B_QFULL], Q_BYTES);
             tma_load_5d(sbase + OFF_Q, &tm_q, &bars[B_QFULL], q0, h, b);
             int issued = 0;
             for (int j = 0; j < n_tiles; ++j) {
                 const int s = j & 1;
-                if (j >= 2 && !khq::mbar_wait_bounded(&bars[B_EMPTY + s], (uint32_t)(((j >> 1) - 1) & 1), status)) break;
+                if (j >= 2 && !khq::mbar_wait_bounded(&bars[B_KEMPTY + s], (uint32_t)(((j >> 1) - 1) & 1), status)) break;
                 khq::mbar_arrive_expect_tx(&bars[B_KFULL + s], KV_BYTES);
                 tma_load_5d(sbase + (s ? OFF_K1 : OFF_K0), &tm_k, &bars[B_KFULL + s], j * BC, kvh, b);
-                khq::mbar_arrive_expect_tx(&bars[B_VFULL + s], KV_BYTES);
-                tma_load_5d(sbase + (s ? OFF_V1 : OFF_V0), &tm_v, &bars[B_VFULL + s], j * BC, kvh, b);
                 issued = j + 1;
             }
             // nothing this thread started may still be in flight when the CTA leaves
             khq::mbar_wait_bounded(&bars[B_QFULL], 0u, status);
-            for (int j = max(0, issued - 2); j < issued; ++j) {
+            for (int j = max(0, issued - 2); j < issued; ++j)
                 khq::mbar_wait_bounded(&bars[B_KFULL + (j & 1)], (uint32_t)((j >> 1) & 1), status);
-                khq::mbar_wait_bounded(&bars[B_VFULL + (j & 1)], (uint32_t)((j >> 1) & 1), status);
+        }
+    } else if (warp == 6) {
+        // ================================ producer of V ============================================
+        // A V stage is free again once P V of its tile has completed.
+        if (lane == 0) {
+            int issued = 0;
+            for (int j = 0; j < n_tiles; ++j) {
+                const int s = j & 1;
+                if (j >= 2 && !khq::mbar_wait_bounded(&bars[B_VEMPTY + s], (uint32_t)(((j >> 1) - 1) & 1), status)) break;
+                khq::mbar_arrive_expect_tx(&bars[B_VFULL + s], KV_BYTES);
+                tma_load_5d(sbase + (s ? OFF_V1 : OFF_V0), &tm_v, &bars[B_VFULL + s], j * BC, kvh, b);
+                issued = j + 1;
             }
+            for (int j = max(0, issued - 2); j < issued; ++j)
+                khq::mbar_wait_bounded(&bars[B_VFULL + (j & 1)], (uint32_t)((j >> 1) & 1), status);
         }
     } else if (warp == 5) {
         // ================================ MMA issuer ==============================================
@@ -195,11 +221,12 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 const uint32_t kaddr = sbase + ((j & 1) ? OFF_K1 : OFF_K0);
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint64_t da = smem_desc(sbase + OFF_Q + ks * 2 * (BR * 16), BR * 16, 128);
-                    const uint64_t db = smem_desc(kaddr + ks * 2 * (BC * 16), BC * 16, 128);
+                    const uint64_t da = smem_desc(sbase + OFF_Q + (ks >> 2) * (BR * 128) + (ks & 3) * 32, 16, 1024);
+                    const uint64_t db = smem_desc(kaddr + (ks >> 2) * (BC * 128) + (ks & 3) * 32, 16, 1024);
                     umma_f16(tmem + TM_S + (uint32_t)(j & 1) * BC, da, db, IDESC_S, ks > 0 ? 1u : 0u);
                 }
                 umma_commit(&bars[B_SFULL + (j & 1)]);
+                umma_commit(&bars[B_KEMPTY + (j & 1)]);
             };
             bool ok = khq::mbar_wait_bounded(&bars[B_QFULL], 0u, status) &&
                       khq::mbar_wait_bounded(&bars[B_KFULL], 0u, status);
@@ -221,12 +248,12 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 const uint32_t vaddr = sbase + ((j & 1) ? OFF_V1 : OFF_V0);
 #pragma unroll
                 for (int ks = 0; ks < BC / 16; ++ks) {
-                    const uint64_t da = smem_desc(sbase + OFF_P + ks * 2 * (BR * 16), BR * 16, 128);
-                    const uint64_t db = smem_desc(vaddr + ks * 2 * 128, 128, BC * 16);
+                    const uint64_t da = smem_desc(sbase + OFF_P + ks * 32, 16, 1024);
+                    const uint64_t db = smem_desc(vaddr + ks * 2048, BC * 128, 1024);
                     umma_f16(tmem + TM_O, da, db, IDESC_O, (j > 0 || ks > 0) ? 1u : 0u);
                 }
                 umma_commit(&bars[B_PVDONE]);
-                umma_commit(&bars[B_EMPTY + (j & 1)]);
+                umma_commit(&bars[B_VEMPTY + (j & 1)]);
             }
         }
     } else {
@@ -244,15 +271,16 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
             tmem_ld32(lane_base + TM_S + (uint32_t)(j & 1) * BC + 32, sr[1]);
             tmem_ld_wait();
             const int k0 = j * BC;
-            const bool need_mask = (k0 + BC - 1 > q0) || (k0 + BC > T);
-            float mx = -1e30f;
+            // raw scores; masked entries (key after the row, or past the prompt) become -inf-like
+            if ((k0 + BC - 1 > q0) || (k0 + BC > T)) {
 #pragma unroll
-            for (int c = 0; c < BC; ++c) {
-                float x = __uint_as_float(sr[c >> 5][c & 31]) * scale_log2e;
-                if (need_mask && (k0 + c > row || k0 + c >= T)) x = -1e30f;
-                sr[c >> 5][c & 31] = __float_as_uint(x);
-                mx = fmaxf(mx, x);
+                for (int c = 0; c < BC; ++c)
+                    if (k0 + c > row || k0 + c >= T) sr[c >> 5][c & 31] = __float_as_uint(-1e30f);
             }
+            float mx4[4] = {-1e30f, -1e30f, -1e30f, -1e30f};
+#pragma unroll
+            for (int c = 0; c < BC; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c >> 5][c & 31]));
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2e;  // scale > 0
             float factor = 1.0f;
             bool grow = false;
             if (j == 0) {
@@ -262,16 +290,19 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 m_used = mx;
                 grow = true;
             }
-            float rs = 0.0f;
+            // p = 2^(s*scale - m): one fused multiply-add and one ex2 per score
+            float rs4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             uint32_t pk[BC / 2];
+            const float neg_m = -m_used;
 #pragma unroll
             for (int c = 0; c < BC; c += 2) {
-                const float p0 = exp2f(__uint_as_float(sr[c >> 5][c & 31]) - m_used);
-                const float p1 = exp2f(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]) - m_used);
-                rs += p0 + p1;
+                const float p0 = ex2_approx(fmaf(__uint_as_float(sr[c >> 5][c & 31]), scale_log2e, neg_m));
+                const float p1 = ex2_approx(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), scale_log2e, neg_m));
+                rs4[(c >> 1) & 3] += p0 + p1;
                 const __half2 hh = __floats2half2_rn(p0, p1);
                 pk[c >> 1] = *reinterpret_cast<const uint32_t*>(&hh);
             }
+            const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
             l_run = l_run * factor + rs;
             if (j > 0) {
                 // P's buffer and the O accumulator are free once P V of the previous tile is done
@@ -291,10 +322,10 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                     tmem_st_wait();
                 }
             }
-            // P row -> shared memory, K-major core-matrix layout: chunk c8 (8 keys) at c8*2048 + row*16
+            // P row -> shared memory, swizzled K-major: chunk c8 (8 keys) at row*128 + ((c8 ^ row%8) << 4)
 #pragma unroll
             for (int c8 = 0; c8 < BC / 8; ++c8) {
-                const uint32_t dst = sbase + OFF_P + c8 * (BR * 16) + tid * 16;
+                const uint32_t dst = sbase + OFF_P + tid * 128 + ((c8 ^ (tid & 7)) << 4);
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[c8 * 4]), "r"(pk[c8 * 4 + 1]),
                              "r"(pk[c8 * 4 + 2]), "r"(pk[c8 * 4 + 3])
                              : "memory");
@@ -371,20 +402,20 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 // Tensor map over a (batch, T, heads, row_halfs) fp16 tensor that exposes, per (head, batch), a
-// T x 256 matrix as {8 halfs, T rows, 32 chunks}; a box is `box_rows` rows of one head.
+// T x 256 matrix as {64 halfs, T rows, 4 column groups}; a box is `box_rows` rows of one head.
 int make_map(CUtensorMap* map, const void* base, int T, int heads, int batch, long long row_halfs,
              long long head_halfs, long long batch_halfs, int box_rows) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return -107;
     if (batch == 1) batch_halfs = (long long)T * row_halfs;
-    const cuuint64_t dims[5] = {8, (cuuint64_t)T, 32, (cuuint64_t)heads, (cuuint64_t)batch};
-    const cuuint64_t strides[4] = {(cuuint64_t)row_halfs * 2, 16, (cuuint64_t)head_halfs * 2, (cuuint64_t)batch_halfs * 2};
-    const cuuint32_t box[5] = {8, (cuuint32_t)box_rows, 32, 1, 1};
+    const cuuint64_t dims[5] = {64, (cuuint64_t)T, 4, (cuuint64_t)heads, (cuuint64_t)batch};
+    const cuuint64_t strides[4] = {(cuuint64_t)row_halfs * 2, 128, (cuuint64_t)head_halfs * 2, (cuuint64_t)batch_halfs * 2};
+    const cuuint32_t box[5] = {64, (cuuint32_t)box_rows, 4, 1, 1};
     const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     for (cuuint64_t st : strides)
         if (st % 16 != 0) return -104;
     const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(base), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : -108;
 }
@@ -427,7 +458,7 @@ extern "C" int launch_khq_gqa_prefill_tc5_fp16(const void* q_gate, const void* k
 }
 
 // Reads and clears the status word of the tcgen05 prefill kernel on the current device
-// (synchronises the device): 0 = clean, 1 = a bounded wait ran out.
+// (synchronises the device): 0 = clean, 1 = a bounded wait ran out, 2 = misaligned shared memory.
 extern "C" int khq_b200_prefill_status(void) {
     int st = 0;
     if (cudaMemcpyFromSymbol(&st, khq_prefill5::g_prefill_status, sizeof(int)) != cudaSuccess) return -1;
