@@ -1,31 +1,35 @@
 // khq_prefill_tc5.cu -- causal GQA prefill attention with sigmoid output gate on the fifth
-// generation tensor cores (tcgen05.mma, accumulators in tensor memory, operands staged by TMA).
+// generation tensor cores (tcgen05.mma, accumulators AND the A operands in tensor memory, the B
+// operands staged in shared memory by TMA).
 //
 // Same math and the same tensors as the warp-level kernel in khq_prefill.cu (the reference's
 // fp16-KV attention, src/kernels/elementwise_sm75.mojo:1140-1231, applied to all prompt rows at
 // once): out[t,h,:] = softmax_{u<=t}(q[t,h].K[u,h/6]*scale) V[u,h/6] * sigmoid(gate[t,h,:]).
 //
 // One CTA = 128 query rows of one query head; key tiles of 64.  Seven warps, three roles:
-//   warps 0-3  softmax: thread i owns query row i -- its S row and its O row are tensor-memory
-//              lane i, so row max / row sum need no shuffles.  Reads S (64 fp32 columns) with
-//              tcgen05.ld, writes P (fp16) to shared memory, rescales O lazily (only when the
-//              running max grew by more than 2^8), and runs the epilogue.
-//   warps 4, 6 producers: one thread each issues the TMA loads of Q and the K tiles (warp 4) and of
-//              the V tiles (warp 6), two stages each; a K stage is released as soon as its
+//   warps 0-3  softmax: thread i owns query row i -- its Q row, its S row and its O row are
+//              tensor-memory lane i, so row max / row sum need no shuffles.  Writes its Q row
+//              (fp16 pairs) into tensor memory once, then per tile reads S (64 fp32 columns) with
+//              tcgen05.ld and writes P (fp16 pairs, 32 columns) back over it with tcgen05.st;
+//              rescales O lazily (only when the running max grew by more than 2^8); epilogue.
+//   warps 4, 6 producers: one thread each issues the TMA loads of the K tiles (warp 4) and of
+//              the V tiles (warp 6), three stages each; a K stage is released as soon as its
 //              Q K^T has completed, a V stage when its P V has.
-//   warp 5     MMA: one thread issues S = Q K^T (M128 N64 K256) for tile j+1, then O += P V
-//              (M128 N256 K64) for tile j; tcgen05.commit signals the mbarriers.
-// Tensor memory columns: S ping [0,64), S pong [64,128), O [256,512).
+//   warp 5     MMA: one thread issues S = Q K^T (M128 N64 K256, A = Q from tensor memory) for
+//              tile j+1, then O += P V (M128 N256 K64, A = P from tensor memory) for tile j;
+//              tcgen05.commit signals the mbarriers.
+// Tensor memory columns: O [0,256), S/P ping [256,320), S/P pong [320,384), Q [384,512).  An A
+// operand in tensor memory is row = lane, 16 consecutive K elements = 8 columns of fp16 pairs.
 //
 // Shared-memory operand layout: the 128-byte-swizzle canonical layouts.  A 5-D tensor map
 // {64 halfs, row, 64-column group, head, batch} with 128-byte swizzle makes TMA write a
-// (rows x 256) tile as four sub-tiles [group][row][128 bytes], 16-byte chunk c of row r at
+// (64 x 256) tile as four sub-tiles [group][row][128 bytes], 16-byte chunk c of row r at
 // r*128 + ((c ^ (r & 7)) << 4).  Descriptors over it:
-//   K-major  (Q, K, P): stride-dim byte offset (between 8-row groups) = 1024; a K step of 16 halfs
-//                       advances the start address by 32 bytes inside a group, then to the next group;
+//   K-major  (K): stride-dim byte offset (between 8-row groups) = 1024; a K step of 16 halfs
+//                 advances the start address by 32 bytes inside a group, then to the next group;
 //   MN-major (V as the B operand of P V, keys are the contraction dim): leading-dim byte offset
-//                       (between 64-column groups) = rows*128, stride-dim byte offset (between 8-key
-//                       groups) = 1024; a K step of 16 keys advances the start address by 2048 bytes.
+//                 (between 64-column groups) = 64*128, stride-dim byte offset (between 8-key
+//                 groups) = 1024; a K step of 16 keys advances the start address by 2048 bytes.
 // Every wait is bounded; a wait that runs out sets a status word the host can read and the CTA
 // falls through to the teardown (tensor memory is always released).
 #include <cuda.h>
@@ -42,22 +46,21 @@ using khq::smem_u32;
 constexpr int D = 256;
 constexpr int BR = 128;  // query rows per CTA
 constexpr int BC = 64;   // keys per tile
+constexpr int NS = 3;    // K stages and V stages
 constexpr int NTHREADS = 224;
-constexpr int Q_BYTES = BR * D * 2;   // 64 KB
 constexpr int KV_BYTES = BC * D * 2;  // 32 KB
-constexpr int P_BYTES = BR * BC * 2;  // 16 KB
-constexpr int OFF_Q = 0;
-constexpr int OFF_K0 = OFF_Q + Q_BYTES;
-constexpr int OFF_V0 = OFF_K0 + KV_BYTES;
-constexpr int OFF_K1 = OFF_V0 + KV_BYTES;
-constexpr int OFF_V1 = OFF_K1 + KV_BYTES;
-constexpr int OFF_P = OFF_V1 + KV_BYTES;
-constexpr int OFF_BARS = OFF_P + P_BYTES;
+constexpr int OFF_K = 0;
+constexpr int OFF_V = OFF_K + NS * KV_BYTES;
+constexpr int OFF_BARS = OFF_V + NS * KV_BYTES;
 constexpr int SMEM_BYTES = OFF_BARS + 256;
-constexpr uint32_t TM_COLS = 512, TM_S = 0, TM_O = 256;
+constexpr uint32_t TM_COLS = 512, TM_O = 0, TM_S = 256, TM_Q = 384;
 constexpr float RESCALE_LOG2 = 8.0f;
 
-enum Bar { B_QFULL = 0, B_KFULL = 1, B_VFULL = 3, B_KEMPTY = 5, B_SFULL = 7, B_PREADY = 9, B_PVDONE = 10, B_VEMPTY = 11, B_COUNT = 13 };
+enum Bar {
+    B_KFULL = 0, B_VFULL = NS, B_KEMPTY = 2 * NS, B_VEMPTY = 3 * NS, B_SFULL = 4 * NS, B_QREADY = 4 * NS + 2,
+    B_PREADY = 4 * NS + 3, B_PVDONE = 4 * NS + 4, B_COUNT = 4 * NS + 5
+};
+static_assert(B_COUNT * 8 <= 192, "barriers overlap the tensor-memory slot");
 
 __device__ int g_prefill_status = 0;
 
@@ -80,6 +83,15 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
         "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Same with the A operand in tensor memory (row = lane, fp16 pairs, 8 columns per K step of 16).
+__device__ __forceinline__ void umma_f16_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
@@ -134,13 +146,12 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map
 // grid = (ceil(T/128), H_q, batch).  q_gate (B, T, H_q, 2D), out (B, T, H_q, D); K and V only
 // through their tensor maps.
 __global__ void __launch_bounds__(NTHREADS, 1)
-khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                           const __grid_constant__ CUtensorMap tm_v, const __half* __restrict__ q_gate,
-                           __half* __restrict__ out, int T, int H_q, int H_kv, float scale_log2e, long long q_bs,
-                           long long o_bs) {
+khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                           const __half* __restrict__ q_gate, __half* __restrict__ out, int T, int H_q, int H_kv,
+                           float scale_log2e, long long q_bs, long long o_bs) {
     extern __shared__ __align__(1024) unsigned char smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BARS);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_BARS + 128);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_BARS + 192);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;  // heaviest row blocks first
     const int h = blockIdx.y, b = blockIdx.z;
@@ -154,14 +165,15 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
     }
 
     if (tid == 0) {
-        khq::mbar_init(&bars[B_QFULL], 1);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < NS; ++s) {
             khq::mbar_init(&bars[B_KFULL + s], 1);
             khq::mbar_init(&bars[B_VFULL + s], 1);
             khq::mbar_init(&bars[B_KEMPTY + s], 1);
             khq::mbar_init(&bars[B_VEMPTY + s], 1);
-            khq::mbar_init(&bars[B_SFULL + s], 1);
         }
+        khq::mbar_init(&bars[B_SFULL], 1);
+        khq::mbar_init(&bars[B_SFULL + 1], 1);
+        khq::mbar_init(&bars[B_QREADY], 128);
         khq::mbar_init(&bars[B_PREADY], 128);
         khq::mbar_init(&bars[B_PVDONE], 1);
         khq::fence_barrier_init();
@@ -178,39 +190,27 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
     const uint32_t tmem = *tmem_slot;
     const uint32_t sbase = smem_u32(smem);
 
-    if (warp == 4) {
-        // ================================ producer of Q and K ======================================
-        // A K stage is free again as soon as Q K^T of its tile has completed.
+    if (warp == 4 || warp == 6) {
+        // ================================ producers ================================================
+        // warp 4 streams the K tiles (a stage is free once Q K^T of its tile has completed), warp 6
+        // the V tiles (free once P V of its tile has completed).
         if (lane == 0) {
-            khq::mbar_arrive_expect_tx(&bars[B_QFULL], Q_BYTES);
-            tma_load_5d(sbase + OFF_Q, &tm_q, &bars[B_QFULL], q0, h, b);
+            const bool is_k = (warp == 4);
+            const CUtensorMap* map = is_k ? &tm_k : &tm_v;
+            uint64_t* full = &bars[is_k ? B_KFULL : B_VFULL];
+            uint64_t* empty = &bars[is_k ? B_KEMPTY : B_VEMPTY];
+            const uint32_t base = sbase + (is_k ? OFF_K : OFF_V);
             int issued = 0;
             for (int j = 0; j < n_tiles; ++j) {
-                const int s = j & 1;
-                if (j >= 2 && !khq::mbar_wait_bounded(&bars[B_KEMPTY + s], (uint32_t)(((j >> 1) - 1) & 1), status)) break;
-                khq::mbar_arrive_expect_tx(&bars[B_KFULL + s], KV_BYTES);
-                tma_load_5d(sbase + (s ? OFF_K1 : OFF_K0), &tm_k, &bars[B_KFULL + s], j * BC, kvh, b);
+                const int s = j % NS;
+                if (j >= NS && !khq::mbar_wait_bounded(&empty[s], (uint32_t)((j / NS - 1) & 1), status)) break;
+                khq::mbar_arrive_expect_tx(&full[s], KV_BYTES);
+                tma_load_5d(base + s * KV_BYTES, map, &full[s], j * BC, kvh, b);
                 issued = j + 1;
             }
             // nothing this thread started may still be in flight when the CTA leaves
-            khq::mbar_wait_bounded(&bars[B_QFULL], 0u, status);
-            for (int j = max(0, issued - 2); j < issued; ++j)
-                khq::mbar_wait_bounded(&bars[B_KFULL + (j & 1)], (uint32_t)((j >> 1) & 1), status);
-        }
-    } else if (warp == 6) {
-        // ================================ producer of V ============================================
-        // A V stage is free again once P V of its tile has completed.
-        if (lane == 0) {
-            int issued = 0;
-            for (int j = 0; j < n_tiles; ++j) {
-                const int s = j & 1;
-                if (j >= 2 && !khq::mbar_wait_bounded(&bars[B_VEMPTY + s], (uint32_t)(((j >> 1) - 1) & 1), status)) break;
-                khq::mbar_arrive_expect_tx(&bars[B_VFULL + s], KV_BYTES);
-                tma_load_5d(sbase + (s ? OFF_V1 : OFF_V0), &tm_v, &bars[B_VFULL + s], j * BC, kvh, b);
-                issued = j + 1;
-            }
-            for (int j = max(0, issued - 2); j < issued; ++j)
-                khq::mbar_wait_bounded(&bars[B_VFULL + (j & 1)], (uint32_t)((j >> 1) & 1), status);
+            for (int j = max(0, issued - NS); j < issued; ++j)
+                khq::mbar_wait_bounded(&full[j % NS], (uint32_t)((j / NS) & 1), status);
         }
     } else if (warp == 5) {
         // ================================ MMA issuer ==============================================
@@ -218,17 +218,16 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
             constexpr uint32_t IDESC_S = instr_desc(BC, false);
             constexpr uint32_t IDESC_O = instr_desc(D, true);
             auto issue_qk = [&](int j) {
-                const uint32_t kaddr = sbase + ((j & 1) ? OFF_K1 : OFF_K0);
+                const uint32_t kaddr = sbase + OFF_K + (j % NS) * KV_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint64_t da = smem_desc(sbase + OFF_Q + (ks >> 2) * (BR * 128) + (ks & 3) * 32, 16, 1024);
                     const uint64_t db = smem_desc(kaddr + (ks >> 2) * (BC * 128) + (ks & 3) * 32, 16, 1024);
-                    umma_f16(tmem + TM_S + (uint32_t)(j & 1) * BC, da, db, IDESC_S, ks > 0 ? 1u : 0u);
+                    umma_f16_ta(tmem + TM_S + (uint32_t)(j & 1) * BC, tmem + TM_Q + ks * 8, db, IDESC_S, ks > 0 ? 1u : 0u);
                 }
                 umma_commit(&bars[B_SFULL + (j & 1)]);
-                umma_commit(&bars[B_KEMPTY + (j & 1)]);
+                umma_commit(&bars[B_KEMPTY + (j % NS)]);
             };
-            bool ok = khq::mbar_wait_bounded(&bars[B_QFULL], 0u, status) &&
+            bool ok = khq::mbar_wait_bounded(&bars[B_QREADY], 0u, status) &&
                       khq::mbar_wait_bounded(&bars[B_KFULL], 0u, status);
             if (ok) {
                 tc_fence_after();
@@ -236,39 +235,62 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
             }
             for (int j = 0; ok && j < n_tiles; ++j) {
                 if (j + 1 < n_tiles) {
-                    ok = khq::mbar_wait_bounded(&bars[B_KFULL + ((j + 1) & 1)], (uint32_t)(((j + 1) >> 1) & 1), status);
+                    ok = khq::mbar_wait_bounded(&bars[B_KFULL + (j + 1) % NS], (uint32_t)(((j + 1) / NS) & 1), status);
                     if (!ok) break;
                     tc_fence_after();
                     issue_qk(j + 1);
                 }
                 ok = khq::mbar_wait_bounded(&bars[B_PREADY], (uint32_t)(j & 1), status) &&
-                     khq::mbar_wait_bounded(&bars[B_VFULL + (j & 1)], (uint32_t)((j >> 1) & 1), status);
+                     khq::mbar_wait_bounded(&bars[B_VFULL + j % NS], (uint32_t)((j / NS) & 1), status);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t vaddr = sbase + ((j & 1) ? OFF_V1 : OFF_V0);
+                const uint32_t vaddr = sbase + OFF_V + (j % NS) * KV_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < BC / 16; ++ks) {
-                    const uint64_t da = smem_desc(sbase + OFF_P + ks * 32, 16, 1024);
                     const uint64_t db = smem_desc(vaddr + ks * 2048, BC * 128, 1024);
-                    umma_f16(tmem + TM_O, da, db, IDESC_O, (j > 0 || ks > 0) ? 1u : 0u);
+                    umma_f16_ta(tmem + TM_O, tmem + TM_S + (uint32_t)(j & 1) * BC + ks * 8, db, IDESC_O,
+                                (j > 0 || ks > 0) ? 1u : 0u);
                 }
                 umma_commit(&bars[B_PVDONE]);
-                umma_commit(&bars[B_VEMPTY + (j & 1)]);
+                umma_commit(&bars[B_VEMPTY + j % NS]);
             }
         }
     } else {
         // ================================ softmax + epilogue ======================================
         const int row = q0 + tid;
+        const bool live = row < T;
+        const long long q_row = (long long)H_q * 2 * D, o_row = (long long)H_q * D;
+        const __half* qrow = q_gate + b * q_bs + (long long)(live ? row : 0) * q_row + (long long)h * 2 * D;
         const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+        // ---- this thread's Q row -> tensor memory (rows past the prompt are zero) ---------------
+#pragma unroll 1
+        for (int c0 = 0; c0 < D / 2; c0 += 32) {
+            uint32_t qr[32];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                uint4 x = make_uint4(0u, 0u, 0u, 0u);
+                if (live) x = __ldg(reinterpret_cast<const uint4*>(qrow + c0 * 2) + i);
+                qr[4 * i] = x.x;
+                qr[4 * i + 1] = x.y;
+                qr[4 * i + 2] = x.z;
+                qr[4 * i + 3] = x.w;
+            }
+            tmem_st32(lane_base + TM_Q + c0, qr);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        khq::mbar_arrive(&bars[B_QREADY]);
+
         float m_used = -1e30f, l_run = 0.0f;
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
             ok = __all_sync(0xFFFFFFFFu, khq::mbar_wait_bounded(&bars[B_SFULL + (j & 1)], (uint32_t)((j >> 1) & 1), status));
             if (!ok) break;
             tc_fence_after();
+            const uint32_t s_addr = lane_base + TM_S + (uint32_t)(j & 1) * BC;
             uint32_t sr[2][32];
-            tmem_ld32(lane_base + TM_S + (uint32_t)(j & 1) * BC, sr[0]);
-            tmem_ld32(lane_base + TM_S + (uint32_t)(j & 1) * BC + 32, sr[1]);
+            tmem_ld32(s_addr, sr[0]);
+            tmem_ld32(s_addr + 32, sr[1]);
             tmem_ld_wait();
             const int k0 = j * BC;
             // raw scores; masked entries (key after the row, or past the prompt) become -inf-like
@@ -305,11 +327,13 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
             const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
             l_run = l_run * factor + rs;
             if (j > 0) {
-                // P's buffer and the O accumulator are free once P V of the previous tile is done
+                // Every thread follows every phase of this barrier (a parity wait can only tell two
+                // neighbouring phases apart).  P V of the previous tile has normally long completed.
                 ok = __all_sync(0xFFFFFFFFu, khq::mbar_wait_bounded(&bars[B_PVDONE], (uint32_t)((j - 1) & 1), status));
                 if (!ok) break;
-                tc_fence_after();
                 if (__any_sync(0xFFFFFFFFu, grow)) {
+                    // O may only be touched between P V of the previous tile and P V of this one
+                    tc_fence_after();
 #pragma unroll 1
                     for (int c0 = 0; c0 < D; c0 += 32) {
                         uint32_t orr[32];
@@ -319,18 +343,11 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                         for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * factor);
                         tmem_st32(lane_base + TM_O + c0, orr);
                     }
-                    tmem_st_wait();
                 }
             }
-            // P row -> shared memory, swizzled K-major: chunk c8 (8 keys) at row*128 + ((c8 ^ row%8) << 4)
-#pragma unroll
-            for (int c8 = 0; c8 < BC / 8; ++c8) {
-                const uint32_t dst = sbase + OFF_P + tid * 128 + ((c8 ^ (tid & 7)) << 4);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[c8 * 4]), "r"(pk[c8 * 4 + 1]),
-                             "r"(pk[c8 * 4 + 2]), "r"(pk[c8 * 4 + 3])
-                             : "memory");
-            }
-            khq::fence_proxy_async();
+            // P row (fp16 pairs) over the first 32 columns of the S buffer it came from
+            tmem_st32(s_addr, pk);
+            tmem_st_wait();
             tc_fence_before();
             khq::mbar_arrive(&bars[B_PREADY]);
         }
@@ -339,9 +356,7 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         if (ok) {
             tc_fence_after();
             const float inv = 1.0f / (l_run + 1e-9f);
-            const long long q_row = (long long)H_q * 2 * D, o_row = (long long)H_q * D;
-            const bool live = row < T;
-            const __half* gate = q_gate + b * q_bs + (long long)(live ? row : 0) * q_row + (long long)h * 2 * D + D;
+            const __half* gate = qrow + D;
             __half* op = out + b * o_bs + (long long)(live ? row : 0) * o_row + (long long)h * D;
 #pragma unroll 1
             for (int c0 = 0; c0 < D; c0 += 32) {
@@ -351,7 +366,7 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                 if (live) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
-                        const uint4 g4 = *reinterpret_cast<const uint4*>(gate + c0 + i);
+                        const uint4 g4 = __ldg(reinterpret_cast<const uint4*>(gate + c0 + i));
                         const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w};
                         uint32_t ow[4];
 #pragma unroll
@@ -435,9 +450,8 @@ extern "C" int launch_khq_gqa_prefill_tc5_fp16(const void* q_gate, const void* k
     for (const void* p : ptrs)
         if ((reinterpret_cast<uintptr_t>(p) & 15) != 0) return -104;
     if (batch > 1 && ((q_batch_stride | kv_batch_stride | out_batch_stride) & 7) != 0) return -104;
-    CUtensorMap mq, mk, mv;
-    int rc = make_map(&mq, q_gate, T, H_q, batch, (long long)H_q * 2 * D, 2 * D, q_batch_stride, BR);
-    if (rc == 0) rc = make_map(&mk, k, T, H_kv, batch, (long long)H_kv * D, D, kv_batch_stride, BC);
+    CUtensorMap mk, mv;
+    int rc = make_map(&mk, k, T, H_kv, batch, (long long)H_kv * D, D, kv_batch_stride, BC);
     if (rc == 0) rc = make_map(&mv, v, T, H_kv, batch, (long long)H_kv * D, D, kv_batch_stride, BC);
     if (rc != 0) return rc;
     static bool attr_done[64] = {};
@@ -451,7 +465,7 @@ extern "C" int launch_khq_gqa_prefill_tc5_fp16(const void* q_gate, const void* k
     }
     const dim3 grid((unsigned)((T + BR - 1) / BR), (unsigned)H_q, (unsigned)batch);
     khq_gqa_prefill_tc5_kernel<<<grid, NTHREADS, SMEM_BYTES, stream>>>(
-        mq, mk, mv, static_cast<const __half*>(q_gate), static_cast<__half*>(out), T, H_q, H_kv,
+        mk, mv, static_cast<const __half*>(q_gate), static_cast<__half*>(out), T, H_q, H_kv,
         scale * 1.4426950408889634f, q_batch_stride, out_batch_stride);
     err = cudaGetLastError();
     return (err == cudaSuccess) ? 0 : static_cast<int>(err);
