@@ -6,18 +6,25 @@
 // fp16-KV attention, src/kernels/elementwise_sm75.mojo:1140-1231, applied to all prompt rows at
 // once): out[t,h,:] = softmax_{u<=t}(q[t,h].K[u,h/6]*scale) V[u,h/6] * sigmoid(gate[t,h,:]).
 //
-// One CTA = 128 query rows of one query head; key tiles of 64.  Seven warps, three roles:
-//   warps 0-3  softmax: thread i owns query row i -- its Q row, its S row and its O row are
-//              tensor-memory lane i, so row max / row sum need no shuffles.  Writes its Q row
-//              (fp16 pairs) into tensor memory once, then per tile reads S (64 fp32 columns) with
-//              tcgen05.ld and writes P (fp16 pairs, 32 columns) back over it with tcgen05.st;
-//              rescales O lazily (only when the running max grew by more than 2^8); epilogue.
-//   warps 4, 6 producers: one thread each issues the TMA loads of the K tiles (warp 4) and of
-//              the V tiles (warp 6), three stages each; a K stage is released as soon as its
+// One CTA = 128 query rows of one query head; key tiles of 64.  Eleven warps, three roles:
+//   warps 0-7  softmax, two threads per query row (warp w and warp w+4 share the tensor-memory
+//              lane quarter w%4 and a scheduler): a row's Q, S and O live in tensor-memory lane
+//              i, so there are no shuffles; the two threads of a row take 32 keys of a tile each
+//              and swap their half maxima (and, at the end, half sums) through shared memory.
+//              Each writes its half of the Q row (fp16 pairs) into tensor memory once, then per
+//              tile reads 32 S columns with tcgen05.ld and writes P (fp16 pairs, 16 columns) back
+//              over the S buffer with tcgen05.st; O is rescaled lazily (only when the running
+//              max grew by more than 2^8); the epilogue normalises, gates and stores.
+//   warps 8,10 producers: one thread each issues the TMA loads of the K tiles (warp 8) and of
+//              the V tiles (warp 10), three stages each; a K stage is released as soon as its
 //              Q K^T has completed, a V stage when its P V has.
-//   warp 5     MMA: one thread issues S = Q K^T (M128 N64 K256, A = Q from tensor memory) for
+//   warp 9     MMA: one thread issues S = Q K^T (M128 N64 K256, A = Q from tensor memory) for
 //              tile j+1, then O += P V (M128 N256 K64, A = P from tensor memory) for tile j;
 //              tcgen05.commit signals the mbarriers.
+// What bounds it: every CTA streams the whole K/V prefix of its rows from L2 (64 KB per 8.4 MFLOP
+// tile step, 128 FLOP per byte), and at ~0.93 PFLOP/s that is ~7.4 TB/s of L2 reads; emptying the
+// softmax does not shorten the kernel.  The next step up is a CTA pair (cta_group::2) that splits
+// each K/V tile between two SMs.
 // Tensor memory columns: O [0,256), S/P ping [256,320), S/P pong [320,384), Q [384,512).  An A
 // operand in tensor memory is row = lane, 16 consecutive K elements = 8 columns of fp16 pairs.
 //
@@ -47,18 +54,20 @@ constexpr int D = 256;
 constexpr int BR = 128;  // query rows per CTA
 constexpr int BC = 64;   // keys per tile
 constexpr int NS = 3;    // K stages and V stages
-constexpr int NTHREADS = 224;
+constexpr int NSOFT = 256;  // softmax threads: two per query row, 32 of a tile's 64 keys each
+constexpr int NTHREADS = NSOFT + 96;
 constexpr int KV_BYTES = BC * D * 2;  // 32 KB
 constexpr int OFF_K = 0;
 constexpr int OFF_V = OFF_K + NS * KV_BYTES;
-constexpr int OFF_BARS = OFF_V + NS * KV_BYTES;
+constexpr int OFF_XCHG = OFF_V + NS * KV_BYTES;  // float [2 parities][2 halves][128 rows]
+constexpr int OFF_BARS = OFF_XCHG + 2 * 2 * 128 * 4;
 constexpr int SMEM_BYTES = OFF_BARS + 256;
 constexpr uint32_t TM_COLS = 512, TM_O = 0, TM_S = 256, TM_Q = 384;
 constexpr float RESCALE_LOG2 = 8.0f;
 
 enum Bar {
     B_KFULL = 0, B_VFULL = NS, B_KEMPTY = 2 * NS, B_VEMPTY = 3 * NS, B_SFULL = 4 * NS, B_QREADY = 4 * NS + 2,
-    B_PREADY = 4 * NS + 3, B_PVDONE = 4 * NS + 4, B_COUNT = 4 * NS + 5
+    B_PREADY = 4 * NS + 3, B_PVDONE = 4 * NS + 4, B_XCHG = 4 * NS + 5, B_COUNT = 4 * NS + 6
 };
 static_assert(B_COUNT * 8 <= 192, "barriers overlap the tensor-memory slot");
 
@@ -113,6 +122,21 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15};" ::"r"(r[0]),
+        "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -152,6 +176,7 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
     extern __shared__ __align__(1024) unsigned char smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BARS);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_BARS + 192);
+    float* xchg = reinterpret_cast<float*>(smem + OFF_XCHG);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;  // heaviest row blocks first
     const int h = blockIdx.y, b = blockIdx.z;
@@ -173,12 +198,13 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
         }
         khq::mbar_init(&bars[B_SFULL], 1);
         khq::mbar_init(&bars[B_SFULL + 1], 1);
-        khq::mbar_init(&bars[B_QREADY], 128);
-        khq::mbar_init(&bars[B_PREADY], 128);
+        khq::mbar_init(&bars[B_QREADY], NSOFT);
+        khq::mbar_init(&bars[B_PREADY], NSOFT);
+        khq::mbar_init(&bars[B_XCHG], NSOFT);
         khq::mbar_init(&bars[B_PVDONE], 1);
         khq::fence_barrier_init();
     }
-    if (warp == 5) {
+    if (warp == 9) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
                      "n"(TM_COLS)
                      : "memory");
@@ -190,12 +216,12 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
     const uint32_t tmem = *tmem_slot;
     const uint32_t sbase = smem_u32(smem);
 
-    if (warp == 4 || warp == 6) {
+    if (warp == 8 || warp == 10) {
         // ================================ producers ================================================
-        // warp 4 streams the K tiles (a stage is free once Q K^T of its tile has completed), warp 6
+        // warp 8 streams the K tiles (a stage is free once Q K^T of its tile has completed), warp 10
         // the V tiles (free once P V of its tile has completed).
         if (lane == 0) {
-            const bool is_k = (warp == 4);
+            const bool is_k = (warp == 8);
             const CUtensorMap* map = is_k ? &tm_k : &tm_v;
             uint64_t* full = &bars[is_k ? B_KFULL : B_VFULL];
             uint64_t* empty = &bars[is_k ? B_KEMPTY : B_VEMPTY];
@@ -212,7 +238,7 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
             for (int j = max(0, issued - NS); j < issued; ++j)
                 khq::mbar_wait_bounded(&full[j % NS], (uint32_t)((j / NS) & 1), status);
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ================================ MMA issuer ==============================================
         if (lane == 0) {
             constexpr uint32_t IDESC_S = instr_desc(BC, false);
@@ -257,14 +283,18 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
         }
     } else {
         // ================================ softmax + epilogue ======================================
-        const int row = q0 + tid;
+        // Two threads per query row: half 0 (warps 0-3) takes keys 0-31 of a tile and columns 0-127
+        // of Q / O, half 1 (warps 4-7) keys 32-63 and columns 128-255.  Both warps of a row sit on
+        // the same tensor-memory lane quarter (warp % 4) and on the same scheduler.
+        const int half = warp >> 2, r = tid & 127;
+        const int row = q0 + r;
         const bool live = row < T;
         const long long q_row = (long long)H_q * 2 * D, o_row = (long long)H_q * D;
         const __half* qrow = q_gate + b * q_bs + (long long)(live ? row : 0) * q_row + (long long)h * 2 * D;
-        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-        // ---- this thread's Q row -> tensor memory (rows past the prompt are zero) ---------------
+        const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        // ---- this thread's half of the Q row -> tensor memory (rows past the prompt are zero) ----
 #pragma unroll 1
-        for (int c0 = 0; c0 < D / 2; c0 += 32) {
+        for (int c0 = half * 64; c0 < half * 64 + 64; c0 += 32) {
             uint32_t qr[32];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -288,21 +318,26 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
             if (!ok) break;
             tc_fence_after();
             const uint32_t s_addr = lane_base + TM_S + (uint32_t)(j & 1) * BC;
-            uint32_t sr[2][32];
-            tmem_ld32(s_addr, sr[0]);
-            tmem_ld32(s_addr + 32, sr[1]);
+            uint32_t sr[32];
+            tmem_ld32(s_addr + half * 32, sr);
             tmem_ld_wait();
-            const int k0 = j * BC;
+            const int k0 = j * BC + half * 32;
             // raw scores; masked entries (key after the row, or past the prompt) become -inf-like
-            if ((k0 + BC - 1 > q0) || (k0 + BC > T)) {
+            if ((k0 + 31 > q0) || (k0 + 32 > T)) {
 #pragma unroll
-                for (int c = 0; c < BC; ++c)
-                    if (k0 + c > row || k0 + c >= T) sr[c >> 5][c & 31] = __float_as_uint(-1e30f);
+                for (int c = 0; c < 32; ++c)
+                    if (k0 + c > row || k0 + c >= T) sr[c] = __float_as_uint(-1e30f);
             }
             float mx4[4] = {-1e30f, -1e30f, -1e30f, -1e30f};
 #pragma unroll
-            for (int c = 0; c < BC; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c >> 5][c & 31]));
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2e;  // scale > 0
+            for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c]));
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            // the row maximum over all 64 keys: swap half maxima with the partner thread
+            xchg[((j & 1) * 2 + half) * 128 + r] = mx;
+            khq::mbar_arrive(&bars[B_XCHG]);
+            ok = __all_sync(0xFFFFFFFFu, khq::mbar_wait_bounded(&bars[B_XCHG], (uint32_t)(j & 1), status));
+            if (!ok) break;
+            mx = fmaxf(mx, xchg[((j & 1) * 2 + (half ^ 1)) * 128 + r]) * scale_log2e;  // scale > 0
             float factor = 1.0f;
             bool grow = false;
             if (j == 0) {
@@ -314,12 +349,12 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
             }
             // p = 2^(s*scale - m): one fused multiply-add and one ex2 per score
             float rs4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            uint32_t pk[BC / 2];
+            uint32_t pk[16];
             const float neg_m = -m_used;
 #pragma unroll
-            for (int c = 0; c < BC; c += 2) {
-                const float p0 = ex2_approx(fmaf(__uint_as_float(sr[c >> 5][c & 31]), scale_log2e, neg_m));
-                const float p1 = ex2_approx(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), scale_log2e, neg_m));
+            for (int c = 0; c < 32; c += 2) {
+                const float p0 = ex2_approx(fmaf(__uint_as_float(sr[c]), scale_log2e, neg_m));
+                const float p1 = ex2_approx(fmaf(__uint_as_float(sr[c + 1]), scale_log2e, neg_m));
                 rs4[(c >> 1) & 3] += p0 + p1;
                 const __half2 hh = __floats2half2_rn(p0, p1);
                 pk[c >> 1] = *reinterpret_cast<const uint32_t*>(&hh);
@@ -335,7 +370,7 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
                     // O may only be touched between P V of the previous tile and P V of this one
                     tc_fence_after();
 #pragma unroll 1
-                    for (int c0 = 0; c0 < D; c0 += 32) {
+                    for (int c0 = half * 128; c0 < half * 128 + 128; c0 += 32) {
                         uint32_t orr[32];
                         tmem_ld32(lane_base + TM_O + c0, orr);
                         tmem_ld_wait();
@@ -345,11 +380,19 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
                     }
                 }
             }
-            // P row (fp16 pairs) over the first 32 columns of the S buffer it came from
-            tmem_st32(s_addr, pk);
+            // P (fp16 pairs) over the S buffer it came from: keys 32*half.. -> columns 16*half..
+            // (the partner has read its S columns: it passed the exchange barrier after its load)
+            tmem_st16(s_addr + half * 16, pk);
             tmem_st_wait();
             tc_fence_before();
             khq::mbar_arrive(&bars[B_PREADY]);
+        }
+        // row sum over both halves
+        if (ok) {
+            xchg[((n_tiles & 1) * 2 + half) * 128 + r] = l_run;
+            khq::mbar_arrive(&bars[B_XCHG]);
+            ok = khq::mbar_wait_bounded(&bars[B_XCHG], (uint32_t)(n_tiles & 1), status);
+            if (ok) l_run += xchg[((n_tiles & 1) * 2 + (half ^ 1)) * 128 + r];
         }
         if (ok) ok = khq::mbar_wait_bounded(&bars[B_PVDONE], (uint32_t)((n_tiles - 1) & 1), status);
         ok = __all_sync(0xFFFFFFFFu, ok);
@@ -359,7 +402,7 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
             const __half* gate = qrow + D;
             __half* op = out + b * o_bs + (long long)(live ? row : 0) * o_row + (long long)h * D;
 #pragma unroll 1
-            for (int c0 = 0; c0 < D; c0 += 32) {
+            for (int c0 = half * 128; c0 < half * 128 + 128; c0 += 32) {
                 uint32_t orr[32];
                 tmem_ld32(lane_base + TM_O + c0, orr);
                 tmem_ld_wait();
@@ -387,7 +430,7 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
     // ---- teardown: every thread arrives here, with or without a failed wait ----------------------
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 9) {
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(TM_COLS) : "memory");
     }
