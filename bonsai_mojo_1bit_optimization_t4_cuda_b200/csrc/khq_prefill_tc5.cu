@@ -67,7 +67,7 @@ constexpr float RESCALE_LOG2 = 8.0f;
 
 enum Bar {
     B_KFULL = 0, B_VFULL = NS, B_KEMPTY = 2 * NS, B_VEMPTY = 3 * NS, B_SFULL = 4 * NS, B_QREADY = 4 * NS + 2,
-    B_PREADY = 4 * NS + 3, B_PVDONE = 4 * NS + 4, B_XCHG = 4 * NS + 5, B_COUNT = 4 * NS + 6
+    B_PREADY = 4 * NS + 3, B_PVDONE = 4 * NS + 4, B_XCHG = 4 * NS + 6, B_COUNT = 4 * NS + 10
 };
 static_assert(B_COUNT * 8 <= 192, "barriers overlap the tensor-memory slot");
 
@@ -198,10 +198,12 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
         }
         khq::mbar_init(&bars[B_SFULL], 1);
         khq::mbar_init(&bars[B_SFULL + 1], 1);
-        khq::mbar_init(&bars[B_QREADY], NSOFT);
-        khq::mbar_init(&bars[B_PREADY], NSOFT);
-        khq::mbar_init(&bars[B_XCHG], NSOFT);
+        // one elected arrival per softmax warp: 256 separate arrivals on one barrier serialise
+        khq::mbar_init(&bars[B_QREADY], NSOFT / 32);
+        khq::mbar_init(&bars[B_PREADY], NSOFT / 32);
+        for (int q = 0; q < 4; ++q) khq::mbar_init(&bars[B_XCHG + q], 2);  // the two warps of a lane quarter
         khq::mbar_init(&bars[B_PVDONE], 1);
+        khq::mbar_init(&bars[B_PVDONE + 1], 1);
         khq::fence_barrier_init();
     }
     if (warp == 9) {
@@ -277,7 +279,7 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
                     umma_f16_ta(tmem + TM_O, tmem + TM_S + (uint32_t)(j & 1) * BC + ks * 8, db, IDESC_O,
                                 (j > 0 || ks > 0) ? 1u : 0u);
                 }
-                umma_commit(&bars[B_PVDONE]);
+                umma_commit(&bars[B_PVDONE + (j & 1)]);
                 umma_commit(&bars[B_VEMPTY + j % NS]);
             }
         }
@@ -309,7 +311,8 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
         }
         tmem_st_wait();
         tc_fence_before();
-        khq::mbar_arrive(&bars[B_QREADY]);
+        __syncwarp();
+        if (lane == 0) khq::mbar_arrive(&bars[B_QREADY]);
 
         float m_used = -1e30f, l_run = 0.0f;
         bool ok = true;
@@ -334,8 +337,9 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
             float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // the row maximum over all 64 keys: swap half maxima with the partner thread
             xchg[((j & 1) * 2 + half) * 128 + r] = mx;
-            khq::mbar_arrive(&bars[B_XCHG]);
-            ok = __all_sync(0xFFFFFFFFu, khq::mbar_wait_bounded(&bars[B_XCHG], (uint32_t)(j & 1), status));
+            __syncwarp();
+            if (lane == 0) khq::mbar_arrive(&bars[B_XCHG + (warp & 3)]);
+            ok = __all_sync(0xFFFFFFFFu, khq::mbar_wait_bounded(&bars[B_XCHG + (warp & 3)], (uint32_t)(j & 1), status));
             if (!ok) break;
             mx = fmaxf(mx, xchg[((j & 1) * 2 + (half ^ 1)) * 128 + r]) * scale_log2e;  // scale > 0
             float factor = 1.0f;
@@ -361,23 +365,24 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
             }
             const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
             l_run = l_run * factor + rs;
-            if (j > 0) {
-                // Every thread follows every phase of this barrier (a parity wait can only tell two
-                // neighbouring phases apart).  P V of the previous tile has normally long completed.
-                ok = __all_sync(0xFFFFFFFFu, khq::mbar_wait_bounded(&bars[B_PVDONE], (uint32_t)((j - 1) & 1), status));
+            if (j > 0 && __any_sync(0xFFFFFFFFu, grow)) {
+                // O may only be touched between P V of the previous tile and P V of this one.  The
+                // completion barriers alternate between two mbarriers so that a thread may skip
+                // phases: barrier (j-1)&1 last completed for tile j-3 (certainly, since Q K^T of
+                // this tile was issued behind P V of tile j-2) and cannot complete for tile j+1
+                // before this thread's own arrival for that tile.
+                ok = __all_sync(0xFFFFFFFFu, khq::mbar_wait_bounded(&bars[B_PVDONE + ((j - 1) & 1)],
+                                                                  (uint32_t)(((j - 1) >> 1) & 1), status));
                 if (!ok) break;
-                if (__any_sync(0xFFFFFFFFu, grow)) {
-                    // O may only be touched between P V of the previous tile and P V of this one
-                    tc_fence_after();
+                tc_fence_after();
 #pragma unroll 1
-                    for (int c0 = half * 128; c0 < half * 128 + 128; c0 += 32) {
-                        uint32_t orr[32];
-                        tmem_ld32(lane_base + TM_O + c0, orr);
-                        tmem_ld_wait();
+                for (int c0 = half * 128; c0 < half * 128 + 128; c0 += 32) {
+                    uint32_t orr[32];
+                    tmem_ld32(lane_base + TM_O + c0, orr);
+                    tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * factor);
-                        tmem_st32(lane_base + TM_O + c0, orr);
-                    }
+                    for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * factor);
+                    tmem_st32(lane_base + TM_O + c0, orr);
                 }
             }
             // P (fp16 pairs) over the S buffer it came from: keys 32*half.. -> columns 16*half..
@@ -385,16 +390,18 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
             tmem_st16(s_addr + half * 16, pk);
             tmem_st_wait();
             tc_fence_before();
-            khq::mbar_arrive(&bars[B_PREADY]);
+            __syncwarp();
+            if (lane == 0) khq::mbar_arrive(&bars[B_PREADY]);
         }
         // row sum over both halves
         if (ok) {
             xchg[((n_tiles & 1) * 2 + half) * 128 + r] = l_run;
-            khq::mbar_arrive(&bars[B_XCHG]);
-            ok = khq::mbar_wait_bounded(&bars[B_XCHG], (uint32_t)(n_tiles & 1), status);
+            __syncwarp();
+            if (lane == 0) khq::mbar_arrive(&bars[B_XCHG + (warp & 3)]);
+            ok = khq::mbar_wait_bounded(&bars[B_XCHG + (warp & 3)], (uint32_t)(n_tiles & 1), status);
             if (ok) l_run += xchg[((n_tiles & 1) * 2 + (half ^ 1)) * 128 + r];
         }
-        if (ok) ok = khq::mbar_wait_bounded(&bars[B_PVDONE], (uint32_t)((n_tiles - 1) & 1), status);
+        if (ok) ok = khq::mbar_wait_bounded(&bars[B_PVDONE + ((n_tiles - 1) & 1)], (uint32_t)(((n_tiles - 1) >> 1) & 1), status);
         ok = __all_sync(0xFFFFFFFFu, ok);
         if (ok) {
             tc_fence_after();
