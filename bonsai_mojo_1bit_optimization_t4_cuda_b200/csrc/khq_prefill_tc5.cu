@@ -1,41 +1,41 @@
 // khq_prefill_tc5.cu -- causal GQA prefill attention with sigmoid output gate on the fifth
-// generation tensor cores (tcgen05.mma, accumulators AND the A operands in tensor memory, the B
-// operands staged in shared memory by TMA).
+// generation tensor cores (tcgen05.mma, accumulators in tensor memory, operands staged by TMA).
 //
 // Same math and the same tensors as the warp-level kernel in khq_prefill.cu (the reference's
 // fp16-KV attention, src/kernels/elementwise_sm75.mojo:1140-1231, applied to all prompt rows at
 // once): out[t,h,:] = softmax_{u<=t}(q[t,h].K[u,h/6]*scale) V[u,h/6] * sigmoid(gate[t,h,:]).
 //
-// One CTA = 128 query rows of one query head; key tiles of 64.  Eleven warps, three roles:
+// One CTA = 128 query rows of one query head; key tiles of 128.  Eleven warps, three roles:
 //   warps 0-7  softmax, two threads per query row (warp w and warp w+4 share the tensor-memory
-//              lane quarter w%4 and a scheduler): a row's Q, S and O live in tensor-memory lane
-//              i, so there are no shuffles; the two threads of a row take 32 keys of a tile each
+//              lane quarter w%4 and a scheduler): a row's S and O live in tensor-memory lane i,
+//              so there are no shuffles; the two threads of a row take 64 keys of a tile each
 //              and swap their half maxima (and, at the end, half sums) through shared memory.
-//              Each writes its half of the Q row (fp16 pairs) into tensor memory once, then per
-//              tile reads 32 S columns with tcgen05.ld and writes P (fp16 pairs, 16 columns) back
-//              over the S buffer with tcgen05.st; O is rescaled lazily (only when the running
-//              max grew by more than 2^8); the epilogue normalises, gates and stores.
-//   warps 8,10 producers: one thread each issues the TMA loads of the K tiles (warp 8) and of
-//              the V tiles (warp 10), three stages each; a K stage is released as soon as its
-//              Q K^T has completed, a V stage when its P V has.
-//   warp 9     MMA: one thread issues S = Q K^T (M128 N64 K256, A = Q from tensor memory) for
-//              tile j+1, then O += P V (M128 N256 K64, A = P from tensor memory) for tile j;
+//              Per tile a thread reads 64 S columns with tcgen05.ld and writes P (fp16 pairs, 32
+//              columns) back over the S buffer with tcgen05.st; O is rescaled lazily (only when
+//              the running max grew by more than 2^8); the epilogue normalises, gates, stores.
+//   warps 8,10 producers: one thread each issues the TMA loads of Q and the K tiles (warp 8, a
+//              K tile in two halves of 128 head dims, each released as soon as the Q K^T steps
+//              that read it have completed) and of the V tiles (warp 10, two halves of 64 keys,
+//              each released when the P V steps that read it have completed).
+//   warp 9     MMA: one thread issues S = Q K^T (M128 N128 K256, A = Q from shared memory) for
+//              tile j+1, then O += P V (M128 N256 K128, A = P from tensor memory) for tile j;
 //              tcgen05.commit signals the mbarriers.
-// What bounds it: every CTA streams the whole K/V prefix of its rows from L2 (64 KB per 8.4 MFLOP
-// tile step, 128 FLOP per byte), and at ~0.93 PFLOP/s that is ~7.4 TB/s of L2 reads; emptying the
-// softmax does not shorten the kernel.  The next step up is a CTA pair (cta_group::2) that splits
-// each K/V tile between two SMs.
-// Tensor memory columns: O [0,256), S/P ping [256,320), S/P pong [320,384), Q [384,512).  An A
-// operand in tensor memory is row = lane, 16 consecutive K elements = 8 columns of fp16 pairs.
+// Tensor memory columns: O [0,256), S/P ping [256,384), S/P pong [384,512).  An A operand in
+// tensor memory is row = lane, 16 consecutive K elements = 8 columns of fp16 pairs.
+// Why these shapes: one tcgen05.mma of M 128 costs the tensor pipe at least ~93 cycles whatever
+// its N (measured: N 64 and N 128 both 93, N 256 138 with A in tensor memory; 107 / 171 for
+// N 128 / 256 with A in shared memory), so 64-key tiles (N 64, ideal 32 cycles) run Q K^T at a
+// third of the pipe's rate; tensor memory (512 columns) holds O plus two 128-key S buffers, which
+// leaves no room for Q, so Q stays in shared memory.
 //
 // Shared-memory operand layout: the 128-byte-swizzle canonical layouts.  A 5-D tensor map
 // {64 halfs, row, 64-column group, head, batch} with 128-byte swizzle makes TMA write a
-// (64 x 256) tile as four sub-tiles [group][row][128 bytes], 16-byte chunk c of row r at
+// (rows x 256) tile as sub-tiles [group][row][128 bytes], 16-byte chunk c of row r at
 // r*128 + ((c ^ (r & 7)) << 4).  Descriptors over it:
-//   K-major  (K): stride-dim byte offset (between 8-row groups) = 1024; a K step of 16 halfs
+//   K-major  (Q, K): stride-dim byte offset (between 8-row groups) = 1024; a K step of 16 halfs
 //                 advances the start address by 32 bytes inside a group, then to the next group;
 //   MN-major (V as the B operand of P V, keys are the contraction dim): leading-dim byte offset
-//                 (between 64-column groups) = 64*128, stride-dim byte offset (between 8-key
+//                 (between 64-column groups) = rows*128, stride-dim byte offset (between 8-key
 //                 groups) = 1024; a K step of 16 keys advances the start address by 2048 bytes.
 // Every wait is bounded; a wait that runs out sets a status word the host can read and the CTA
 // falls through to the teardown (tensor memory is always released).
@@ -51,23 +51,25 @@ namespace khq_prefill5 {
 using khq::smem_u32;
 
 constexpr int D = 256;
-constexpr int BR = 128;  // query rows per CTA
-constexpr int BC = 64;   // keys per tile
-constexpr int NS = 3;    // K stages and V stages
-constexpr int NSOFT = 256;  // softmax threads: two per query row, 32 of a tile's 64 keys each
+constexpr int BR = 128;     // query rows per CTA
+constexpr int BC = 128;     // keys per tile
+constexpr int NSOFT = 256;  // softmax threads: two per query row, 64 of a tile's 128 keys each
 constexpr int NTHREADS = NSOFT + 96;
-constexpr int KV_BYTES = BC * D * 2;  // 32 KB
-constexpr int OFF_K = 0;
-constexpr int OFF_V = OFF_K + NS * KV_BYTES;
-constexpr int OFF_XCHG = OFF_V + NS * KV_BYTES;  // float [2 parities][2 halves][128 rows]
+constexpr int Q_BYTES = BR * D * 2;        // 64 KB
+constexpr int KHALF_BYTES = BC * 128 * 2;  // 32 KB: 128 keys x 128 head dims (two 64-dim groups)
+constexpr int VHALF_BYTES = 64 * D * 2;    // 32 KB: 64 keys x 256 head dims (four 64-dim groups)
+constexpr int OFF_Q = 0;
+constexpr int OFF_K = OFF_Q + Q_BYTES;
+constexpr int OFF_V = OFF_K + 2 * KHALF_BYTES;
+constexpr int OFF_XCHG = OFF_V + 2 * VHALF_BYTES;  // float [2 parities][2 halves][128 rows]
 constexpr int OFF_BARS = OFF_XCHG + 2 * 2 * 128 * 4;
 constexpr int SMEM_BYTES = OFF_BARS + 256;
-constexpr uint32_t TM_COLS = 512, TM_O = 0, TM_S = 256, TM_Q = 384;
+constexpr uint32_t TM_COLS = 512, TM_O = 0, TM_S = 256;
 constexpr float RESCALE_LOG2 = 8.0f;
 
 enum Bar {
-    B_KFULL = 0, B_VFULL = NS, B_KEMPTY = 2 * NS, B_VEMPTY = 3 * NS, B_SFULL = 4 * NS, B_QREADY = 4 * NS + 2,
-    B_PREADY = 4 * NS + 3, B_PVDONE = 4 * NS + 4, B_XCHG = 4 * NS + 6, B_COUNT = 4 * NS + 10
+    B_KFULL = 0, B_VFULL = 2, B_KEMPTY = 4, B_VEMPTY = 6, B_SFULL = 8, B_QFULL = 10, B_PREADY = 11, B_PVDONE = 12,
+    B_XCHG = 14, B_COUNT = 18
 };
 static_assert(B_COUNT * 8 <= 192, "barriers overlap the tensor-memory slot");
 
@@ -157,22 +159,23 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // One 5-D tiled TMA load of a single CTA; coordinate 0 is always 0, so the 16-byte rule holds.
-__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int c1, int c3,
-                                            int c4) {
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int c1, int c2,
+                                            int c3, int c4) {
     asm volatile(
         "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, "
         "%6, %7}], [%2];" ::"r"(dst),
-        "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(0), "r"(c1), "r"(0), "r"(c3), "r"(c4)
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
         : "memory");
 }
 
 // ---- the kernel ----------------------------------------------------------------------------------
-// grid = (ceil(T/128), H_q, batch).  q_gate (B, T, H_q, 2D), out (B, T, H_q, D); K and V only
-// through their tensor maps.
+// grid = (ceil(T/128), H_q, batch).  q_gate (B, T, H_q, 2D), out (B, T, H_q, D); Q, K and V operands
+// come through their tensor maps.
 __global__ void __launch_bounds__(NTHREADS, 1)
-khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                           const __half* __restrict__ q_gate, __half* __restrict__ out, int T, int H_q, int H_kv,
-                           float scale_log2e, long long q_bs, long long o_bs) {
+khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                           const __grid_constant__ CUtensorMap tm_v, const __half* __restrict__ q_gate,
+                           __half* __restrict__ out, int T, int H_q, int H_kv, float scale_log2e, long long q_bs,
+                           long long o_bs) {
     extern __shared__ __align__(1024) unsigned char smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BARS);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_BARS + 192);
@@ -182,7 +185,7 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
     const int h = blockIdx.y, b = blockIdx.z;
     const int kvh = h / (H_q / H_kv);
     const int q0 = qb * BR;
-    const int n_tiles = min((T + BC - 1) / BC, (q0 + BR) / BC);
+    const int n_tiles = min((T + BC - 1) / BC, qb + 1);  // causal: key tiles 0..qb (BR == BC)
     int* status = &g_prefill_status;
     if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled layouts need a 1024-byte aligned base
         if (tid == 0) atomicExch(status, 2);
@@ -190,20 +193,18 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
     }
 
     if (tid == 0) {
-        for (int s = 0; s < NS; ++s) {
+        for (int s = 0; s < 2; ++s) {
             khq::mbar_init(&bars[B_KFULL + s], 1);
             khq::mbar_init(&bars[B_VFULL + s], 1);
             khq::mbar_init(&bars[B_KEMPTY + s], 1);
             khq::mbar_init(&bars[B_VEMPTY + s], 1);
+            khq::mbar_init(&bars[B_SFULL + s], 1);
+            khq::mbar_init(&bars[B_PVDONE + s], 1);
         }
-        khq::mbar_init(&bars[B_SFULL], 1);
-        khq::mbar_init(&bars[B_SFULL + 1], 1);
+        khq::mbar_init(&bars[B_QFULL], 1);
         // one elected arrival per softmax warp: 256 separate arrivals on one barrier serialise
-        khq::mbar_init(&bars[B_QREADY], NSOFT / 32);
         khq::mbar_init(&bars[B_PREADY], NSOFT / 32);
         for (int q = 0; q < 4; ++q) khq::mbar_init(&bars[B_XCHG + q], 2);  // the two warps of a lane quarter
-        khq::mbar_init(&bars[B_PVDONE], 1);
-        khq::mbar_init(&bars[B_PVDONE + 1], 1);
         khq::fence_barrier_init();
     }
     if (warp == 9) {
@@ -218,101 +219,112 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
     const uint32_t tmem = *tmem_slot;
     const uint32_t sbase = smem_u32(smem);
 
-    if (warp == 8 || warp == 10) {
-        // ================================ producers ================================================
-        // warp 8 streams the K tiles (a stage is free once Q K^T of its tile has completed), warp 10
-        // the V tiles (free once P V of its tile has completed).
+    if (warp == 8) {
+        // ================================ producer of Q and K ======================================
+        // K tile j = two halves by head dim (groups 0-1 and 2-3), each [2 groups][128 keys][128 B].
         if (lane == 0) {
-            const bool is_k = (warp == 8);
-            const CUtensorMap* map = is_k ? &tm_k : &tm_v;
-            uint64_t* full = &bars[is_k ? B_KFULL : B_VFULL];
-            uint64_t* empty = &bars[is_k ? B_KEMPTY : B_VEMPTY];
-            const uint32_t base = sbase + (is_k ? OFF_K : OFF_V);
+            khq::mbar_arrive_expect_tx(&bars[B_QFULL], Q_BYTES);
+            tma_load_5d(sbase + OFF_Q, &tm_q, &bars[B_QFULL], q0, 0, h, b);
             int issued = 0;
-            for (int j = 0; j < n_tiles; ++j) {
-                const int s = j % NS;
-                if (j >= NS && !khq::mbar_wait_bounded(&empty[s], (uint32_t)((j / NS - 1) & 1), status)) break;
-                khq::mbar_arrive_expect_tx(&full[s], KV_BYTES);
-                tma_load_5d(base + s * KV_BYTES, map, &full[s], j * BC, kvh, b);
-                issued = j + 1;
+            bool ok = true;
+            for (int j = 0; ok && j < n_tiles; ++j) {
+                for (int hf = 0; hf < 2; ++hf) {
+                    if (j >= 1 && !khq::mbar_wait_bounded(&bars[B_KEMPTY + hf], (uint32_t)((j - 1) & 1), status)) {
+                        ok = false;
+                        break;
+                    }
+                    khq::mbar_arrive_expect_tx(&bars[B_KFULL + hf], KHALF_BYTES);
+                    tma_load_5d(sbase + OFF_K + hf * KHALF_BYTES, &tm_k, &bars[B_KFULL + hf], j * BC, 2 * hf, kvh, b);
+                    issued = 2 * j + hf + 1;
+                }
             }
             // nothing this thread started may still be in flight when the CTA leaves
-            for (int j = max(0, issued - NS); j < issued; ++j)
-                khq::mbar_wait_bounded(&full[j % NS], (uint32_t)((j / NS) & 1), status);
+            khq::mbar_wait_bounded(&bars[B_QFULL], 0u, status);
+            for (int i = max(0, issued - 2); i < issued; ++i)
+                khq::mbar_wait_bounded(&bars[B_KFULL + (i & 1)], (uint32_t)((i >> 1) & 1), status);
+        }
+    } else if (warp == 10) {
+        // ================================ producer of V ============================================
+        // V tile j = two halves by key (64 keys each), each [4 groups][64 keys][128 B].
+        if (lane == 0) {
+            int issued = 0;
+            bool ok = true;
+            for (int j = 0; ok && j < n_tiles; ++j) {
+                for (int hf = 0; hf < 2; ++hf) {
+                    if (j >= 1 && !khq::mbar_wait_bounded(&bars[B_VEMPTY + hf], (uint32_t)((j - 1) & 1), status)) {
+                        ok = false;
+                        break;
+                    }
+                    khq::mbar_arrive_expect_tx(&bars[B_VFULL + hf], VHALF_BYTES);
+                    tma_load_5d(sbase + OFF_V + hf * VHALF_BYTES, &tm_v, &bars[B_VFULL + hf], j * BC + hf * 64, 0, kvh, b);
+                    issued = 2 * j + hf + 1;
+                }
+            }
+            for (int i = max(0, issued - 2); i < issued; ++i)
+                khq::mbar_wait_bounded(&bars[B_VFULL + (i & 1)], (uint32_t)((i >> 1) & 1), status);
         }
     } else if (warp == 9) {
         // ================================ MMA issuer ==============================================
         if (lane == 0) {
             constexpr uint32_t IDESC_S = instr_desc(BC, false);
             constexpr uint32_t IDESC_O = instr_desc(D, true);
+            bool ok = true;
             auto issue_qk = [&](int j) {
-                const uint32_t kaddr = sbase + OFF_K + (j % NS) * KV_BYTES;
+                const uint32_t s_tmem = tmem + TM_S + (uint32_t)(j & 1) * BC;
 #pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint64_t db = smem_desc(kaddr + (ks >> 2) * (BC * 128) + (ks & 3) * 32, 16, 1024);
-                    umma_f16_ta(tmem + TM_S + (uint32_t)(j & 1) * BC, tmem + TM_Q + ks * 8, db, IDESC_S, ks > 0 ? 1u : 0u);
+                for (int hf = 0; hf < 2; ++hf) {
+                    ok = ok && khq::mbar_wait_bounded(&bars[B_KFULL + hf], (uint32_t)(j & 1), status);
+                    if (!ok) return;
+                    tc_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk) {
+                        const int ks = hf * 8 + kk;
+                        const uint64_t da = smem_desc(sbase + OFF_Q + (ks >> 2) * (BR * 128) + (ks & 3) * 32, 16, 1024);
+                        const uint64_t db = smem_desc(sbase + OFF_K + hf * KHALF_BYTES + (kk >> 2) * (BC * 128) + (kk & 3) * 32,
+                                                      16, 1024);
+                        umma_f16(s_tmem, da, db, IDESC_S, ks > 0 ? 1u : 0u);
+                    }
+                    umma_commit(&bars[B_KEMPTY + hf]);
                 }
                 umma_commit(&bars[B_SFULL + (j & 1)]);
-                umma_commit(&bars[B_KEMPTY + (j % NS)]);
             };
-            bool ok = khq::mbar_wait_bounded(&bars[B_QREADY], 0u, status) &&
-                      khq::mbar_wait_bounded(&bars[B_KFULL], 0u, status);
-            if (ok) {
-                tc_fence_after();
-                issue_qk(0);
-            }
+            ok = khq::mbar_wait_bounded(&bars[B_QFULL], 0u, status);
+            if (ok) issue_qk(0);
             for (int j = 0; ok && j < n_tiles; ++j) {
                 if (j + 1 < n_tiles) {
-                    ok = khq::mbar_wait_bounded(&bars[B_KFULL + (j + 1) % NS], (uint32_t)(((j + 1) / NS) & 1), status);
+                    issue_qk(j + 1);
+                    if (!ok) break;
+                }
+                ok = khq::mbar_wait_bounded(&bars[B_PREADY], (uint32_t)(j & 1), status);
+                if (!ok) break;
+                const uint32_t p_tmem = tmem + TM_S + (uint32_t)(j & 1) * BC;
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf) {
+                    ok = khq::mbar_wait_bounded(&bars[B_VFULL + hf], (uint32_t)(j & 1), status);
                     if (!ok) break;
                     tc_fence_after();
-                    issue_qk(j + 1);
-                }
-                ok = khq::mbar_wait_bounded(&bars[B_PREADY], (uint32_t)(j & 1), status) &&
-                     khq::mbar_wait_bounded(&bars[B_VFULL + j % NS], (uint32_t)((j / NS) & 1), status);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t vaddr = sbase + OFF_V + (j % NS) * KV_BYTES;
 #pragma unroll
-                for (int ks = 0; ks < BC / 16; ++ks) {
-                    const uint64_t db = smem_desc(vaddr + ks * 2048, BC * 128, 1024);
-                    umma_f16_ta(tmem + TM_O, tmem + TM_S + (uint32_t)(j & 1) * BC + ks * 8, db, IDESC_O,
-                                (j > 0 || ks > 0) ? 1u : 0u);
+                    for (int kk = 0; kk < 4; ++kk) {
+                        const uint64_t db = smem_desc(sbase + OFF_V + hf * VHALF_BYTES + kk * 2048, 64 * 128, 1024);
+                        umma_f16_ta(tmem + TM_O, p_tmem + (hf * 4 + kk) * 8, db, IDESC_O, (j > 0 || hf > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    if (hf == 1) umma_commit(&bars[B_PVDONE + (j & 1)]);
+                    umma_commit(&bars[B_VEMPTY + hf]);
                 }
-                umma_commit(&bars[B_PVDONE + (j & 1)]);
-                umma_commit(&bars[B_VEMPTY + j % NS]);
             }
         }
     } else {
         // ================================ softmax + epilogue ======================================
-        // Two threads per query row: half 0 (warps 0-3) takes keys 0-31 of a tile and columns 0-127
-        // of Q / O, half 1 (warps 4-7) keys 32-63 and columns 128-255.  Both warps of a row sit on
-        // the same tensor-memory lane quarter (warp % 4) and on the same scheduler.
+        // Two threads per query row: half 0 (warps 0-3) takes keys 0-63 of a tile and columns 0-127
+        // of O, half 1 (warps 4-7) keys 64-127 and columns 128-255.  Both warps of a row sit on the
+        // same tensor-memory lane quarter (warp % 4) and on the same scheduler.
         const int half = warp >> 2, r = tid & 127;
         const int row = q0 + r;
         const bool live = row < T;
         const long long q_row = (long long)H_q * 2 * D, o_row = (long long)H_q * D;
         const __half* qrow = q_gate + b * q_bs + (long long)(live ? row : 0) * q_row + (long long)h * 2 * D;
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-        // ---- this thread's half of the Q row -> tensor memory (rows past the prompt are zero) ----
-#pragma unroll 1
-        for (int c0 = half * 64; c0 < half * 64 + 64; c0 += 32) {
-            uint32_t qr[32];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                uint4 x = make_uint4(0u, 0u, 0u, 0u);
-                if (live) x = __ldg(reinterpret_cast<const uint4*>(qrow + c0 * 2) + i);
-                qr[4 * i] = x.x;
-                qr[4 * i + 1] = x.y;
-                qr[4 * i + 2] = x.z;
-                qr[4 * i + 3] = x.w;
-            }
-            tmem_st32(lane_base + TM_Q + c0, qr);
-        }
-        tmem_st_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) khq::mbar_arrive(&bars[B_QREADY]);
+        uint64_t* xbar = &bars[B_XCHG + (warp & 3)];
 
         float m_used = -1e30f, l_run = 0.0f;
         bool ok = true;
@@ -321,25 +333,26 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
             if (!ok) break;
             tc_fence_after();
             const uint32_t s_addr = lane_base + TM_S + (uint32_t)(j & 1) * BC;
-            uint32_t sr[32];
-            tmem_ld32(s_addr + half * 32, sr);
+            uint32_t sr[2][32];
+            tmem_ld32(s_addr + half * 64, sr[0]);
+            tmem_ld32(s_addr + half * 64 + 32, sr[1]);
             tmem_ld_wait();
-            const int k0 = j * BC + half * 32;
+            const int k0 = j * BC + half * 64;
             // raw scores; masked entries (key after the row, or past the prompt) become -inf-like
-            if ((k0 + 31 > q0) || (k0 + 32 > T)) {
+            if ((k0 + 63 > q0) || (k0 + 64 > T)) {
 #pragma unroll
-                for (int c = 0; c < 32; ++c)
-                    if (k0 + c > row || k0 + c >= T) sr[c] = __float_as_uint(-1e30f);
+                for (int c = 0; c < 64; ++c)
+                    if (k0 + c > row || k0 + c >= T) sr[c >> 5][c & 31] = __float_as_uint(-1e30f);
             }
             float mx4[4] = {-1e30f, -1e30f, -1e30f, -1e30f};
 #pragma unroll
-            for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c]));
+            for (int c = 0; c < 64; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c >> 5][c & 31]));
             float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            // the row maximum over all 64 keys: swap half maxima with the partner thread
+            // the row maximum over all 128 keys: swap half maxima with the partner thread
             xchg[((j & 1) * 2 + half) * 128 + r] = mx;
             __syncwarp();
-            if (lane == 0) khq::mbar_arrive(&bars[B_XCHG + (warp & 3)]);
-            ok = __all_sync(0xFFFFFFFFu, khq::mbar_wait_bounded(&bars[B_XCHG + (warp & 3)], (uint32_t)(j & 1), status));
+            if (lane == 0) khq::mbar_arrive(xbar);
+            ok = __all_sync(0xFFFFFFFFu, khq::mbar_wait_bounded(xbar, (uint32_t)(j & 1), status));
             if (!ok) break;
             mx = fmaxf(mx, xchg[((j & 1) * 2 + (half ^ 1)) * 128 + r]) * scale_log2e;  // scale > 0
             float factor = 1.0f;
@@ -353,12 +366,12 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
             }
             // p = 2^(s*scale - m): one fused multiply-add and one ex2 per score
             float rs4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            uint32_t pk[16];
+            uint32_t pk[32];
             const float neg_m = -m_used;
 #pragma unroll
-            for (int c = 0; c < 32; c += 2) {
-                const float p0 = ex2_approx(fmaf(__uint_as_float(sr[c]), scale_log2e, neg_m));
-                const float p1 = ex2_approx(fmaf(__uint_as_float(sr[c + 1]), scale_log2e, neg_m));
+            for (int c = 0; c < 64; c += 2) {
+                const float p0 = ex2_approx(fmaf(__uint_as_float(sr[c >> 5][c & 31]), scale_log2e, neg_m));
+                const float p1 = ex2_approx(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), scale_log2e, neg_m));
                 rs4[(c >> 1) & 3] += p0 + p1;
                 const __half2 hh = __floats2half2_rn(p0, p1);
                 pk[c >> 1] = *reinterpret_cast<const uint32_t*>(&hh);
@@ -385,9 +398,9 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
                     tmem_st32(lane_base + TM_O + c0, orr);
                 }
             }
-            // P (fp16 pairs) over the S buffer it came from: keys 32*half.. -> columns 16*half..
+            // P (fp16 pairs) over the S buffer it came from: keys 64*half.. -> columns 32*half..
             // (the partner has read its S columns: it passed the exchange barrier after its load)
-            tmem_st16(s_addr + half * 16, pk);
+            tmem_st32(s_addr + half * 32, pk);
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
@@ -397,8 +410,8 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
         if (ok) {
             xchg[((n_tiles & 1) * 2 + half) * 128 + r] = l_run;
             __syncwarp();
-            if (lane == 0) khq::mbar_arrive(&bars[B_XCHG + (warp & 3)]);
-            ok = khq::mbar_wait_bounded(&bars[B_XCHG + (warp & 3)], (uint32_t)(n_tiles & 1), status);
+            if (lane == 0) khq::mbar_arrive(xbar);
+            ok = khq::mbar_wait_bounded(xbar, (uint32_t)(n_tiles & 1), status);
             if (ok) l_run += xchg[((n_tiles & 1) * 2 + (half ^ 1)) * 128 + r];
         }
         if (ok) ok = khq::mbar_wait_bounded(&bars[B_PVDONE + ((n_tiles - 1) & 1)], (uint32_t)(((n_tiles - 1) >> 1) & 1), status);
@@ -467,15 +480,16 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 // Tensor map over a (batch, T, heads, row_halfs) fp16 tensor that exposes, per (head, batch), a
-// T x 256 matrix as {64 halfs, T rows, 4 column groups}; a box is `box_rows` rows of one head.
+// T x 256 matrix as {64 halfs, T rows, 4 column groups}; a box is `box_rows` rows x `box_groups`
+// column groups of one head.
 int make_map(CUtensorMap* map, const void* base, int T, int heads, int batch, long long row_halfs,
-             long long head_halfs, long long batch_halfs, int box_rows) {
+             long long head_halfs, long long batch_halfs, int box_rows, int box_groups) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return -107;
     if (batch == 1) batch_halfs = (long long)T * row_halfs;
     const cuuint64_t dims[5] = {64, (cuuint64_t)T, 4, (cuuint64_t)heads, (cuuint64_t)batch};
     const cuuint64_t strides[4] = {(cuuint64_t)row_halfs * 2, 128, (cuuint64_t)head_halfs * 2, (cuuint64_t)batch_halfs * 2};
-    const cuuint32_t box[5] = {64, (cuuint32_t)box_rows, 4, 1, 1};
+    const cuuint32_t box[5] = {64, (cuuint32_t)box_rows, (cuuint32_t)box_groups, 1, 1};
     const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     for (cuuint64_t st : strides)
         if (st % 16 != 0) return -104;
@@ -500,9 +514,10 @@ extern "C" int launch_khq_gqa_prefill_tc5_fp16(const void* q_gate, const void* k
     for (const void* p : ptrs)
         if ((reinterpret_cast<uintptr_t>(p) & 15) != 0) return -104;
     if (batch > 1 && ((q_batch_stride | kv_batch_stride | out_batch_stride) & 7) != 0) return -104;
-    CUtensorMap mk, mv;
-    int rc = make_map(&mk, k, T, H_kv, batch, (long long)H_kv * D, D, kv_batch_stride, BC);
-    if (rc == 0) rc = make_map(&mv, v, T, H_kv, batch, (long long)H_kv * D, D, kv_batch_stride, BC);
+    CUtensorMap mq, mk, mv;
+    int rc = make_map(&mq, q_gate, T, H_q, batch, (long long)H_q * 2 * D, 2 * D, q_batch_stride, BR, 4);
+    if (rc == 0) rc = make_map(&mk, k, T, H_kv, batch, (long long)H_kv * D, D, kv_batch_stride, BC, 2);
+    if (rc == 0) rc = make_map(&mv, v, T, H_kv, batch, (long long)H_kv * D, D, kv_batch_stride, 64, 4);
     if (rc != 0) return rc;
     static bool attr_done[64] = {};
     int dev = 0;
@@ -515,7 +530,7 @@ extern "C" int launch_khq_gqa_prefill_tc5_fp16(const void* q_gate, const void* k
     }
     const dim3 grid((unsigned)((T + BR - 1) / BR), (unsigned)H_q, (unsigned)batch);
     khq_gqa_prefill_tc5_kernel<<<grid, NTHREADS, SMEM_BYTES, stream>>>(
-        mk, mv, static_cast<const __half*>(q_gate), static_cast<__half*>(out), T, H_q, H_kv,
+        mq, mk, mv, static_cast<const __half*>(q_gate), static_cast<__half*>(out), T, H_q, H_kv,
         scale * 1.4426950408889634f, q_batch_stride, out_batch_stride);
     err = cudaGetLastError();
     return (err == cudaSuccess) ? 0 : static_cast<int>(err);

@@ -27,7 +27,7 @@ def _run(cuda_ops, qg, k, v, B, T, H_q=H_Q, H_kv=H_KV, kernel="tc5"):
 
 
 @pytest.mark.parametrize("kernel", KERNELS)
-@pytest.mark.parametrize("T", [1, 64, 65, 200, 321, 1000])
+@pytest.mark.parametrize("T", [1, 64, 65, 128, 129, 200, 257, 321, 384, 1000])
 def test_prefill_vs_oracle(cuda_ops, oracle, T, kernel):
     B = 2
     rng = np.random.default_rng(50 + T)
