@@ -168,6 +168,44 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map
         : "memory");
 }
 
+// Bounded wait on up to three barriers at once.  A satisfied mbarrier wait still costs a ~250-cycle
+// round trip, so the MMA thread polls the barriers of a step together (the polls overlap) instead
+// of one after the other; a barrier found complete stays "done" (its next phase cannot complete
+// before this thread moves on).
+__device__ __forceinline__ uint32_t mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok;
+}
+template <int N>
+__device__ __forceinline__ bool mbar_wait_all_bounded(uint64_t* const (&bar)[N], const uint32_t (&parity)[N], int* status) {
+    uint32_t done = 0;
+    for (uint32_t it = 0; it < (1u << 22); ++it) {
+        uint32_t got[N];
+#pragma unroll
+        for (int i = 0; i < N; ++i) got[i] = mbar_test(bar[i], parity[i]);
+#pragma unroll
+        for (int i = 0; i < N; ++i) done |= got[i] << i;
+        if (done == (1u << N) - 1u) return true;
+        bool parked = false;  // park (a blocking try_wait) on the first barrier that is still open
+#pragma unroll
+        for (int i = 0; i < N; ++i)
+            if (!parked && !((done >> i) & 1u)) {
+                if (khq::mbar_try_wait(bar[i], parity[i])) done |= 1u << i;
+                parked = true;
+            }
+        if (done == (1u << N) - 1u) return true;
+    }
+    atomicExch(status, 1);
+    return false;
+}
+
 // ---- the kernel ----------------------------------------------------------------------------------
 // grid = (ceil(T/128), H_q, batch).  q_gate (B, T, H_q, 2D), out (B, T, H_q, D); Q, K and V operands
 // come through their tensor maps.
@@ -271,11 +309,13 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
             bool ok = true;
             auto issue_qk = [&](int j) {
                 const uint32_t s_tmem = tmem + TM_S + (uint32_t)(j & 1) * BC;
+                uint64_t* const kb[2] = {&bars[B_KFULL], &bars[B_KFULL + 1]};
+                const uint32_t kp[2] = {(uint32_t)(j & 1), (uint32_t)(j & 1)};
+                ok = ok && mbar_wait_all_bounded(kb, kp, status);
+                if (!ok) return;
+                tc_fence_after();
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
-                    ok = ok && khq::mbar_wait_bounded(&bars[B_KFULL + hf], (uint32_t)(j & 1), status);
-                    if (!ok) return;
-                    tc_fence_after();
 #pragma unroll
                     for (int kk = 0; kk < 8; ++kk) {
                         const int ks = hf * 8 + kk;
@@ -295,14 +335,14 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                     issue_qk(j + 1);
                     if (!ok) break;
                 }
-                ok = khq::mbar_wait_bounded(&bars[B_PREADY], (uint32_t)(j & 1), status);
+                uint64_t* const pb[3] = {&bars[B_PREADY], &bars[B_VFULL], &bars[B_VFULL + 1]};
+                const uint32_t pp[3] = {(uint32_t)(j & 1), (uint32_t)(j & 1), (uint32_t)(j & 1)};
+                ok = mbar_wait_all_bounded(pb, pp, status);
                 if (!ok) break;
+                tc_fence_after();
                 const uint32_t p_tmem = tmem + TM_S + (uint32_t)(j & 1) * BC;
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
-                    ok = khq::mbar_wait_bounded(&bars[B_VFULL + hf], (uint32_t)(j & 1), status);
-                    if (!ok) break;
-                    tc_fence_after();
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk) {
                         const uint64_t db = smem_desc(sbase + OFF_V + hf * VHALF_BYTES + kk * 2048, 64 * 128, 1024);
