@@ -360,3 +360,82 @@ class KhqRuntime:
             lines.append(">> [KHQ-PROF]   %-16s %8.4f" % (name, ns / 1e6 / n_tokens))
         lines.append(">> [KHQ-PROF]   %-16s %8.4f" % ("total", total / 1e6 / n_tokens))
         return "\n".join(lines)
+
+    # ------------------------------------------------------------------ checkpoint / resume (addition)
+    _STATE_ROW_ARRAYS = (("kmask", 16 * 4), ("kpay", 40), ("knorm", 2), ("krn", 2), ("vpay", 104), ("vnorm", 2),
+                         ("vrn", 2), ("vsm", 4))
+
+    def khq_save_state(self, path) -> int:
+        """Write the decode state of every initialised layer (rings, the compressed rows up to
+        ``boundary``, ``boundary`` / ``write_pos``) to a ``khq_state.bin`` container
+        (``formats`` module docstring).  The reference keeps this state in device memory only and
+        cannot resume a sequence.  Tables are not stored: they come from khq_calib.bin.  Returns
+        the number of layers written."""
+        import struct
+
+        from .formats import KHQS_MAGIC, KHQS_VERSION
+
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        ids = [i for i, L in enumerate(self.layers) if L.ready]
+        with open(path, "wb") as f:
+            f.write(struct.pack("<III", KHQS_MAGIC, KHQS_VERSION, len(ids)))
+            for i in ids:
+                L = self.layers[i]
+                f.write(struct.pack("<IIIIIII", i, L.H_q, L.H_kv, L.D, L.cap, L.boundary, L.write_pos))
+                for r in ("ring_k", "ring_v", "ring_u"):
+                    f.write(L.t[r].cpu().numpy().tobytes())
+                rows = L.boundary * L.H_kv
+                for name, row_bytes in self._STATE_ROW_ARRAYS:
+                    flat = L.t[name].view(torch.uint8)
+                    f.write(flat[:rows * row_bytes].cpu().numpy().tobytes())
+        return len(ids)
+
+    def khq_load_state(self, path) -> int:
+        """Restore what ``khq_save_state`` wrote into this runtime (tables must already be loaded
+        with ``khq_init`` / ``khq_activate`` and ``max_seq`` must be at least the saved boundary).
+        Layers are initialised on demand.  Raises ValueError on a malformed file or a shape that
+        does not fit; returns the number of layers restored."""
+        import struct
+
+        from .formats import KHQS_MAGIC, KHQS_VERSION
+
+        raw = open(path, "rb").read()
+        if len(raw) < 12:
+            raise ValueError("khq_state: shorter than its header")
+        magic, version, n = struct.unpack_from("<III", raw, 0)
+        if magic != KHQS_MAGIC or version != KHQS_VERSION:
+            raise ValueError(f"khq_state: bad magic/version 0x{magic:08X}/{version}")
+        if not self.ready:
+            raise ValueError("khq_state: load the calibration tables first (khq_init)")
+        off = 12
+        for _ in range(n):
+            if off + 28 > len(raw):
+                raise ValueError("khq_state: truncated layer header")
+            i, H_q, H_kv, D, cap, boundary, write_pos = struct.unpack_from("<IIIIIII", raw, off)
+            off += 28
+            if i >= KHQ_MAX_LAYERS or not self.layers[i].has_tables:
+                raise ValueError(f"khq_state: layer {i} has no tables in this runtime")
+            L = self.layers[i]
+            if boundary > L.cap or boundary % KHQ_CHUNK != 0 or write_pos < boundary or write_pos - boundary > KHQ_RING:
+                raise ValueError(f"khq_state: layer {i}: boundary {boundary} / write_pos {write_pos} do not fit cap {L.cap}")
+            self.khq_init_layer(i, H_q, H_kv, D)
+            if (L.H_q, L.H_kv, L.D) != (H_q, H_kv, D):
+                raise ValueError(f"khq_state: layer {i} shape differs from the initialised layer")
+            ring_bytes = KHQ_RING * H_kv * D * 2
+            rows = boundary * H_kv
+            need = 3 * ring_bytes + sum(rows * rb for _, rb in self._STATE_ROW_ARRAYS)
+            if off + need > len(raw):
+                raise ValueError(f"khq_state: layer {i} data truncated")
+            for r in ("ring_k", "ring_v", "ring_u"):
+                src = torch.frombuffer(bytearray(raw[off:off + ring_bytes]), dtype=torch.float16)
+                L.t[r].copy_(src.to(self.device))
+                off += ring_bytes
+            for name, row_bytes in self._STATE_ROW_ARRAYS:
+                nb = rows * row_bytes
+                if nb:
+                    src = torch.frombuffer(bytearray(raw[off:off + nb]), dtype=torch.uint8)
+                    L.t[name].view(torch.uint8)[:nb].copy_(src.to(self.device))
+                off += nb
+            L.boundary, L.write_pos = boundary, write_pos
+        return n

@@ -150,3 +150,44 @@ def test_prefill_leaves_the_per_token_state(cuda_ops, oracle, T, monkeypatch):
         assert rt.khq_step(3, qn, kr[T], v[T], o, SCALE)
     torch.cuda.synchronize()
     assert torch.equal(oa, ob)
+
+
+def test_checkpoint_resume_is_bit_identical(cuda_ops, tmp_path, monkeypatch):
+    """Decode 300 steps, checkpoint the KHQ state, restore it into a fresh runtime and continue
+    both for 120 more steps (across the compression event at write_pos 384): every output and every
+    code word must be bit-identical -- the state file holds all that the path carries from step to
+    step."""
+    import torch
+
+    from bonsai_mojo_1bit_optimization_t4_cuda_b200.runtime import KhqRuntime
+
+    monkeypatch.setenv("BONSAI_KHQ_SPLITS", "8")
+    n_a, n_b = 300, 120
+    case = cases.make_case(cases.synth.seed_for(1, 11), n_a + n_b, "calib", layer_id=3)
+
+    def step(rt, t):
+        qg = torch.from_numpy(cases.synth.make_q_gate(np.random.default_rng(7000 + t), t)).cuda()
+        out = torch.zeros(H_Q * D, dtype=torch.float16, device="cuda")
+        rt.khq_capture_unroped(3, torch.from_numpy(case["k_unroped"][t]).cuda())
+        assert rt.khq_step(3, qg, torch.from_numpy(case["k_roped"][t]).cuda(), torch.from_numpy(case["v"][t]).cuda(), out, SCALE)
+        return out.cpu()
+
+    rt = KhqRuntime(cuda_ops, device="cuda")
+    assert rt.khq_activate([case["tables"]], max_seq=1024)
+    rt.khq_init_layer(3, H_Q, H_KV, D)
+    for t in range(n_a):
+        step(rt, t)
+    path = tmp_path / "khq_state.bin"
+    assert rt.khq_save_state(path) == 1
+    rt2 = KhqRuntime(cuda_ops, device="cuda")
+    assert rt2.khq_activate([case["tables"]], max_seq=1024)
+    assert rt2.khq_load_state(path) == 1
+    assert (rt2.layers[3].boundary, rt2.layers[3].write_pos) == (rt.layers[3].boundary, rt.layers[3].write_pos) == (128, 300)
+    for t in range(n_a, n_a + n_b):
+        a, b = step(rt, t), step(rt2, t)
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16)), f"step {t}"
+    assert rt.layers[3].boundary == rt2.layers[3].boundary == 256
+    rows = 256 * H_KV
+    for key, rb in KhqRuntime._STATE_ROW_ARRAYS:
+        a, b = rt.layers[3].t[key].view(torch.uint8)[:rows * rb], rt2.layers[3].t[key].view(torch.uint8)[:rows * rb]
+        assert torch.equal(a, b), key
