@@ -39,6 +39,12 @@ N_LAYERS = 16
 LAYER_IDS = [4 * i + 3 for i in range(N_LAYERS)]  # Bonsai-27B's full-attention layers
 
 
+# dram bytes per algorithmic byte of the batched decode kernel, from the ncu capture summarised
+# in profiles/khq_decode_batched_mma_kernel__8seq_1layer.md (117.0 MB read + 0.4 MB written for
+# 116 604 928 algorithmic bytes); the ratio does not depend on the number of rows
+NCU_TRAFFIC_RATIO = 1.0034
+
+
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -529,8 +535,12 @@ def main():
                     "d2h_bytes_per_step": eng.d2h_bytes_per_step, "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": 2 * eng.L * args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
-                         "frac": achieved / peak_gbs, "traffic": None, "peak_source": peak_src,
-                         "kernel": "khq_decode_batched_kernel (+ its merge kernel and a 256 B memset, inside the same events)",
+                         "frac": achieved / peak_gbs, "traffic": NCU_TRAFFIC_RATIO * bytes_layer,
+                         "traffic_source": "ncu dram__bytes_read+write of an 8-sequence x 1-layer launch (117.0 MB for "
+                                           "116.6 MB algorithmic), scaled by payload rows: nothing is re-read",
+                         "peak_source": peak_src,
+                         "kernel": "%s (+ its merge kernel and a 256 B memset, inside the same events)" % (
+                             "khq_decode_batched_kernel" if args.kernel == "cuda-core" else "khq_decode_batched_mma_kernel"),
                          "algorithmic_bytes_per_launch": bytes_layer, "avg_launch_ms": avg_launch_ms},
             "us_per_layer_step_per_sequence": 1e3 * avg_launch_ms / args.seqs,
             "clocks": clocks, "device_status": status, "setup_s": setup_s,
