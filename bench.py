@@ -61,7 +61,7 @@ def parse():
     ap.add_argument("--prefill-len", type=int, default=8192, help="prompt length (--workload prefill)")
     ap.add_argument("--prefill-kernel", default="tc5", choices=["tc5", "mma"],
                     help="tc5: tcgen05 / tensor-memory kernel; mma: warp-level mma.sync kernel")
-    ap.add_argument("--workload", default="batched", choices=["batched", "long", "prefill"],
+    ap.add_argument("--workload", default="batched", choices=["batched", "long", "prefill", "compress"],
                     help="batched = BASELINE configs[3] (default); long = configs[2], one 131072-token sequence "
                          "split by context range over the ranks")
     ap.add_argument("--long-ctx", type=int, default=131072)
@@ -418,6 +418,83 @@ def run_prefill(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_compress(args, rank, world, local_rank):
+    """KHQ compression of a prompt prefix (BASELINE configs[4]: --prefill-batch prompts of
+    --prefill-len tokens per GPU, rows 0..T-129 of every prompt, K launch + V launch per prompt)
+    and of one 128-token event (512 rows).  Value: rows per second; roofline: algorithmic bytes
+    N x (512 + 512 + 220) against the measured HBM copy bandwidth."""
+    import torch
+    import torch.distributed as dist
+
+    from bonsai_mojo_1bit_optimization_t4_cuda_b200.ops import CudaOps
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    ops = CudaOps()
+    tb = make_tables(1)[0]
+    f = tb.as_f16()
+    tab = {k: torch.from_numpy(v).to(dev) for k, v in f.items()}
+    B, T = args.prefill_batch, args.prefill_len
+    n_tok = (T // 128 - 1) * 128  # every full chunk but the last stays raw
+    rows = n_tok * 4
+    g = torch.Generator(device=dev).manual_seed(20260914 + 4000 + rank)
+    ks = [torch.randn(rows, 256, generator=g, device=dev).half() for _ in range(B)]
+    vs = [torch.randn(rows, 256, generator=g, device=dev).half() for _ in range(B)]
+    out = dict(mask=torch.zeros(rows * 16, dtype=torch.int32, device=dev), kpay=torch.zeros(rows * 40, dtype=torch.uint8, device=dev),
+               vpay=torch.zeros(rows * 104, dtype=torch.uint8, device=dev), sm=torch.zeros(rows * 4, dtype=torch.uint8, device=dev),
+               kn=torch.zeros(rows, dtype=torch.float16, device=dev), krn=torch.zeros(rows, dtype=torch.float16, device=dev),
+               vn=torch.zeros(rows, dtype=torch.float16, device=dev), vrn=torch.zeros(rows, dtype=torch.float16, device=dev))
+
+    def one(k, v, n):
+        ops.compress(k, tab["d_k"], tab["rotor_k"], tab["cents_k"], tab["cents_k"], out["mask"], out["kn"], out["krn"],
+                     out["kpay"], out["sm"], n, 256, tb.ts_k, tb.alpha_k, False)
+        ops.compress(v, tab["d_v"], tab["rotor_v"], tab["cents_v"], tab["vq"], out["mask"], out["vn"], out["vrn"],
+                     out["vpay"], out["sm"], n, 256, tb.ts_v, tb.alpha_v, True)
+
+    def timed(fn, reps):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / reps], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms_prompt = timed(lambda: [one(ks[b], vs[b], rows) for b in range(B)], args.steps)
+    ms_event = timed(lambda: one(ks[0], vs[0], 512), max(args.steps, 50))
+    clocks = sampler.stop()
+    if rank == 0:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        b_alg = B * rows * (512 + 512 + 220)
+        ach = b_alg / (ms_prompt * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "KHQ compression throughput", "value": B * rows * world / (ms_prompt * 1e-3), "unit": "rows/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_prompt,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "BASELINE configs[4] compression: %d prompts x %d tokens per GPU, %d rows of 256 per "
+                                   "prompt (K launch + V launch each)" % (B, T, rows),
+                       "l2": "%.0f MB of fp16 rows per step, larger than the 126 MB L2" % (2 * B * rows * 512 / 1e6), "world": world},
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                         "algorithmic_bytes_per_step": b_alg},
+            "event_512_rows_us": ms_event * 1e3, "gpu_launches": 2 * B * args.steps, "clocks": clocks}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     args = parse()
     rank = int(os.environ.get("RANK", "0"))
@@ -431,6 +508,9 @@ def main():
         return
     if args.workload == "prefill":
         run_prefill(args, rank, world, local_rank)
+        return
+    if args.workload == "compress":
+        run_compress(args, rank, world, local_rank)
         return
 
     import torch
