@@ -446,6 +446,12 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
             __syncwarp();
             if (lane == 0) khq::mbar_arrive(&bars[B_PREADY]);
         }
+        // this thread's 128 gate values: all sixteen 16-byte loads go out together, ahead of the
+        // final waits (issued one per use they cost a full memory latency each)
+        const __half* gate = qrow + D + half * 128;
+        uint4 g4[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) g4[i] = live ? __ldg(reinterpret_cast<const uint4*>(gate) + i) : make_uint4(0u, 0u, 0u, 0u);
         // row sum over both halves
         if (ok) {
             xchg[((n_tiles & 1) * 2 + half) * 128 + r] = l_run;
@@ -459,29 +465,28 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         if (ok) {
             tc_fence_after();
             const float inv = 1.0f / (l_run + 1e-9f);
-            const __half* gate = qrow + D;
-            __half* op = out + b * o_bs + (long long)(live ? row : 0) * o_row + (long long)h * D;
-#pragma unroll 1
-            for (int c0 = half * 128; c0 < half * 128 + 128; c0 += 32) {
+            __half* op = out + b * o_bs + (long long)(live ? row : 0) * o_row + (long long)h * D + half * 128;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
                 uint32_t orr[32];
-                tmem_ld32(lane_base + TM_O + c0, orr);
+                tmem_ld32(lane_base + TM_O + half * 128 + c * 32, orr);
                 tmem_ld_wait();
                 if (live) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        const uint4 g4 = __ldg(reinterpret_cast<const uint4*>(gate + c0 + i));
-                        const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w};
+                    for (int i = 0; i < 4; ++i) {
+                        const uint4 gq = g4[c * 4 + i];
+                        const uint32_t gw[4] = {gq.x, gq.y, gq.z, gq.w};
                         uint32_t ow[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             const __half2 gg = *reinterpret_cast<const __half2*>(&gw[e]);
                             const float g0 = __half2float(__low2half(gg)), g1 = __half2float(__high2half(gg));
-                            const float x0 = __uint_as_float(orr[i + 2 * e]) * inv * (1.0f / (1.0f + __expf(-g0)));
-                            const float x1 = __uint_as_float(orr[i + 2 * e + 1]) * inv * (1.0f / (1.0f + __expf(-g1)));
+                            const float x0 = __uint_as_float(orr[i * 8 + 2 * e]) * inv * __fdividef(1.0f, 1.0f + __expf(-g0));
+                            const float x1 = __uint_as_float(orr[i * 8 + 2 * e + 1]) * inv * __fdividef(1.0f, 1.0f + __expf(-g1));
                             const __half2 oo = __floats2half2_rn(x0, x1);
                             ow[e] = *reinterpret_cast<const uint32_t*>(&oo);
                         }
-                        *reinterpret_cast<uint4*>(op + c0 + i) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                        *reinterpret_cast<uint4*>(op + c * 32 + i * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
                     }
                 }
             }
