@@ -61,7 +61,7 @@ def parse():
     ap.add_argument("--prefill-len", type=int, default=8192, help="prompt length (--workload prefill)")
     ap.add_argument("--prefill-kernel", default="tc5", choices=["tc5", "mma"],
                     help="tc5: tcgen05 / tensor-memory kernel; mma: warp-level mma.sync kernel")
-    ap.add_argument("--workload", default="batched", choices=["batched", "long", "prefill", "compress"],
+    ap.add_argument("--workload", default="batched", choices=["batched", "long", "prefill", "compress", "single"],
                     help="batched = BASELINE configs[3] (default); long = configs[2], one 131072-token sequence "
                          "split by context range over the ranks")
     ap.add_argument("--long-ctx", type=int, default=131072)
@@ -418,6 +418,111 @@ def run_prefill(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_single(args, rank, world, local_rank):
+    """BASELINE configs[0]: one decode-attention layer-step of one sequence through the drop-in
+    launches (compressed attention, splits 1 + window attention + merge/gate), context 512 = 384
+    compressed + 128 raw tokens.  Value: microseconds per layer-step (plain launches; CUDA-graph
+    replay beside it).  When the reference's own kernels, recompiled for sm_100a, are present
+    (oracle/_ref/, a baseline leg like the CPU one), the same three launches are timed through that
+    library.  Replicas only: every rank runs the same step."""
+    import ctypes
+
+    import torch
+
+    from bonsai_mojo_1bit_optimization_t4_cuda_b200 import lib as khqlib
+    from bonsai_mojo_1bit_optimization_t4_cuda_b200.ops import CudaOps
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    ops = CudaOps()
+    tb = make_tables(1)[0]
+    tab = {k: torch.from_numpy(v).to(dev) for k, v in tb.as_f16().items()}
+    c_len, win_len, win_start = 384, 128, 384 % 256
+    rows = c_len * 4
+    g = torch.Generator(device=dev).manual_seed(20260914 + rank)
+    kv = dict(k_mask=torch.zeros(rows * 16, dtype=torch.int32, device=dev), k_payload=torch.zeros(rows * 40, dtype=torch.uint8, device=dev),
+              v_payload=torch.zeros(rows * 104, dtype=torch.uint8, device=dev), v_shared_meta=torch.zeros(rows * 4, dtype=torch.uint8, device=dev),
+              k_norms=torch.zeros(rows, dtype=torch.float16, device=dev), k_r_norms=torch.zeros(rows, dtype=torch.float16, device=dev),
+              v_norms=torch.zeros(rows, dtype=torch.float16, device=dev), v_r_norms=torch.zeros(rows, dtype=torch.float16, device=dev))
+    k = torch.randn(c_len, 4, 256, generator=g, device=dev).half()
+    v = torch.randn(c_len, 4, 256, generator=g, device=dev).half()
+    ops.compress(k, tab["d_k"], tab["rotor_k"], tab["cents_k"], tab["cents_k"], kv["k_mask"], kv["k_norms"], kv["k_r_norms"],
+                 kv["k_payload"], kv["v_shared_meta"], rows, 256, tb.ts_k, tb.alpha_k, False)
+    ops.compress(v, tab["d_v"], tab["rotor_v"], tab["cents_v"], tab["vq"], kv["k_mask"], kv["v_norms"], kv["v_r_norms"],
+                 kv["v_payload"], kv["v_shared_meta"], rows, 256, tb.ts_v, tb.alpha_v, True)
+    ring_k = torch.randn(256 * 1024, generator=g, device=dev).half()
+    ring_v = torch.randn(256 * 1024, generator=g, device=dev).half()
+    qg = torch.randn(24 * 512, generator=g, device=dev).half()
+    ac = torch.zeros(24 * 258, dtype=torch.float32, device=dev)
+    aw = torch.zeros(24 * 258, dtype=torch.float32, device=dev)
+    ap = torch.zeros(24 * 32 * 258, dtype=torch.float32, device=dev)
+    out = torch.zeros(24 * 256, dtype=torch.float16, device=dev)
+
+    def step_with(lib_handle, stream):
+        P = lambda t: t.data_ptr()
+        rc = lib_handle.launch_khq_attn_fp16(
+            P(qg), P(kv["k_payload"]), P(kv["v_payload"]), P(kv["v_shared_meta"]), P(kv["k_mask"]), P(kv["k_norms"]),
+            P(kv["k_r_norms"]), P(kv["v_norms"]), P(kv["v_r_norms"]), P(tab["cents_k"]), P(tab["cents_v"]), P(tab["vq"]),
+            P(tab["rotor_k"]), P(tab["rotor_v"]), P(tab["d_k"]), P(tab["d_v"]), P(ac), P(ap), 24, 24, 1, c_len, c_len, 6,
+            1.0 / 16.0, tb.alpha_k, tb.alpha_v, 1e7, 0, 1, stream)
+        rc |= lib_handle.launch_khq_window_attn_fp16(P(qg), P(ring_k), P(ring_v), P(aw), win_start, win_len, 256, 24, 4, 256,
+                                                     1.0 / 16.0, stream)
+        rc |= lib_handle.launch_khq_merge_gate_fp16(P(ac), P(aw), P(qg), P(out), 24, 256, 1, stream)
+        assert rc == 0, rc
+
+    def timed(fn, n):
+        for _ in range(max(args.warmup, 3) * 10):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / n
+
+    n_it = max(args.steps, 10) * 20
+    ours = khqlib.load()
+    cur = lambda: torch.cuda.current_stream().cuda_stream
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    us_plain = timed(lambda: step_with(ours, cur()), n_it)
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        step_with(ours, side.cuda_stream)
+    torch.cuda.synchronize()
+    with torch.cuda.graph(graph, stream=side):
+        step_with(ours, side.cuda_stream)
+    us_graph = timed(graph.replay, n_it)
+    ref_us = None
+    ref_path = ROOT / "oracle" / "_ref" / "libbonsai_ref_sm100a.so"
+    if ref_path.exists():
+        so = ctypes.CDLL(str(ref_path))
+        for name in ("launch_khq_attn_fp16", "launch_khq_window_attn_fp16", "launch_khq_merge_gate_fp16"):
+            fn = getattr(so, name)
+            fn.restype, fn.argtypes = khqlib.SIGNATURES[name]
+        ref_us = timed(lambda: step_with(so, 0), max(n_it // 10, 20))
+    clocks = sampler.stop()
+    if rank == 0:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        b_alg = 4 * (220 * c_len + 1024 * win_len)
+        ach = b_alg / (us_graph * 1e-6) / 1e9
+        print(json.dumps({
+            "metric": "KHQ decode attention latency", "value": us_plain, "unit": "us/layer-step", "n_gpus": world,
+            "steps": n_it, "warmup": max(args.warmup, 3) * 10, "ms_per_step": us_plain / 1e3, "higher_is_better": False,
+            "scaling": "replicas only", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "BASELINE configs[0]: one sequence, 384 compressed + 128 raw tokens, 1 layer, splits 1, "
+                                   "three drop-in launches per step", "l2": "862 KB working set: L2-resident by nature (a "
+                       "latency case, not a bandwidth one)"},
+            "graph_replay_us": us_graph, "reference_kernels_sm100a_us": ref_us,
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                         "algorithmic_bytes_per_step": b_alg, "note": "launch-latency bound at this size"},
+            "gpu_launches": 3 * n_it, "clocks": clocks, "device_status": ours.khq_b200_device_status()}), flush=True)
+
+
 def run_compress(args, rank, world, local_rank):
     """KHQ compression of a prompt prefix (BASELINE configs[4]: --prefill-batch prompts of
     --prefill-len tokens per GPU, rows 0..T-129 of every prompt, K launch + V launch per prompt)
@@ -511,6 +616,9 @@ def main():
         return
     if args.workload == "compress":
         run_compress(args, rank, world, local_rank)
+        return
+    if args.workload == "single":
+        run_single(args, rank, world, local_rank)
         return
 
     import torch

@@ -245,22 +245,30 @@ khq_compress_kernel(const __half* __restrict__ x, const __half* __restrict__ d_v
                 *reinterpret_cast<uint4*>(&hcb[0]) = __ldg(cbp);
                 *reinterpret_cast<uint4*>(&hcb[8]) = __ldg(cbp + 1);
                 *reinterpret_cast<uint4*>(&hcb[16]) = __ldg(cbp + 2);
+                float cf[24];  // the lane's 8 codes x 3 dims as fp32 (exact), converted two at a time
+#pragma unroll
+                for (int e = 0; e < 24; e += 2) {
+                    const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&hcb[e]));
+                    cf[e] = f2.x;
+                    cf[e + 1] = f2.y;
+                }
                 float best = 1e20f;
                 unsigned bi = 0;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    const float d0 = __fmaf_rn(-__half2float(hcb[i * 3 + 0]), alpha, v0);
-                    const float d1 = __fmaf_rn(-__half2float(hcb[i * 3 + 1]), alpha, v1);
-                    const float d2 = __fmaf_rn(-__half2float(hcb[i * 3 + 2]), alpha, v2);
+                    const float d0 = __fmaf_rn(-cf[i * 3 + 0], alpha, v0);
+                    const float d1 = __fmaf_rn(-cf[i * 3 + 1], alpha, v1);
+                    const float d2 = __fmaf_rn(-cf[i * 3 + 2], alpha, v2);
                     const float dist = __fmaf_rn(d2, d2, __fmaf_rn(d0, d0, d1 * d1));
                     if (dist < best) { best = dist; bi = (unsigned)(lane * 8 + i); }
                 }
-#pragma unroll
-                for (int m = 16; m > 0; m >>= 1) {
-                    const float ob = __shfl_xor_sync(0xFFFFFFFFu, best, m);
-                    const unsigned oi = __shfl_xor_sync(0xFFFFFFFFu, bi, m);
-                    if (ob < best || (ob == best && oi < bi)) { best = ob; bi = oi; }
-                }
+                // warp minimum of (distance, index): a lane's best is a non-negative, non-NaN float
+                // (it starts at 1e20 and only a strictly smaller distance replaces it), so its bit
+                // pattern orders like the value and two hardware warp reductions do the work of
+                // five shuffle-and-compare steps
+                const unsigned best_bits = __reduce_min_sync(0xFFFFFFFFu, __float_as_uint(best));
+                bi = __reduce_min_sync(0xFFFFFFFFu, (__float_as_uint(best) == best_bits) ? bi : 0xFFFFFFFFu);
+                best = __uint_as_float(best_bits);
                 // The reference starts from min=1e20 with a strict '<': if no distance is below
                 // 1e20 (NaN/inf input) it keeps code 0.
                 if (!(best < 1e20f)) bi = 0;
