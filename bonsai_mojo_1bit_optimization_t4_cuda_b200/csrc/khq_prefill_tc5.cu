@@ -650,6 +650,16 @@ int make_map(CUtensorMap* map, const void* base, int T, int heads, int batch, lo
 
 }  // namespace
 
+static int g_tc5_items_per_cta = 0;
+
+// 0 = choose by prompt length, 1 = one item per CTA, n > 1 = n items per CTA (a large n gives
+// the fully persistent grid).  Returns -100 for a negative value.
+extern "C" int khq_b200_prefill_tc5_items_per_cta(int n) {
+    if (n < 0) return -100;
+    g_tc5_items_per_cta = n;
+    return 0;
+}
+
 // Same arguments as launch_khq_gqa_prefill_fp16.  Returns -107 when the driver offers no tensor-map
 // encoder and -108 when it refuses these shapes.
 extern "C" int launch_khq_gqa_prefill_tc5_fp16(const void* q_gate, const void* k, const void* v, void* out, int batch,
@@ -690,14 +700,15 @@ extern "C" int launch_khq_gqa_prefill_tc5_fp16(const void* q_gate, const void* k
     // (batch, kv head) group after the other, heaviest first, which leaves the balancing of the
     // triangular workload to the hardware's dynamic CTA scheduler and runs the leaner instantiation
     // of the kernel (4 x 4096: 0.78 ms against 0.81; 4 x 8192: 2.72 against 2.99).
-    // KHQ_PREFILL_ITEMS_PER_CTA (read once) forces a mode: 1 = one item per CTA, larger = that many
-    // items per CTA.
-    static int forced = -1;
-    if (forced < 0) {
+    // khq_b200_prefill_tc5_items_per_cta(n) or KHQ_PREFILL_ITEMS_PER_CTA (read once) force a mode:
+    // 1 = one item per CTA, larger = that many items per CTA (the setter wins; 0 = automatic).
+    static int env_forced = -1;
+    if (env_forced < 0) {
         const char* e = getenv("KHQ_PREFILL_ITEMS_PER_CTA");
-        forced = e ? atoi(e) : 0;
-        if (forced < 0) forced = 0;
+        env_forced = e ? atoi(e) : 0;
+        if (env_forced < 0) env_forced = 0;
     }
+    const int forced = g_tc5_items_per_cta > 0 ? g_tc5_items_per_cta : env_forced;
     const int nqb = (T + BR - 1) / BR;
     long long ctas;
     int group_major = 0;

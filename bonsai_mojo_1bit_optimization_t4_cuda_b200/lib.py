@@ -41,6 +41,7 @@ SIGNATURES = {
     "launch_khq_gqa_prefill_mma_fp16": (
         c_int, [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_longlong, c_longlong, c_longlong, _P]),
     "khq_b200_prefill_select": (c_int, [c_int]),
+    "khq_b200_prefill_tc5_items_per_cta": (c_int, [c_int]),
     "khq_b200_prefill_status": (c_int, []),
     "launch_khq_prestep_fp16": (c_int, [_P] * 8 + [c_int] * 5 + [c_float, c_float, c_int, _P]),
     "khq_b200_version": (c_char_p, []),

@@ -223,6 +223,10 @@ int launch_khq_gqa_prefill_mma_fp16(const void* q_gate, const void* k, const voi
                                     long long kv_batch_stride, long long out_batch_stride,
                                     khq_stream_t stream);
 int khq_b200_prefill_select(int which);
+/* Work distribution of the _tc5_ kernel: 0 = by prompt length (persistent CTAs up to 24 row blocks of
+ * 128 rows, one CTA per 128-row item beyond), 1 = one item per CTA, n > 1 = n items per CTA (a large
+ * n gives one persistent CTA per SM).  Returns -100 for a negative n. */
+int khq_b200_prefill_tc5_items_per_cta(int n);
 int khq_b200_prefill_status(void);
 
 /* ---- Context parallelism: one long sequence split by context range over several GPUs ------

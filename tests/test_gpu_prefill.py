@@ -8,7 +8,9 @@ from cases import D, H_KV, H_Q, SCALE
 pytestmark = pytest.mark.gpu
 
 
-KERNELS = ["tc5", "mma"]  # tcgen05 / tensor-memory kernel (the default) and the warp-level mma.sync kernel
+# tcgen05 / tensor-memory kernel (the default; also forced into each of its two work distributions)
+# and the warp-level mma.sync kernel
+KERNELS = ["tc5", "mma", "tc5-one-item-per-cta", "tc5-persistent"]
 
 
 def _run(cuda_ops, qg, k, v, B, T, H_q=H_Q, H_kv=H_KV, kernel="tc5"):
@@ -16,12 +18,14 @@ def _run(cuda_ops, qg, k, v, B, T, H_q=H_Q, H_kv=H_KV, kernel="tc5"):
 
     dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
     out = torch.full((B, T, H_q, D), float("nan"), dtype=torch.float16, device="cuda")
-    assert cuda_ops.lib.khq_b200_prefill_select(KERNELS.index(kernel)) == 0
+    assert cuda_ops.lib.khq_b200_prefill_select(1 if kernel == "mma" else 0) == 0
+    assert cuda_ops.lib.khq_b200_prefill_tc5_items_per_cta({"tc5-one-item-per-cta": 1, "tc5-persistent": 1 << 20}.get(kernel, 0)) == 0
     try:
         cuda_ops.gqa_prefill(dev(qg), dev(k), dev(v), out, B, T, H_q, H_kv, D, SCALE)
         torch.cuda.synchronize()
     finally:
         cuda_ops.lib.khq_b200_prefill_select(0)
+        cuda_ops.lib.khq_b200_prefill_tc5_items_per_cta(0)
     assert cuda_ops.lib.khq_b200_prefill_status() == 0
     return out.float().cpu().numpy()
 
@@ -71,3 +75,43 @@ def test_prefill_error_codes(cuda_ops):
         assert fn(0, 0, 0, 0, 1, 8, 24, 4, 128, 0.0625, 0, 0, 0, 0) == -103
         assert fn(8, 0, 0, 0, 1, 8, 24, 4, 256, 0.0625, 0, 0, 0, 0) == -104
     assert lib.khq_b200_prefill_select(2) == -100
+    assert lib.khq_b200_prefill_tc5_items_per_cta(-1) == -100
+
+
+@pytest.mark.parametrize("mode", [1, 3, 1 << 20])
+def test_prefill_tc5_against_the_warp_level_kernel_on_random_shapes(cuda_ops, mode):
+    """Twelve random (batch, length) shapes per work distribution -- lengths around and off the
+    128-row block size, several items per persistent CTA -- each launched three times back to back:
+    the tcgen05 kernel must agree with the warp-level kernel (an independent implementation) and
+    repeat itself bit for bit (its barriers carry no state from one item or launch to the next)."""
+    import torch
+
+    lib = cuda_ops.lib
+    rng = np.random.default_rng(mode % 1000)
+    try:
+        for _ in range(12):
+            B = int(rng.integers(1, 6))
+            T = int(rng.choice([int(rng.integers(1, 140)), int(rng.integers(140, 1200)), 128 * int(rng.integers(1, 12)),
+                                128 * int(rng.integers(1, 12)) + 1, int(rng.integers(1200, 2600))]))
+            g = torch.Generator(device="cuda").manual_seed(int(rng.integers(1 << 30)))
+            qg = torch.randn(B, T, H_Q, 2 * D, generator=g, device="cuda").half()
+            k = (torch.randn(B, T, H_KV, D, generator=g, device="cuda") * 0.25).half()
+            v = torch.randn(B, T, H_KV, D, generator=g, device="cuda").half()
+            ref = torch.zeros(B, T, H_Q, D, dtype=torch.float16, device="cuda")
+            assert lib.khq_b200_prefill_select(1) == 0
+            cuda_ops.gqa_prefill(qg, k, v, ref, B, T, H_Q, H_KV, D, SCALE)
+            assert lib.khq_b200_prefill_select(0) == 0 and lib.khq_b200_prefill_tc5_items_per_cta(mode) == 0
+            outs = []
+            for _rep in range(3):
+                out = torch.full((B, T, H_Q, D), float("nan"), dtype=torch.float16, device="cuda")
+                cuda_ops.gqa_prefill(qg, k, v, out, B, T, H_Q, H_KV, D, SCALE)
+                outs.append(out)
+            torch.cuda.synchronize()
+            assert lib.khq_b200_prefill_status() == 0
+            ok, mx, exc = cases.attention_close(outs[0].float().cpu().numpy(), ref.float().cpu().numpy())
+            assert ok, f"B={B} T={T} mode={mode}: max abs {mx:.3e}, excess {exc:.3e}"
+            for o in outs[1:]:
+                assert torch.equal(o.view(torch.int16), outs[0].view(torch.int16)), f"B={B} T={T} mode={mode}: not repeatable"
+    finally:
+        lib.khq_b200_prefill_select(0)
+        lib.khq_b200_prefill_tc5_items_per_cta(0)
