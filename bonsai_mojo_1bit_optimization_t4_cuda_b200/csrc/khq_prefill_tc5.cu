@@ -43,6 +43,7 @@
 // Every wait is bounded; a wait that runs out sets a status word the host can read and the CTA
 // falls through to the teardown (tensor memory is always released).
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -84,8 +85,25 @@ __device__ int g_prefill_status = 0;
 // 16-byte units; bits 0-13, 16-29, 32-45), descriptor version 1 in bits 46-47, layout type 2
 // (128-byte swizzle) in bits 61-63.  It is assembled from a low and a high word, see desc_lo/desc_hi.
 // Instruction descriptor for kind::f16: fp32 accumulate, fp16 A and B, A K-major, M = 128.
-__host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
-    return (1u << 4) | (b_mn_major ? (1u << 16) : 0u) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+// (A/B format field: 0 = fp16, 1 = bf16, bits 7-9 and 10-12.)
+__host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major, bool bf16) {
+    return (1u << 4) | (bf16 ? ((1u << 7) | (1u << 10)) : 0u) | (b_mn_major ? (1u << 16) : 0u) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(128 >> 4) << 24);
+}
+// Two floats -> one 32-bit word of the 16-bit storage type (round to nearest even), and back.
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    if (BF16) {
+        const __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&t);
+    }
+    const __half2 t = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&t);
+}
+template <bool BF16>
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
+    if (BF16) return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+    return __half22float2(*reinterpret_cast<const __half2*>(&w));
 }
 
 // ---- tcgen05 / TMA wrappers ----------------------------------------------------------------------
@@ -266,7 +284,7 @@ __device__ __forceinline__ bool get_item(int ordinal, int T, int H_q, int H_kv, 
 // operands come through their tensor maps.  Per-tile barriers are indexed by g, the running count of
 // tiles this CTA has processed over all its items, so that the producers and the MMA thread run
 // ahead into the next item while the softmax warps are still in the epilogue of the current one.
-template <bool PERSIST>
+template <bool PERSIST, bool BF16>
 __global__ void __launch_bounds__(NTHREADS, 1)
 khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                            const __grid_constant__ CUtensorMap tm_v, const __half* __restrict__ q_gate,
@@ -375,8 +393,8 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
     } else if (warp == 9) {
         // ================================ MMA issuer ==============================================
         if (lane == 0) {
-            constexpr uint32_t IDESC_S = instr_desc(BC, false);
-            constexpr uint32_t IDESC_O = instr_desc(D, true);
+            constexpr uint32_t IDESC_S = instr_desc(BC, false, BF16);
+            constexpr uint32_t IDESC_O = instr_desc(D, true, BF16);
             constexpr uint32_t HI_K = desc_hi(1024);  // Q, K (K-major) and V (MN-major): 1024 bytes between 8-row groups
             const uint32_t q_lo = desc_lo(sbase + OFF_Q, 16), k_lo = desc_lo(sbase + OFF_K, 16);
             const uint32_t v_lo = desc_lo(sbase + OFF_V, 64 * 128);  // leading offset: the next 64-column group
@@ -511,8 +529,7 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                     const float p0 = ex2_approx(fmaf(__uint_as_float(sr[c >> 5][c & 31]), scale_log2e, neg_m));
                     const float p1 = ex2_approx(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), scale_log2e, neg_m));
                     rs4[(c >> 1) & 3] += p0 + p1;
-                    const __half2 hh = __floats2half2_rn(p0, p1);
-                    pk[c >> 1] = *reinterpret_cast<const uint32_t*>(&hh);
+                    pk[c >> 1] = pack2<BF16>(p0, p1);
                 }
                 const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
                 l_run = l_run * factor + rs;
@@ -583,12 +600,11 @@ khq_gqa_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
                         uint32_t ow[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const __half2 gg = *reinterpret_cast<const __half2*>(&gw[e]);
-                            const float g0 = __half2float(__low2half(gg)), g1 = __half2float(__high2half(gg));
+                            const float2 gf = unpack2<BF16>(gw[e]);
+                            const float g0 = gf.x, g1 = gf.y;
                             const float x0 = __uint_as_float(orr[q * 8 + 2 * e]) * inv * __fdividef(1.0f, 1.0f + __expf(-g0));
                             const float x1 = __uint_as_float(orr[q * 8 + 2 * e + 1]) * inv * __fdividef(1.0f, 1.0f + __expf(-g1));
-                            const __half2 oo = __floats2half2_rn(x0, x1);
-                            ow[e] = *reinterpret_cast<const uint32_t*>(&oo);
+                            ow[e] = pack2<BF16>(x0, x1);
                         }
                         *reinterpret_cast<uint4*>(op + c * 32 + q * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
                     }
@@ -632,7 +648,7 @@ EncodeTiledFn encode_tiled_fn() {
 // T x 256 matrix as {64 halfs, T rows, 4 column groups}; a box is `box_rows` rows x `box_groups`
 // column groups of one head.
 int make_map(CUtensorMap* map, const void* base, int T, int heads, int batch, long long row_halfs,
-             long long head_halfs, long long batch_halfs, int box_rows, int box_groups) {
+             long long head_halfs, long long batch_halfs, int box_rows, int box_groups, bool bf16) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return -107;
     if (batch == 1) batch_halfs = (long long)T * row_halfs;
@@ -642,7 +658,7 @@ int make_map(CUtensorMap* map, const void* base, int T, int heads, int batch, lo
     const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     for (cuuint64_t st : strides)
         if (st % 16 != 0) return -104;
-    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(base), dims, strides, box, estr,
+    const CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(base), dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : -108;
@@ -660,12 +676,10 @@ extern "C" int khq_b200_prefill_tc5_items_per_cta(int n) {
     return 0;
 }
 
-// Same arguments as launch_khq_gqa_prefill_fp16.  Returns -107 when the driver offers no tensor-map
-// encoder and -108 when it refuses these shapes.
-extern "C" int launch_khq_gqa_prefill_tc5_fp16(const void* q_gate, const void* k, const void* v, void* out, int batch,
-                                               int T, int H_q, int H_kv, int d, float scale,
-                                               long long q_batch_stride, long long kv_batch_stride,
-                                               long long out_batch_stride, cudaStream_t stream) {
+namespace {
+int launch_tc5(const void* q_gate, const void* k, const void* v, void* out, int batch, int T, int H_q, int H_kv, int d,
+               float scale, long long q_batch_stride, long long kv_batch_stride, long long out_batch_stride,
+               cudaStream_t stream, bool bf16) {
     using namespace khq_prefill5;
     if (batch <= 0 || T <= 0 || H_q <= 0 || H_kv <= 0) return -100;
     if (d != D || H_q % H_kv != 0) return -103;
@@ -674,9 +688,9 @@ extern "C" int launch_khq_gqa_prefill_tc5_fp16(const void* q_gate, const void* k
         if ((reinterpret_cast<uintptr_t>(p) & 15) != 0) return -104;
     if (batch > 1 && ((q_batch_stride | kv_batch_stride | out_batch_stride) & 7) != 0) return -104;
     CUtensorMap mq, mk, mv;
-    int rc = make_map(&mq, q_gate, T, H_q, batch, (long long)H_q * 2 * D, 2 * D, q_batch_stride, BR, 4);
-    if (rc == 0) rc = make_map(&mk, k, T, H_kv, batch, (long long)H_kv * D, D, kv_batch_stride, BC, 2);
-    if (rc == 0) rc = make_map(&mv, v, T, H_kv, batch, (long long)H_kv * D, D, kv_batch_stride, 64, 4);
+    int rc = make_map(&mq, q_gate, T, H_q, batch, (long long)H_q * 2 * D, 2 * D, q_batch_stride, BR, 4, bf16);
+    if (rc == 0) rc = make_map(&mk, k, T, H_kv, batch, (long long)H_kv * D, D, kv_batch_stride, BC, 2, bf16);
+    if (rc == 0) rc = make_map(&mv, v, T, H_kv, batch, (long long)H_kv * D, D, kv_batch_stride, 64, 4, bf16);
     if (rc != 0) return rc;
     static bool attr_done[64] = {};
     static int sm_count[64] = {};
@@ -685,10 +699,12 @@ extern "C" int launch_khq_gqa_prefill_tc5_fp16(const void* q_gate, const void* k
     if (err != cudaSuccess) return static_cast<int>(err);
     if (dev < 0 || dev >= 64) return -100;
     if (!attr_done[dev]) {
-        err = cudaFuncSetAttribute(khq_gqa_prefill_tc5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        if (err != cudaSuccess) return static_cast<int>(err);
-        err = cudaFuncSetAttribute(khq_gqa_prefill_tc5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        if (err != cudaSuccess) return static_cast<int>(err);
+        const void* kernels[4] = {(const void*)khq_gqa_prefill_tc5_kernel<true, false>, (const void*)khq_gqa_prefill_tc5_kernel<false, false>,
+                                  (const void*)khq_gqa_prefill_tc5_kernel<true, true>, (const void*)khq_gqa_prefill_tc5_kernel<false, true>};
+        for (const void* kf : kernels) {
+            err = cudaFuncSetAttribute(kf, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+            if (err != cudaSuccess) return static_cast<int>(err);
+        }
         err = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
         if (err != cudaSuccess) return static_cast<int>(err);
         attr_done[dev] = true;
@@ -722,16 +738,41 @@ extern "C" int launch_khq_gqa_prefill_tc5_fp16(const void* q_gate, const void* k
         ctas = items < sm_count[dev] ? items : sm_count[dev];
     }
     const unsigned grid = (unsigned)ctas;
-    if (ctas == items)
-        khq_gqa_prefill_tc5_kernel<false><<<grid, NTHREADS, SMEM_BYTES, stream>>>(
-            mq, mk, mv, static_cast<const __half*>(q_gate), static_cast<__half*>(out), T, H_q, H_kv, batch, group_major,
-            scale * 1.4426950408889634f, q_batch_stride, out_batch_stride);
-    else
-        khq_gqa_prefill_tc5_kernel<true><<<grid, NTHREADS, SMEM_BYTES, stream>>>(
-            mq, mk, mv, static_cast<const __half*>(q_gate), static_cast<__half*>(out), T, H_q, H_kv, batch, group_major,
-            scale * 1.4426950408889634f, q_batch_stride, out_batch_stride);
+    const __half* qp = static_cast<const __half*>(q_gate);  // 16-bit storage; the kernel converts per its type flag
+    __half* op = static_cast<__half*>(out);
+    const float sl2 = scale * 1.4426950408889634f;
+#define KHQ_TC5_LAUNCH(PERSIST, BF16)                                                                                  \
+    khq_gqa_prefill_tc5_kernel<PERSIST, BF16><<<grid, NTHREADS, SMEM_BYTES, stream>>>(                                  \
+        mq, mk, mv, qp, op, T, H_q, H_kv, batch, group_major, sl2, q_batch_stride, out_batch_stride)
+    if (ctas == items) {
+        if (bf16) KHQ_TC5_LAUNCH(false, true);
+        else KHQ_TC5_LAUNCH(false, false);
+    } else {
+        if (bf16) KHQ_TC5_LAUNCH(true, true);
+        else KHQ_TC5_LAUNCH(true, false);
+    }
+#undef KHQ_TC5_LAUNCH
     err = cudaGetLastError();
     return (err == cudaSuccess) ? 0 : static_cast<int>(err);
+}
+}  // namespace
+
+// Same arguments as launch_khq_gqa_prefill_fp16.  Returns -107 when the driver offers no tensor-map
+// encoder and -108 when it refuses these shapes.
+extern "C" int launch_khq_gqa_prefill_tc5_fp16(const void* q_gate, const void* k, const void* v, void* out, int batch,
+                                               int T, int H_q, int H_kv, int d, float scale,
+                                               long long q_batch_stride, long long kv_batch_stride,
+                                               long long out_batch_stride, cudaStream_t stream) {
+    return launch_tc5(q_gate, k, v, out, batch, T, H_q, H_kv, d, scale, q_batch_stride, kv_batch_stride, out_batch_stride,
+                      stream, false);
+}
+
+// The same attention over bf16 tensors (bf16 operands and P, fp32 accumulation, bf16 output).
+extern "C" int launch_khq_gqa_prefill_bf16(const void* q_gate, const void* k, const void* v, void* out, int batch, int T,
+                                           int H_q, int H_kv, int d, float scale, long long q_batch_stride,
+                                           long long kv_batch_stride, long long out_batch_stride, cudaStream_t stream) {
+    return launch_tc5(q_gate, k, v, out, batch, T, H_q, H_kv, d, scale, q_batch_stride, kv_batch_stride, out_batch_stride,
+                      stream, true);
 }
 
 // Reads and clears the status word of the tcgen05 prefill kernel on the current device

@@ -38,6 +38,8 @@ SIGNATURES = {
         c_int, [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_longlong, c_longlong, c_longlong, _P]),
     "launch_khq_gqa_prefill_tc5_fp16": (
         c_int, [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_longlong, c_longlong, c_longlong, _P]),
+    "launch_khq_gqa_prefill_bf16": (
+        c_int, [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_longlong, c_longlong, c_longlong, _P]),
     "launch_khq_gqa_prefill_mma_fp16": (
         c_int, [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_longlong, c_longlong, c_longlong, _P]),
     "khq_b200_prefill_select": (c_int, [c_int]),

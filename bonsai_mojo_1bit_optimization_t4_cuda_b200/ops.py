@@ -67,11 +67,18 @@ class CudaOps:
 
     # -- launch_khq_gqa_prefill_fp16: causal GQA attention of whole prompts -----------------------
     def gqa_prefill(self, q_gate, k, v, out, batch, T, H_q, H_kv, d, scale):
-        """q_gate (batch, T, H_q, 2d), k/v (batch, T, H_kv, d), out (batch, T, H_q, d): contiguous fp16."""
-        rc = self.lib.launch_khq_gqa_prefill_fp16(
+        """q_gate (batch, T, H_q, 2d), k/v (batch, T, H_kv, d), out (batch, T, H_q, d): contiguous, all
+        fp16 (launch_khq_gqa_prefill_fp16) or all bf16 (launch_khq_gqa_prefill_bf16)."""
+        dtypes = {getattr(t, "dtype", None) for t in (q_gate, k, v, out)}
+        name = "launch_khq_gqa_prefill_fp16"
+        if len(dtypes) == 1 and str(next(iter(dtypes))) == "torch.bfloat16":
+            name = "launch_khq_gqa_prefill_bf16"
+        elif len(dtypes) != 1:
+            raise TypeError(f"gqa_prefill: mixed tensor types {dtypes}")
+        rc = getattr(self.lib, name)(
             ptr(q_gate), ptr(k), ptr(v), ptr(out), int(batch), int(T), int(H_q), int(H_kv), int(d), float(scale),
             int(T) * H_q * 2 * d, int(T) * H_kv * d, int(T) * H_q * d, current_stream())
-        check("launch_khq_gqa_prefill_fp16", rc)
+        check(name, rc)
 
     # -- launch_khq_prestep_fp16: q/k head RMSNorm + K capture + partial RoPE + ring appends --------
     def prestep(self, q_gate, k, v, q_norm_w, k_norm_w, ring_k_slot, ring_v_slot, ring_u_slot, H_q, H_kv, d,

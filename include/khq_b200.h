@@ -222,6 +222,12 @@ int launch_khq_gqa_prefill_mma_fp16(const void* q_gate, const void* k, const voi
                                     int T, int H_q, int H_kv, int d, float scale, long long q_batch_stride,
                                     long long kv_batch_stride, long long out_batch_stride,
                                     khq_stream_t stream);
+/* The same attention over bf16 tensors (bf16 operands and probabilities, fp32 accumulation, bf16
+ * output): the _tc5_ kernel with its bf16 instruction format.  Same arguments, layouts and error
+ * codes as launch_khq_gqa_prefill_tc5_fp16.  No reference counterpart (the reference is fp16 only). */
+int launch_khq_gqa_prefill_bf16(const void* q_gate, const void* k, const void* v, void* out, int batch, int T,
+                                int H_q, int H_kv, int d, float scale, long long q_batch_stride,
+                                long long kv_batch_stride, long long out_batch_stride, khq_stream_t stream);
 int khq_b200_prefill_select(int which);
 /* Work distribution of the _tc5_ kernel: 0 = by prompt length (persistent CTAs up to 24 row blocks of
  * 128 rows, one CTA per 128-row item beyond), 1 = one item per CTA, n > 1 = n items per CTA (a large

@@ -115,3 +115,38 @@ def test_prefill_tc5_against_the_warp_level_kernel_on_random_shapes(cuda_ops, mo
     finally:
         lib.khq_b200_prefill_select(0)
         lib.khq_b200_prefill_tc5_items_per_cta(0)
+
+
+@pytest.mark.parametrize("mode", [0, 1, 1 << 20])
+@pytest.mark.parametrize("T", [77, 128, 700])
+def test_prefill_bf16_vs_torch_fp32(cuda_ops, T, mode):
+    """bf16 tensors: the tcgen05 kernel with bf16 operands against a plain PyTorch fp32 reference of
+    the same op on the same (bf16-rounded) inputs.  bf16 keeps 8 mantissa bits, so the bar is the
+    storage type's: |err| <= 4e-3 + 2e-2*|ref| (probabilities and the output are rounded to bf16)."""
+    import torch
+
+    B = 2
+    g = torch.Generator(device="cuda").manual_seed(300 + T)
+    qg = torch.randn(B, T, H_Q, 2 * D, generator=g, device="cuda").bfloat16()
+    k = (torch.randn(B, T, H_KV, D, generator=g, device="cuda") * 0.25).bfloat16()
+    v = torch.randn(B, T, H_KV, D, generator=g, device="cuda").bfloat16()
+    out = torch.full((B, T, H_Q, D), float("nan"), dtype=torch.bfloat16, device="cuda")
+    lib = cuda_ops.lib
+    assert lib.khq_b200_prefill_tc5_items_per_cta(mode) == 0
+    try:
+        cuda_ops.gqa_prefill(qg, k, v, out, B, T, H_Q, H_KV, D, SCALE)
+        torch.cuda.synchronize()
+    finally:
+        lib.khq_b200_prefill_tc5_items_per_cta(0)
+    assert lib.khq_b200_prefill_status() == 0
+    q = qg[..., :D].float().permute(0, 2, 1, 3)                       # (B, H_q, T, D)
+    gate = qg[..., D:].float().permute(0, 2, 1, 3)
+    kk = k.float().repeat_interleave(H_Q // H_KV, dim=2).permute(0, 2, 1, 3)
+    vv = v.float().repeat_interleave(H_Q // H_KV, dim=2).permute(0, 2, 1, 3)
+    s = (q @ kk.transpose(-1, -2)) * SCALE
+    s = s.masked_fill(torch.ones(T, T, device="cuda", dtype=torch.bool).triu(1), float("-inf"))
+    ref = (torch.softmax(s, dim=-1) @ vv) * torch.sigmoid(gate)
+    ref = ref.permute(0, 2, 1, 3)
+    err = (out.float() - ref).abs()
+    lim = 4e-3 + 2e-2 * ref.abs()
+    assert bool((err <= lim).all()), f"T={T}: max abs {err.max().item():.3e}, worst excess {(err - lim).max().item():.3e}"
