@@ -59,6 +59,7 @@ def parse():
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--prefill-batch", type=int, default=4, help="prompts per GPU (--workload prefill)")
     ap.add_argument("--prefill-len", type=int, default=8192, help="prompt length (--workload prefill)")
+    ap.add_argument("--prefill-dtype", default="fp16", choices=["fp16", "bf16"], help="storage type of the prefill tensors")
     ap.add_argument("--prefill-kernel", default="tc5", choices=["tc5", "mma"],
                     help="tc5: tcgen05 / tensor-memory kernel; mma: warp-level mma.sync kernel")
     ap.add_argument("--workload", default="batched", choices=["batched", "long", "prefill", "compress", "single"],
@@ -366,10 +367,12 @@ def run_prefill(args, rank, world, local_rank):
     assert lib.khq_b200_prefill_select(0 if args.prefill_kernel == "tc5" else 1) == 0
     B, T = args.prefill_batch, args.prefill_len
     g = torch.Generator(device=dev).manual_seed(20260914 + 3000 + rank)
-    qg = torch.randn(B, T, 24, 512, generator=g, device=dev).half()
-    k = (torch.randn(B, T, 4, 256, generator=g, device=dev) * 0.25).half()
-    v = torch.randn(B, T, 4, 256, generator=g, device=dev).half()
-    out = torch.zeros(B, T, 24, 256, device=dev, dtype=torch.float16)
+    dt = torch.bfloat16 if args.prefill_dtype == "bf16" else torch.float16
+    assert not (args.prefill_dtype == "bf16" and args.prefill_kernel == "mma"), "the warp-level kernel is fp16 only"
+    qg = torch.randn(B, T, 24, 512, generator=g, device=dev).to(dt)
+    k = (torch.randn(B, T, 4, 256, generator=g, device=dev) * 0.25).to(dt)
+    v = torch.randn(B, T, 4, 256, generator=g, device=dev).to(dt)
+    out = torch.zeros(B, T, 24, 256, device=dev, dtype=dt)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # larger than the 126 MB L2
 
     def barrier():
@@ -406,7 +409,8 @@ def run_prefill(args, rank, world, local_rank):
         print(json.dumps({
             "metric": "causal GQA prefill attention throughput", "value": B * T * world / (ms * 1e-3), "unit": "prompt tok/s/layer",
             "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
+            "scaling": "weak", "vs_baseline": None, "dtype": "%s operands, f32 accumulate" % ("bf16" if dt == torch.bfloat16 else "f16"),
+            "data": "synthetic",
             "config": {"workload": "causal GQA prefill attention + gate, %d prompts x %d tokens per GPU, H_q 24 / H_kv 4 / "
                                    "d 256, kernel %s" % (B, T, args.prefill_kernel),
                        "l2": "a 256 MB buffer is rewritten between timed launches", "world": world},
