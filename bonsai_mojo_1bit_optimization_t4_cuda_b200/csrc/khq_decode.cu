@@ -702,6 +702,37 @@ static int sm_count() {
     return n[dev];
 }
 
+// How many clusters of `c` CTAs of the compressed-attention kernels fit on the device at once.
+static int max_clusters(bool mma, int c) {
+    static int cache[64][2][9] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || c < 1 || c > 8) return 1;
+    int& slot = cache[dev][mma ? 1 : 0][c];
+    if (slot == 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)c, 1, 1);
+        cfg.blockDim = dim3(mma ? (unsigned)M2_THREADS : (unsigned)DEC_THREADS, 1, 1);
+        cfg.dynamicSmemBytes = mma ? (size_t)M2_SM_TOTAL : (size_t)SM_TOTAL;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)c;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        const cudaError_t e = mma ? cudaOccupancyMaxActiveClusters(&n, khq_attn_compressed_mma_kernel, &cfg)
+                                  : cudaOccupancyMaxActiveClusters(&n, khq_attn_compressed_kernel<false>, &cfg);
+        if (e != cudaSuccess || n <= 0) {
+            (void)cudaGetLastError();
+            n = sm_count() / c > 0 ? sm_count() / c : 1;
+        }
+        slot = n;
+    }
+    return slot;
+}
+
+
 }  // namespace khq
 
 using namespace khq;
@@ -759,11 +790,30 @@ extern "C" int launch_khq_attn_fp16(const void* q, const void* k_payload, const 
     for (int l = 0; l < L_q; ++l) {
         const int s_limit = (L_q > 1) ? (c_len < l + 1 ? c_len : l + 1) : c_len;
         const int per = (s_limit + num_splits - 1) / num_splits;
-        // CTAs per split: aim at ~TT tokens per CTA, at most a portable cluster of 8.
+        // CTAs per split (a portable cluster of at most 8) and the kernel generation, by estimated
+        // time in units of one token of tensor-core decode (0.23 us measured): waves x (per-CTA
+        // set-up + tokens per CTA x cost per token), waves = splits / clusters of that size that
+        // fit on the GPU at once (clusters are placed inside a GPC, so fewer than SMs / size fit).
+        // Tensor-core generation: set-up ~160 (codebook staging, query folding), pays from ~192
+        // tokens per CTA on.  CUDA-core generation: set-up ~116, 3.06 per token, ~TT tokens per CTA.
         int cluster = (per + TT - 1) / TT;
         if (cluster < 1) cluster = 1;
         if (cluster > 8) cluster = 8;
-        // Staging the 128 KB V codebook in shared memory pays once a CTA decodes a few hundred tokens.
+        {
+            const int tpc1 = (per + cluster - 1) / cluster;
+            const long long w1 = (num_splits + max_clusters(false, cluster) - 1) / max_clusters(false, cluster);
+            long long best = w1 * (116 + (tpc1 * 306LL) / 100);
+            for (int c = 1; c <= 8; ++c) {
+                const int tpc = (per + c - 1) / c;
+                if (tpc < 192) break;
+                const long long waves = (num_splits + max_clusters(true, c) - 1) / max_clusters(true, c);
+                const long long cost = waves * (160 + tpc);
+                if (cost < best) {
+                    best = cost;
+                    cluster = c;
+                }
+            }
+        }
         const int tok_per_cta = (per + cluster - 1) / cluster;
         if (tok_per_cta >= 192)  // tensor-core generation: its per-CTA table set-up pays from here on
             err = launch_cluster(khq_attn_compressed_mma_kernel, (unsigned)(num_splits * cluster), (unsigned)cluster,
