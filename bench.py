@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the KHQ decode-attention path on B200.
 
-Workload (BASELINE.json configs[3]): batched decode of 256 independent sequences with contexts
+Default workload (the benchmark specification's configuration 3): batched decode of 256 independent sequences with contexts
 uniform in [4096, 32768] (compressed prefix + raw window of 128..256 tokens), 16 attention layers,
 H_q 24 / H_kv 4 / head_dim 256, fp16 payloads, fp32 accumulate.  A "step" generates one token for
 every sequence: per layer one batched launch over all sequences.  Seeded synthetic state (the
@@ -63,7 +63,7 @@ def parse():
     ap.add_argument("--prefill-kernel", default="tc5", choices=["tc5", "mma"],
                     help="tc5: tcgen05 / tensor-memory kernel; mma: warp-level mma.sync kernel")
     ap.add_argument("--workload", default="batched", choices=["batched", "long", "prefill", "compress", "single"],
-                    help="batched = BASELINE configs[3] (default); long = configs[2], one 131072-token sequence "
+                    help="batched = configuration 3 of the benchmark specification (default); long = configuration 2, one 131072-token sequence "
                          "split by context range over the ranks")
     ap.add_argument("--long-ctx", type=int, default=131072)
     ap.add_argument("--splits", type=int, default=32)
@@ -268,7 +268,7 @@ def config_dict(args, world):
 
 # ------------------------------------------------------------------------------------------------
 def run_long(args, rank, world, local_rank):
-    """BASELINE configs[2]: one sequence, --long-ctx compressed tokens + 256 raw ring tokens, one
+    """Configuration 2 of the benchmark specification: one sequence, --long-ctx compressed tokens + 256 raw ring tokens, one
     layer, the compressed region partitioned by context range over the ranks; per step every rank
     computes its (24, 258) partial, one NCCL all-gather exchanges them, every rank merges + gates.
     Value: microseconds per layer-step (max over ranks)."""
@@ -423,7 +423,7 @@ def run_prefill(args, rank, world, local_rank):
 
 
 def run_single(args, rank, world, local_rank):
-    """BASELINE configs[0]: one decode-attention layer-step of one sequence through the drop-in
+    """Configuration 0 of the benchmark specification: one decode-attention layer-step of one sequence through the drop-in
     launches (compressed attention, splits 1 + window attention + merge/gate), context 512 = 384
     compressed + 128 raw tokens.  Value: microseconds per layer-step (plain launches; CUDA-graph
     replay beside it).  When the reference's own kernels, recompiled for sm_100a, are present
@@ -528,7 +528,7 @@ def run_single(args, rank, world, local_rank):
 
 
 def run_compress(args, rank, world, local_rank):
-    """KHQ compression of a prompt prefix (BASELINE configs[4]: --prefill-batch prompts of
+    """KHQ compression of a prompt prefix (configuration 4 of the benchmark specification: --prefill-batch prompts of
     --prefill-len tokens per GPU, rows 0..T-129 of every prompt, K launch + V launch per prompt)
     and of one 128-token event (512 rows).  Value: rows per second; roofline: algorithmic bytes
     N x (512 + 512 + 220) against the measured HBM copy bandwidth."""

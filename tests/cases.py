@@ -14,7 +14,7 @@ VARIANTS = {
     # what the reference's calibration produces in shape: K-static centroids (base multiplier
     # clamps to 1), random V rotor; K rotor random so the inverse-rotor path is exercised
     "calib": dict(vq_scale=1.0 / 16.0),
-    # BASELINE's literal codebook (N(0,1)) and the identity K rotor the real calibration leaves
+    # the benchmark specification's literal codebook (N(0,1)) and the identity K rotor the real calibration leaves
     "n01_idrot": dict(vq_scale=1.0, k_rotor_identity=True),
     # unscaled centroids: the per-row adaptive base multiplier is live (c_mult != 1000)
     "adaptive": dict(vq_scale=1.0 / 16.0, adaptive_mult=True),

@@ -1,6 +1,6 @@
-"""Size-independent properties at the full BASELINE sizes, where the CPU oracle is too slow to be
+"""Size-independent properties at the full sizes of the benchmark specification, where the CPU oracle is too slow to be
 the checker: row independence of the compress kernel, context-split invariance of the
-compressed-region attention (long context, BASELINE configs[2]), causal-prefix invariance of the
+compressed-region attention (long context, configuration 2), causal-prefix invariance of the
 prefill and agreement of its two independent kernels (configs[4]), and agreement of the batched
 persistent kernel with the per-sequence drop-in launches on long sequences (configs[3])."""
 import numpy as np
