@@ -67,6 +67,9 @@ def parse():
                          "split by context range over the ranks")
     ap.add_argument("--long-ctx", type=int, default=131072)
     ap.add_argument("--splits", type=int, default=32)
+    ap.add_argument("--exchange", default="peer", choices=["peer", "collective"],
+                    help="--workload long on N>1 GPUs: partials stored into the peers' buffers over NVLink (peer) or "
+                         "one NCCL all-gather (collective)")
     ap.add_argument("--kernel", default="auto", choices=["auto", "cuda-core", "mma"],
                     help="generation of the batched decode kernel")
     return ap.parse_args()
@@ -310,7 +313,16 @@ def run_long(args, rank, world, local_rank):
     ring_v = torch.randn(256 * 1024, generator=g, device=dev).half()
     owner = world - 1
     cp = ContextParallelDecode(ops, dist.group.WORLD, kv, tab, lo, hi, tb.alpha_k, tb.alpha_v, ring_k, ring_v, owner=owner,
-                               splits=args.splits, device=dev)
+                               splits=args.splits, device=dev, exchange=args.exchange)
+    if world > 1 and args.exchange == "peer":
+        # the two exchanges must give the same answer
+        ref = ContextParallelDecode(ops, dist.group.WORLD, kv, tab, lo, hi, tb.alpha_k, tb.alpha_v, ring_k, ring_v, owner=owner,
+                                    splits=args.splits, device=dev, exchange="collective")
+        qg0 = torch.randn(24 * 512, generator=g, device=dev).half()
+        a = cp.step(qg0.clone(), args.long_ctx % 256, 256).clone()
+        b = ref.step(qg0.clone(), args.long_ctx % 256, 256).clone()
+        torch.cuda.synchronize()
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16)), "peer exchange differs from the all-gather"
     qg = torch.randn(24 * 512, generator=g, device=dev).half()
     win_start, win_len = args.long_ctx % 256, 256
     for _ in range(max(args.warmup, 3)):
@@ -338,8 +350,10 @@ def run_long(args, rank, world, local_rank):
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": us / 1e3, "higher_is_better": False,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "BASELINE configs[2]: one sequence, %d compressed + %d raw tokens, 1 layer, splits %d, "
-                                   "context-partitioned over %d GPU(s), partials merged after one NCCL all-gather"
-                                   % (args.long_ctx, win_len, args.splits, world), "l2": "payload 115 MB per step, "
+                                   "context-partitioned over %d GPU(s), partials %s"
+                                   % (args.long_ctx, win_len, args.splits, world,
+                                      "stored into the peers' buffers over NVLink, merge kernel waits for their flags"
+                                      if (world > 1 and args.exchange == "peer") else "merged after one NCCL all-gather"), "l2": "payload 115 MB per step, "
                        "larger than L2 only in aggregate at 1 GPU"},
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peak * world, "unit": "GB/s", "frac": ach / (peak * world),
                          "traffic": None, "algorithmic_bytes_per_step": b_alg},

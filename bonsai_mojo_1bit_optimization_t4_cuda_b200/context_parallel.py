@@ -8,8 +8,10 @@ The reference has nothing distributed; what maps onto its kernel is that
 slice ``[lo, hi)`` of the compressed region is the call ``start_pos=lo, c_len=hi-lo`` on arrays
 that hold only that slice's rows.
 
-The one exchange step is ``all_gather`` (NCCL on GPUs, gloo in the CPU tests): an all-reduce
-formulation would need two rounds (max, then rescaled sums) and is not better at this size.
+The one exchange step is either ``all_gather`` (NCCL on GPUs, gloo in the CPU tests; an all-reduce
+formulation would need two rounds -- max, then rescaled sums -- and is not better at this size) or,
+on GPUs, direct stores into the peers' slot buffers with a flag per producer, the merge kernel
+waiting for the flags itself (``PeerExchange``): no collective launch on the step's critical path.
 """
 from __future__ import annotations
 
@@ -37,6 +39,57 @@ def partition_context(c_len: int, world: int, chunk: int = CHUNK) -> List[Tuple[
     return out
 
 
+class PeerExchange:
+    """Slot buffers and flags of a context-parallel group, mapped into every process (CUDA IPC
+    through ``torch.multiprocessing``'s tensor reductions; no multicast object is involved).
+
+    Every rank owns ``slots`` (2 parities x ``world * per_rank`` records of (24, 258) floats) and
+    ``flags`` (one 32-bit epoch word per producer).  ``publish`` stores this rank's records into
+    every peer's buffer and raises its flag there; ``merge`` waits (bounded) for all producers of the
+    step and finishes with the LSE merge + gate."""
+
+    def __init__(self, ops, group, per_rank: int = 2, device="cuda"):
+        from torch.multiprocessing.reductions import reduce_tensor
+
+        self.ops, self.group = ops, group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.per_rank = per_rank
+        dev = torch.device(device)
+        self.n_slots = self.world * per_rank
+        self.slots = torch.zeros(2, self.n_slots, H_Q, PART, dtype=torch.float32, device=dev)
+        self.flags = torch.zeros(self.world, dtype=torch.int32, device=dev)
+        torch.cuda.synchronize(dev)
+        mine = (reduce_tensor(self.slots), reduce_tensor(self.flags))
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, mine, group=group)
+        self._peers = []  # keeps the mappings alive
+        slot_ptrs, flag_ptrs = [], []
+        for r, ((f_s, a_s), (f_f, a_f)) in enumerate(everyone):
+            if r == self.rank:
+                ps, pf = self.slots, self.flags
+            else:
+                ps, pf = f_s(*a_s), f_f(*a_f)
+            self._peers.append((ps, pf))
+            slot_ptrs.append(ps.data_ptr())
+            flag_ptrs.append(pf.data_ptr())
+        self.peer_slots = torch.tensor(slot_ptrs, dtype=torch.int64, device=dev)
+        self.peer_flags = torch.tensor(flag_ptrs, dtype=torch.int64, device=dev)
+        self.epoch = 0
+        dist.barrier(group=group)
+
+    def publish(self, records: torch.Tensor) -> None:
+        """records: (per_rank, 24, 258) fp32 of this rank for the step that starts now."""
+        self.epoch += 1
+        par = self.epoch & 1
+        self.ops.publish_partials(records, self.per_rank, self.peer_slots, self.peer_flags, self.world, self.rank,
+                                  self.rank * self.per_rank, par * self.n_slots, self.epoch)
+
+    def merge(self, q_gate: torch.Tensor, out: torch.Tensor, max_polls: int = 0) -> None:
+        par = self.epoch & 1
+        self.ops.merge_slots_wait_gate(self.slots[par], self.flags, self.world, self.epoch, self.n_slots, q_gate, out,
+                                       H_Q, D, max_polls)
+
+
 class ContextParallelDecode:
     """One rank's share of a context-parallel decode step.
 
@@ -46,7 +99,10 @@ class ContextParallelDecode:
     """
 
     def __init__(self, ops, group, kv: dict, tables: dict, lo: int, hi: int, alpha_k: float, alpha_v: float,
-                 ring_k=None, ring_v=None, owner: int = 0, splits: int = 32, device="cuda"):
+                 ring_k=None, ring_v=None, owner: int = 0, splits: int = 32, device="cuda", exchange: str = "collective"):
+        """``exchange``: "collective" = one all-gather of the partials (NCCL / gloo), "peer" = every
+        rank stores its partials into the peers' buffers over NVLink and the merge kernel waits for
+        the flags (``PeerExchange``; CUDA only)."""
         self.ops, self.group = ops, group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
@@ -63,6 +119,8 @@ class ContextParallelDecode:
         self.out = torch.zeros(H_Q * D, dtype=torch.float16, device=dev)
         self._neutral = torch.zeros(H_Q, PART, dtype=torch.float32, device=dev)
         self._neutral[:, D] = -1e20
+        assert exchange in ("collective", "peer")
+        self.peer = PeerExchange(ops, group, per_rank=2, device=device) if exchange == "peer" and self.world > 1 else None
 
     def split_count(self, n_tok: int) -> int:
         return int(min(max(n_tok // 8, 1), self.splits))
@@ -87,6 +145,10 @@ class ContextParallelDecode:
                             scale)
         else:
             self.mine[1].copy_(self._neutral)
+        if self.peer is not None:
+            self.peer.publish(self.mine)
+            self.peer.merge(q_gate, self.out)
+            return self.out
         if self.world > 1:
             dist.all_gather_into_tensor(self.all.view(-1), self.mine.view(-1), group=self.group)
         else:

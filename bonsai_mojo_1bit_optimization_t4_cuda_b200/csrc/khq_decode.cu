@@ -640,6 +640,63 @@ khq_merge_slots_gate_kernel(const float* __restrict__ partials, int n_slots, con
     out[(size_t)h * D + dd] = __float2half(val * (1.0f / (1.0f + __expf(-g))));
 }
 
+// ---- context-parallel exchange over peer memory ----------------------------------------------
+// Instead of an all-gather, every GPU stores its partial records straight into every peer's slot
+// buffer (plain st.global over NVLink), fences system-wide and raises its flag on that peer to the
+// step's epoch; the consumer's merge kernel waits (bounded) for all flags, then merges and gates.
+// One CTA per destination GPU.
+__global__ void __launch_bounds__(256)
+khq_publish_partials_kernel(const float* __restrict__ src, int n_floats, float* const* __restrict__ peer_slots,
+                            unsigned int* const* __restrict__ peer_flags, long long dst_offset, int rank,
+                            unsigned int epoch) {
+    const int p = blockIdx.x;
+    float4* dst = reinterpret_cast<float4*>(peer_slots[p] + dst_offset);
+    const float4* s4 = reinterpret_cast<const float4*>(src);
+    for (int i = threadIdx.x; i < n_floats / 4; i += blockDim.x) dst[i] = s4[i];
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned int* flag = peer_flags[p] + rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
+    }
+}
+
+// The slot merge of khq_merge_slots_gate_kernel, preceded by a bounded wait for the `n_flags`
+// producers of this step (flag >= epoch, compared modulo 2^32).  Slots are read around L1 (peers
+// wrote them).  A wait that runs out sets the status word to 3 and the CTA still finishes.
+__global__ void __launch_bounds__(D)
+khq_merge_slots_wait_gate_kernel(const float* __restrict__ partials, const unsigned int* __restrict__ flags, int n_flags,
+                                 unsigned int epoch, int n_slots, const __half* __restrict__ q_gate,
+                                 __half* __restrict__ out, unsigned int max_polls) {
+    const int h = blockIdx.x, dd = threadIdx.x;
+    if (dd < n_flags) {
+        bool seen = false;
+        for (unsigned int it = 0; it < max_polls; ++it) {
+            unsigned int v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + dd) : "memory");
+            if ((int)(v - epoch) >= 0) {
+                seen = true;
+                break;
+            }
+            __nanosleep(64);
+        }
+        if (!seen) atomicExch(&g_status, 3);
+    }
+    __syncthreads();
+    float M = NEG_BIG;
+    for (int s = 0; s < n_slots; ++s) M = fmaxf(M, __ldcv(partials + ((size_t)s * HQ + h) * PART + D));
+    float num = 0.0f, den = 0.0f;
+    for (int s = 0; s < n_slots; ++s) {
+        const float* p = partials + ((size_t)s * HQ + h) * PART;
+        const float w = __expf(__ldcv(p + D) - M);
+        num = fmaf(__ldcv(p + dd), w, num);
+        den = fmaf(__ldcv(p + D + 1), w, den);
+    }
+    const float val = num / (den + 1e-8f);
+    const float g = __half2float(q_gate[(size_t)h * 2 * D + D + dd]);
+    out[(size_t)h * D + dd] = __float2half(val * (1.0f / (1.0f + __expf(-g))));
+}
+
 __global__ void khq_gather_q_kernel(const __half* __restrict__ q_gate, __half* __restrict__ q_out, int H_q,
                                     int d_v) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -1024,6 +1081,32 @@ extern "C" int launch_khq_merge_slots_gate_fp16(const void* partials, int n_slot
     return (err == cudaSuccess) ? 0 : static_cast<int>(err);
 }
 
+extern "C" int launch_khq_publish_partials_fp32(const void* src, int n_records, const void* peer_slots,
+                                                const void* peer_flags, int world, int rank, int first_slot,
+                                                long long parity_offset_records, unsigned int epoch, cudaStream_t stream) {
+    if (!src || !peer_slots || !peer_flags || n_records <= 0 || world <= 0 || rank < 0 || rank >= world || first_slot < 0)
+        return -100;
+    if (!aligned(src, 16)) return -104;
+    const long long off = (parity_offset_records + first_slot) * (long long)(HQ * PART);
+    khq_publish_partials_kernel<<<(unsigned)world, 256, 0, stream>>>(
+        static_cast<const float*>(src), n_records * HQ * PART, static_cast<float* const*>(peer_slots),
+        static_cast<unsigned int* const*>(peer_flags), off, rank, epoch);
+    const cudaError_t err = cudaGetLastError();
+    return (err == cudaSuccess) ? 0 : static_cast<int>(err);
+}
+
+extern "C" int launch_khq_merge_slots_wait_gate_fp16(const void* partials, const void* flags, int n_flags,
+                                                     unsigned int epoch, int n_slots, const void* q_gate, void* out,
+                                                     int H_q, int d, unsigned int max_polls, cudaStream_t stream) {
+    if (n_slots <= 0 || n_flags < 0 || n_flags > D || !partials || !flags || !q_gate || !out) return -100;
+    if (H_q != HQ || d != D) return -103;
+    khq_merge_slots_wait_gate_kernel<<<HQ, D, 0, stream>>>(
+        static_cast<const float*>(partials), static_cast<const unsigned int*>(flags), n_flags, epoch, n_slots,
+        static_cast<const __half*>(q_gate), static_cast<__half*>(out), max_polls ? max_polls : (1u << 22));
+    const cudaError_t err = cudaGetLastError();
+    return (err == cudaSuccess) ? 0 : static_cast<int>(err);
+}
+
 static void* g_khq_slots[3] = {nullptr, nullptr, nullptr};
 extern "C" void* khq_state_slot(int which) {
     if (which < 0 || which > 2) which = 0;
@@ -1031,6 +1114,14 @@ extern "C" void* khq_state_slot(int which) {
 }
 extern "C" int bonsai_cuda_sm75_init(void) { return 0; }
 extern "C" const char* khq_b200_version(void) { return "khq-b200 0.1 sm_100a"; }
+extern "C" int khq_b200_device_status_clear(void) {
+    int v = 0;
+    cudaError_t err = cudaMemcpyFromSymbol(&v, khq::g_status, sizeof(int));
+    if (err != cudaSuccess) return -static_cast<int>(err);
+    const int zero = 0;
+    err = cudaMemcpyToSymbol(khq::g_status, &zero, sizeof(int));
+    return (err == cudaSuccess) ? v : -static_cast<int>(err);
+}
 extern "C" int khq_b200_device_status(void) {
     int v = 0;
     const cudaError_t err = cudaMemcpyFromSymbol(&v, khq::g_status, sizeof(int));

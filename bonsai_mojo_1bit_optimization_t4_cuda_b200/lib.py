@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import POINTER, c_char_p, c_float, c_int, c_longlong, c_size_t, c_void_p
+from ctypes import POINTER, c_char_p, c_float, c_int, c_longlong, c_size_t, c_uint, c_void_p
 from pathlib import Path
 
 _PKG_DIR = Path(__file__).resolve().parent
@@ -48,6 +48,9 @@ SIGNATURES = {
     "launch_khq_prestep_fp16": (c_int, [_P] * 8 + [c_int] * 5 + [c_float, c_float, c_int, _P]),
     "khq_b200_version": (c_char_p, []),
     "khq_b200_device_status": (c_int, []),
+    "khq_b200_device_status_clear": (c_int, []),
+    "launch_khq_publish_partials_fp32": (c_int, [_P, c_int, _P, _P, c_int, c_int, c_int, c_longlong, c_uint, _P]),
+    "launch_khq_merge_slots_wait_gate_fp16": (c_int, [_P, _P, c_int, c_uint, c_int, _P, _P, c_int, c_int, c_uint, _P]),
 }
 
 _lib = None

@@ -65,6 +65,19 @@ class CudaOps:
                                                        int(H_q), int(d), current_stream())
         check("launch_khq_merge_slots_gate_fp16", rc)
 
+    # -- peer-memory exchange of context-parallel partials ----------------------------------------
+    def publish_partials(self, src, n_records, peer_slots, peer_flags, world, rank, first_slot, parity_offset_records, epoch):
+        rc = self.lib.launch_khq_publish_partials_fp32(ptr(src), int(n_records), ptr(peer_slots), ptr(peer_flags), int(world),
+                                                       int(rank), int(first_slot), int(parity_offset_records),
+                                                       int(epoch) & 0xFFFFFFFF, current_stream())
+        check("launch_khq_publish_partials_fp32", rc)
+
+    def merge_slots_wait_gate(self, partials, flags, n_flags, epoch, n_slots, q_gate, out, H_q, d, max_polls=0):
+        rc = self.lib.launch_khq_merge_slots_wait_gate_fp16(ptr(partials), ptr(flags), int(n_flags), int(epoch) & 0xFFFFFFFF,
+                                                            int(n_slots), ptr(q_gate), ptr(out), int(H_q), int(d),
+                                                            int(max_polls), current_stream())
+        check("launch_khq_merge_slots_wait_gate_fp16", rc)
+
     # -- launch_khq_gqa_prefill_fp16: causal GQA attention of whole prompts -----------------------
     def gqa_prefill(self, q_gate, k, v, out, batch, T, H_q, H_kv, d, scale):
         """q_gate (batch, T, H_q, 2d), k/v (batch, T, H_kv, d), out (batch, T, H_q, d): contiguous, all

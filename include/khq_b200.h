@@ -276,6 +276,29 @@ const char* khq_b200_version(void);
  * (0 = never).  Reads the device flag of the current device with a blocking 4-byte copy, so
  * call it outside the hot loop.  Returns the flag, or -(cudaError_t) on failure. */
 int khq_b200_device_status(void);
+/* The same read, then the word is reset to 0.  Values: 1 = a bounded wait on an asynchronous copy
+ * gave up, 3 = launch_khq_merge_slots_wait_gate_fp16 gave up waiting for a peer's flag. */
+int khq_b200_device_status_clear(void);
+
+/* ---- Context parallelism without a collective library: partials exchanged over peer memory ----
+ * Every GPU owns a slot buffer (2 parities x n_slots records of 24 x 258 floats) and a flag array
+ * (one 32-bit word per producer GPU), both mapped into the other processes (CUDA IPC).
+ * launch_khq_publish_partials_fp32 copies `n_records` consecutive (24, 258) records from `src` into
+ * slots first_slot.. of EVERY peer's buffer (peer_slots / peer_flags: device arrays of `world`
+ * pointers, entry p = GPU p's buffer as mapped here; parity_offset_records selects the parity
+ * half), fences system-wide and stores `epoch` into flag[rank] of every peer: one CTA per peer,
+ * plain stores over NVLink.  launch_khq_merge_slots_wait_gate_fp16 is
+ * launch_khq_merge_slots_gate_fp16 preceded by a wait for flags[0..n_flags) >= epoch (modulo
+ * 2^32), bounded by `max_polls` polls of ~64 ns (0 = 2^22): when it runs out the status word
+ * becomes 3 and the launch still completes.  Epochs grow by one per step; a producer is at most one
+ * step ahead of a consumer, so two parities of slots suffice.  No reference counterpart.
+ * Return -100 (bad arguments), -103 (shape), -104 (alignment). */
+int launch_khq_publish_partials_fp32(const void* src, int n_records, const void* peer_slots, const void* peer_flags,
+                                     int world, int rank, int first_slot, long long parity_offset_records,
+                                     unsigned int epoch, khq_stream_t stream);
+int launch_khq_merge_slots_wait_gate_fp16(const void* partials, const void* flags, int n_flags, unsigned int epoch,
+                                          int n_slots, const void* q_gate, void* out, int H_q, int d,
+                                          unsigned int max_polls, khq_stream_t stream);
 
 #ifdef __cplusplus
 }
