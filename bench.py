@@ -358,6 +358,8 @@ def run_long(args, rank, world, local_rank):
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peak * world, "unit": "GB/s", "frac": ach / (peak * world),
                          "traffic": None, "algorithmic_bytes_per_step": b_alg},
             "gpu_launches": 5 * args.steps, "device_status": khqlib.load().khq_b200_device_status()}), flush=True)
+    if cp.peer is not None:
+        cp.peer.close()
     dist.destroy_process_group()
 
 

@@ -40,40 +40,64 @@ def partition_context(c_len: int, world: int, chunk: int = CHUNK) -> List[Tuple[
 
 
 class PeerExchange:
-    """Slot buffers and flags of a context-parallel group, mapped into every process (CUDA IPC
-    through ``torch.multiprocessing``'s tensor reductions; no multicast object is involved).
+    """Slot buffers and flags of a context-parallel group, mapped into every process with CUDA IPC
+    (the library's ``khq_b200_peer_*`` helpers: plain ``cudaMalloc`` memory, opened by each peer on
+    its own device, which also enables peer access; no multicast object is involved).
 
-    Every rank owns ``slots`` (2 parities x ``world * per_rank`` records of (24, 258) floats) and
-    ``flags`` (one 32-bit epoch word per producer).  ``publish`` stores this rank's records into
-    every peer's buffer and raises its flag there; ``merge`` waits (bounded) for all producers of the
-    step and finishes with the LSE merge + gate."""
+    Every rank owns one allocation: ``slots`` (2 parities x ``world * per_rank`` records of (24, 258)
+    floats), ``flags`` (one 32-bit epoch word per producer) and a small check area.  ``publish``
+    stores this rank's records into every peer's buffer and raises its flag there; ``merge`` waits
+    (bounded) for all producers of the step and finishes with the LSE merge + gate.  Before any
+    kernel touches a mapping the constructor proves it with blocking 4-byte runtime copies."""
 
     def __init__(self, ops, group, per_rank: int = 2, device="cuda"):
-        from torch.multiprocessing.reductions import reduce_tensor
+        import ctypes
 
         self.ops, self.group = ops, group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.per_rank = per_rank
         dev = torch.device(device)
+        lib = ops.lib
         self.n_slots = self.world * per_rank
-        self.slots = torch.zeros(2, self.n_slots, H_Q, PART, dtype=torch.float32, device=dev)
-        self.flags = torch.zeros(self.world, dtype=torch.int32, device=dev)
-        torch.cuda.synchronize(dev)
-        mine = (reduce_tensor(self.slots), reduce_tensor(self.flags))
-        everyone = [None] * self.world
-        dist.all_gather_object(everyone, mine, group=group)
-        self._peers = []  # keeps the mappings alive
-        slot_ptrs, flag_ptrs = [], []
-        for r, ((f_s, a_s), (f_f, a_f)) in enumerate(everyone):
-            if r == self.rank:
-                ps, pf = self.slots, self.flags
-            else:
-                ps, pf = f_s(*a_s), f_f(*a_f)
-            self._peers.append((ps, pf))
-            slot_ptrs.append(ps.data_ptr())
-            flag_ptrs.append(pf.data_ptr())
-        self.peer_slots = torch.tensor(slot_ptrs, dtype=torch.int64, device=dev)
-        self.peer_flags = torch.tensor(flag_ptrs, dtype=torch.int64, device=dev)
+        rec_bytes = H_Q * PART * 4
+        self.flags_off = 2 * self.n_slots * rec_bytes              # multiple of 256 bytes (24768 = 96.75 * 256: rounded below)
+        self.flags_off = (self.flags_off + 255) // 256 * 256
+        self.check_off = self.flags_off + 256 * ((4 * self.world + 255) // 256)
+        total = self.check_off + 256 * ((4 * self.world + 255) // 256)
+        with torch.cuda.device(dev):
+            base = ctypes.c_void_p()
+            handle = ctypes.create_string_buffer(64)
+            rc = lib.khq_b200_peer_alloc(total, ctypes.byref(base), handle)
+            if rc != 0:
+                raise RuntimeError(f"khq_b200_peer_alloc failed ({rc})")
+            self.base = int(base.value)
+            everyone = [None] * self.world
+            dist.all_gather_object(everyone, bytes(handle.raw), group=group)
+            self.peer_base = []
+            for r, h in enumerate(everyone):
+                if r == self.rank:
+                    self.peer_base.append(self.base)
+                    continue
+                p = ctypes.c_void_p()
+                rc = lib.khq_b200_peer_open(h, ctypes.byref(p))
+                if rc != 0:
+                    raise RuntimeError(f"khq_b200_peer_open of rank {r}'s buffer failed ({rc})")
+                self.peer_base.append(int(p.value))
+            # prove every mapping with runtime copies: write rank+1 into check[rank] of every peer ...
+            for r in range(self.world):
+                rc = lib.khq_b200_peer_poke(self.peer_base[r] + self.check_off + 4 * self.rank, self.rank + 1)
+                if rc != 0:
+                    raise RuntimeError(f"write through the mapping of rank {r}'s buffer failed ({rc})")
+            dist.barrier(group=group)
+            # ... and read back what the peers wrote here
+            for r in range(self.world):
+                v = ctypes.c_uint(0)
+                rc = lib.khq_b200_peer_peek(self.base + self.check_off + 4 * r, ctypes.byref(v))
+                if rc != 0 or v.value != r + 1:
+                    raise RuntimeError(f"rank {r}'s write did not arrive here (code {rc}, value {v.value})")
+        self.peer_slots = torch.tensor(self.peer_base, dtype=torch.int64, device=dev)
+        self.peer_flags = torch.tensor([b + self.flags_off for b in self.peer_base], dtype=torch.int64, device=dev)
+        self.rec_bytes = rec_bytes
         self.epoch = 0
         dist.barrier(group=group)
 
@@ -86,8 +110,20 @@ class PeerExchange:
 
     def merge(self, q_gate: torch.Tensor, out: torch.Tensor, max_polls: int = 0) -> None:
         par = self.epoch & 1
-        self.ops.merge_slots_wait_gate(self.slots[par], self.flags, self.world, self.epoch, self.n_slots, q_gate, out,
-                                       H_Q, D, max_polls)
+        self.ops.merge_slots_wait_gate(self.base + par * self.n_slots * self.rec_bytes, self.base + self.flags_off, self.world,
+                                       self.epoch, self.n_slots, q_gate, out, H_Q, D, max_polls)
+
+    def close(self) -> None:
+        """Unmap the peers' buffers and free this rank's (after a barrier: nobody may still write)."""
+        if getattr(self, "base", 0):
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)
+            for r, p in enumerate(self.peer_base):
+                if r != self.rank:
+                    self.ops.lib.khq_b200_peer_close(p)
+            dist.barrier(group=self.group)
+            self.ops.lib.khq_b200_peer_free(self.base)
+            self.base = 0
 
 
 class ContextParallelDecode:

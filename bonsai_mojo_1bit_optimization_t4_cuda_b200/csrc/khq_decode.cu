@@ -4,6 +4,8 @@
 //   khq_window_attn_kernel      raw fp16 ring window
 //   khq_merge_gate_kernel       LSE merge of the two regions + sigmoid output gate
 // and the launch_khq_* entry points with the reference's signatures.
+#include <string.h>
+
 #include "khq_decode.cuh"
 
 namespace khq {
@@ -1079,6 +1081,79 @@ extern "C" int launch_khq_merge_slots_gate_fp16(const void* partials, int n_slot
                                                       static_cast<__half*>(out));
     const cudaError_t err = cudaGetLastError();
     return (err == cudaSuccess) ? 0 : static_cast<int>(err);
+}
+
+// Kernels of the current device may only dereference another GPU's memory (an IPC mapping is made
+// in the exporting device's context) once peer access from the current device to it is enabled.
+extern "C" int khq_b200_enable_peer_access(int peer_device) {
+    int cur = 0;
+    cudaError_t e = cudaGetDevice(&cur);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (peer_device == cur) return 0;
+    int can = 0;
+    e = cudaDeviceCanAccessPeer(&can, cur, peer_device);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (!can) return -109;
+    e = cudaDeviceEnablePeerAccess(peer_device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    return (e == cudaSuccess) ? 0 : static_cast<int>(e);
+}
+
+// ---- peer-visible buffers (CUDA IPC), for the exchange above -----------------------------------
+// khq_b200_peer_alloc: cudaMalloc + zero fill on the current device and the 64-byte IPC handle
+// of the allocation.  khq_b200_peer_open: maps another process's allocation for the CURRENT
+// device (peer access between the two GPUs is enabled by the open itself).  Both return 0 or a
+// positive cudaError_t; -100 for null arguments.
+extern "C" int khq_b200_peer_alloc(size_t bytes, void** ptr_out, unsigned char* handle_out) {
+    if (!ptr_out || !handle_out || bytes == 0) return -100;
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    e = cudaMemset(p, 0, bytes);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return static_cast<int>(e);
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    memcpy(handle_out, &h, 64);
+    *ptr_out = p;
+    return 0;
+}
+extern "C" int khq_b200_peer_open(const unsigned char* handle, void** ptr_out) {
+    if (!handle || !ptr_out) return -100;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    void* p = nullptr;
+    const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    *ptr_out = p;
+    return 0;
+}
+extern "C" int khq_b200_peer_close(void* ptr) {
+    if (!ptr) return -100;
+    const cudaError_t e = cudaIpcCloseMemHandle(ptr);
+    return (e == cudaSuccess) ? 0 : static_cast<int>(e);
+}
+extern "C" int khq_b200_peer_free(void* ptr) {
+    if (!ptr) return -100;
+    const cudaError_t e = cudaFree(ptr);
+    return (e == cudaSuccess) ? 0 : static_cast<int>(e);
+}
+// Blocking 4-byte writes / reads through the runtime (no kernel): lets a host check a mapping before
+// any kernel dereferences it.
+extern "C" int khq_b200_peer_poke(void* dst, unsigned int value) {
+    const cudaError_t e = cudaMemcpy(dst, &value, 4, cudaMemcpyHostToDevice);
+    return (e == cudaSuccess) ? 0 : static_cast<int>(e);
+}
+extern "C" int khq_b200_peer_peek(const void* src, unsigned int* value_out) {
+    if (!value_out) return -100;
+    const cudaError_t e = cudaMemcpy(value_out, src, 4, cudaMemcpyDeviceToHost);
+    return (e == cudaSuccess) ? 0 : static_cast<int>(e);
 }
 
 extern "C" int launch_khq_publish_partials_fp32(const void* src, int n_records, const void* peer_slots,

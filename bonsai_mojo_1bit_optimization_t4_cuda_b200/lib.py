@@ -49,6 +49,13 @@ SIGNATURES = {
     "khq_b200_version": (c_char_p, []),
     "khq_b200_device_status": (c_int, []),
     "khq_b200_device_status_clear": (c_int, []),
+    "khq_b200_enable_peer_access": (c_int, [c_int]),
+    "khq_b200_peer_alloc": (c_int, [c_size_t, POINTER(c_void_p), c_char_p]),
+    "khq_b200_peer_open": (c_int, [c_char_p, POINTER(c_void_p)]),
+    "khq_b200_peer_close": (c_int, [_P]),
+    "khq_b200_peer_free": (c_int, [_P]),
+    "khq_b200_peer_poke": (c_int, [_P, c_uint]),
+    "khq_b200_peer_peek": (c_int, [_P, POINTER(c_uint)]),
     "launch_khq_publish_partials_fp32": (c_int, [_P, c_int, _P, _P, c_int, c_int, c_int, c_longlong, c_uint, _P]),
     "launch_khq_merge_slots_wait_gate_fp16": (c_int, [_P, _P, c_int, c_uint, c_int, _P, _P, c_int, c_int, c_uint, _P]),
 }

@@ -293,6 +293,22 @@ int khq_b200_device_status_clear(void);
  * becomes 3 and the launch still completes.  Epochs grow by one per step; a producer is at most one
  * step ahead of a consumer, so two parities of slots suffice.  No reference counterpart.
  * Return -100 (bad arguments), -103 (shape), -104 (alignment). */
+/* Enables peer access from the current device to `peer_device` (a CUDA IPC mapping of a peer's
+ * buffer lives in the peer's context; kernels of the current device may dereference it only after
+ * this).  0 = enabled (or already enabled, or the same device), -109 = the GPUs are not peers. */
+int khq_b200_enable_peer_access(int peer_device);
+/* Peer-visible buffers for that exchange.  khq_b200_peer_alloc: cudaMalloc + zero fill on the current
+ * device, returns the pointer and the 64-byte CUDA IPC handle of the allocation (to be sent to the
+ * other processes).  khq_b200_peer_open: maps another process's allocation for the current device
+ * (the open enables peer access between the two GPUs).  khq_b200_peer_close / _free undo them.
+ * khq_b200_peer_poke / _peek: blocking 4-byte write / read through the runtime, with which a host
+ * checks a mapping before any kernel uses it.  All return 0, a positive cudaError_t, or -100. */
+int khq_b200_peer_alloc(size_t bytes, void** ptr_out, unsigned char* handle_out);
+int khq_b200_peer_open(const unsigned char* handle, void** ptr_out);
+int khq_b200_peer_close(void* ptr);
+int khq_b200_peer_free(void* ptr);
+int khq_b200_peer_poke(void* dst, unsigned int value);
+int khq_b200_peer_peek(const void* src, unsigned int* value_out);
 int launch_khq_publish_partials_fp32(const void* src, int n_records, const void* peer_slots, const void* peer_flags,
                                      int world, int rank, int first_slot, long long parity_offset_records,
                                      unsigned int epoch, khq_stream_t stream);
