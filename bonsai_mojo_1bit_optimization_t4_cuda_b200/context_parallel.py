@@ -62,8 +62,11 @@ class PeerExchange:
         rec_bytes = H_Q * PART * 4
         self.flags_off = 2 * self.n_slots * rec_bytes              # multiple of 256 bytes (24768 = 96.75 * 256: rounded below)
         self.flags_off = (self.flags_off + 255) // 256 * 256
-        self.check_off = self.flags_off + 256 * ((4 * self.world + 255) // 256)
-        total = self.check_off + 256 * ((4 * self.world + 255) // 256)
+        # flags: word r = producer r's partials; word `world` = the owner's q_gate
+        self.check_off = self.flags_off + 256 * ((4 * (self.world + 1) + 255) // 256)
+        self.q_off = self.check_off + 256 * ((4 * self.world + 255) // 256)
+        self.q_bytes = H_Q * 2 * D * 2                               # (24, 512) fp16, one per parity
+        total = self.q_off + 2 * self.q_bytes
         with torch.cuda.device(dev):
             base = ctypes.c_void_p()
             handle = ctypes.create_string_buffer(64)
@@ -95,15 +98,32 @@ class PeerExchange:
                 rc = lib.khq_b200_peer_peek(self.base + self.check_off + 4 * r, ctypes.byref(v))
                 if rc != 0 or v.value != r + 1:
                     raise RuntimeError(f"rank {r}'s write did not arrive here (code {rc}, value {v.value})")
-        self.peer_slots = torch.tensor(self.peer_base, dtype=torch.int64, device=dev)
+        self.peer_bufs = torch.tensor(self.peer_base, dtype=torch.int64, device=dev)
+        self.peer_slots = self.peer_bufs
         self.peer_flags = torch.tensor([b + self.flags_off for b in self.peer_base], dtype=torch.int64, device=dev)
         self.rec_bytes = rec_bytes
         self.epoch = 0
         dist.barrier(group=group)
 
-    def publish(self, records: torch.Tensor) -> None:
-        """records: (per_rank, 24, 258) fp32 of this rank for the step that starts now."""
+    def begin_step(self) -> int:
+        """Advance to the next epoch (once per step on every rank); returns the parity in use."""
         self.epoch += 1
+        return self.epoch & 1
+
+    def publish_q(self, q_gate: torch.Tensor) -> None:
+        """On the owner of the query: store q_gate (24*512 fp16) into every rank's buffer."""
+        par = self.epoch & 1
+        self.ops.publish_bytes(q_gate, self.q_bytes, self.peer_bufs, self.q_off + par * self.q_bytes, self.peer_flags,
+                               self.world, self.world, self.epoch)
+
+    def wait_q(self, max_polls: int = 0) -> int:
+        """Queue a wait for this step's q_gate on the stream; returns its device address here."""
+        par = self.epoch & 1
+        self.ops.wait_flag(self.base + self.flags_off + 4 * self.world, self.epoch, max_polls)
+        return self.base + self.q_off + par * self.q_bytes
+
+    def publish(self, records: torch.Tensor) -> None:
+        """records: (per_rank, 24, 258) fp32 of this rank for the current step."""
         par = self.epoch & 1
         self.ops.publish_partials(records, self.per_rank, self.peer_slots, self.peer_flags, self.world, self.rank,
                                   self.rank * self.per_rank, par * self.n_slots, self.epoch)
@@ -166,7 +186,13 @@ class ContextParallelDecode:
         """q_gate: (24*512,) fp16, valid on ``owner`` (broadcast to the others unless the caller
         already did).  Returns the gated output (24*256,) fp16, identical on every rank."""
         ops, kv, tb = self.ops, self.kv, self.tables
-        if broadcast_q and self.world > 1:
+        if self.peer is not None:
+            self.peer.begin_step()
+            if broadcast_q:  # the owner's q_gate reaches the others through their buffers, no collective
+                if self.rank == self.owner:
+                    self.peer.publish_q(q_gate)
+                q_gate = self.peer.wait_q()
+        elif broadcast_q and self.world > 1:
             dist.broadcast(q_gate, src=dist.get_global_rank(self.group, self.owner), group=self.group)
         n = self.hi - self.lo
         if n > 0:

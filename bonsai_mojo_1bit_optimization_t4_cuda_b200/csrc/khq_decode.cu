@@ -663,6 +663,39 @@ khq_publish_partials_kernel(const float* __restrict__ src, int n_floats, float* 
     }
 }
 
+// Generic form of the same: `n16` 16-byte units from `src` to byte offset `dst_off` of every peer's
+// buffer, then the epoch into word `flag_index` of every peer's flag array.
+__global__ void __launch_bounds__(256)
+khq_publish_bytes_kernel(const uint4* __restrict__ src, int n16, unsigned char* const* __restrict__ peer_bufs,
+                         long long dst_off, unsigned int* const* __restrict__ peer_flags, int flag_index,
+                         unsigned int epoch) {
+    const int p = blockIdx.x;
+    uint4* dst = reinterpret_cast<uint4*>(peer_bufs[p] + dst_off);
+    for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = src[i];
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned int* flag = peer_flags[p] + flag_index;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
+    }
+}
+
+// One thread waits (bounded) until *flag >= epoch (modulo 2^32): stream-orders the kernels behind it
+// after a peer's publish.  Status word 3 when the wait runs out.
+__global__ void khq_wait_flag_kernel(const unsigned int* __restrict__ flag, unsigned int epoch, unsigned int max_polls) {
+    bool seen = false;
+    for (unsigned int it = 0; it < max_polls; ++it) {
+        unsigned int v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if ((int)(v - epoch) >= 0) {
+            seen = true;
+            break;
+        }
+        __nanosleep(64);
+    }
+    if (!seen) atomicExch(&g_status, 3);
+}
+
 // The slot merge of khq_merge_slots_gate_kernel, preceded by a bounded wait for the `n_flags`
 // producers of this step (flag >= epoch, compared modulo 2^32).  Slots are read around L1 (peers
 // wrote them).  A wait that runs out sets the status word to 3 and the CTA still finishes.
@@ -1166,6 +1199,25 @@ extern "C" int launch_khq_publish_partials_fp32(const void* src, int n_records, 
     khq_publish_partials_kernel<<<(unsigned)world, 256, 0, stream>>>(
         static_cast<const float*>(src), n_records * HQ * PART, static_cast<float* const*>(peer_slots),
         static_cast<unsigned int* const*>(peer_flags), off, rank, epoch);
+    const cudaError_t err = cudaGetLastError();
+    return (err == cudaSuccess) ? 0 : static_cast<int>(err);
+}
+
+extern "C" int launch_khq_publish_bytes(const void* src, size_t bytes, const void* peer_bufs, long long dst_byte_offset,
+                                        const void* peer_flags, int flag_index, int world, unsigned int epoch,
+                                        cudaStream_t stream) {
+    if (!src || !peer_bufs || !peer_flags || bytes == 0 || world <= 0 || flag_index < 0 || dst_byte_offset < 0) return -100;
+    if (!aligned(src, 16) || (bytes & 15) != 0 || (dst_byte_offset & 15) != 0) return -104;
+    khq_publish_bytes_kernel<<<(unsigned)world, 256, 0, stream>>>(
+        static_cast<const uint4*>(src), (int)(bytes / 16), static_cast<unsigned char* const*>(peer_bufs), dst_byte_offset,
+        static_cast<unsigned int* const*>(peer_flags), flag_index, epoch);
+    const cudaError_t err = cudaGetLastError();
+    return (err == cudaSuccess) ? 0 : static_cast<int>(err);
+}
+
+extern "C" int launch_khq_wait_flag(const void* flag, unsigned int epoch, unsigned int max_polls, cudaStream_t stream) {
+    if (!flag) return -100;
+    khq_wait_flag_kernel<<<1, 1, 0, stream>>>(static_cast<const unsigned int*>(flag), epoch, max_polls ? max_polls : (1u << 22));
     const cudaError_t err = cudaGetLastError();
     return (err == cudaSuccess) ? 0 : static_cast<int>(err);
 }

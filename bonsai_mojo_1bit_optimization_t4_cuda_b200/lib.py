@@ -57,6 +57,8 @@ SIGNATURES = {
     "khq_b200_peer_poke": (c_int, [_P, c_uint]),
     "khq_b200_peer_peek": (c_int, [_P, POINTER(c_uint)]),
     "launch_khq_publish_partials_fp32": (c_int, [_P, c_int, _P, _P, c_int, c_int, c_int, c_longlong, c_uint, _P]),
+    "launch_khq_publish_bytes": (c_int, [_P, c_size_t, _P, c_longlong, _P, c_int, c_int, c_uint, _P]),
+    "launch_khq_wait_flag": (c_int, [_P, c_uint, c_uint, _P]),
     "launch_khq_merge_slots_wait_gate_fp16": (c_int, [_P, _P, c_int, c_uint, c_int, _P, _P, c_int, c_int, c_uint, _P]),
 }
 

@@ -72,6 +72,15 @@ class CudaOps:
                                                        int(epoch) & 0xFFFFFFFF, current_stream())
         check("launch_khq_publish_partials_fp32", rc)
 
+    def publish_bytes(self, src, nbytes, peer_bufs, dst_byte_offset, peer_flags, flag_index, world, epoch):
+        rc = self.lib.launch_khq_publish_bytes(ptr(src), int(nbytes), ptr(peer_bufs), int(dst_byte_offset), ptr(peer_flags),
+                                               int(flag_index), int(world), int(epoch) & 0xFFFFFFFF, current_stream())
+        check("launch_khq_publish_bytes", rc)
+
+    def wait_flag(self, flag, epoch, max_polls=0):
+        rc = self.lib.launch_khq_wait_flag(ptr(flag), int(epoch) & 0xFFFFFFFF, int(max_polls), current_stream())
+        check("launch_khq_wait_flag", rc)
+
     def merge_slots_wait_gate(self, partials, flags, n_flags, epoch, n_slots, q_gate, out, H_q, d, max_polls=0):
         rc = self.lib.launch_khq_merge_slots_wait_gate_fp16(ptr(partials), ptr(flags), int(n_flags), int(epoch) & 0xFFFFFFFF,
                                                             int(n_slots), ptr(q_gate), ptr(out), int(H_q), int(d),

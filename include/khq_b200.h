@@ -312,6 +312,15 @@ int khq_b200_peer_peek(const void* src, unsigned int* value_out);
 int launch_khq_publish_partials_fp32(const void* src, int n_records, const void* peer_slots, const void* peer_flags,
                                      int world, int rank, int first_slot, long long parity_offset_records,
                                      unsigned int epoch, khq_stream_t stream);
+/* launch_khq_publish_bytes: the same publish for any payload (here: the owner's q_gate): `bytes`
+ * (multiple of 16) from `src` to byte offset dst_byte_offset of every peer's buffer (peer_bufs:
+ * device array of `world` base pointers), then `epoch` into word flag_index of every peer's flag
+ * array.  launch_khq_wait_flag: a one-thread kernel that waits (bounded as above) until
+ * *flag >= epoch, so that the kernels queued behind it on the stream see the payload.
+ * Return -100 (bad arguments), -104 (alignment). */
+int launch_khq_publish_bytes(const void* src, size_t bytes, const void* peer_bufs, long long dst_byte_offset,
+                             const void* peer_flags, int flag_index, int world, unsigned int epoch, khq_stream_t stream);
+int launch_khq_wait_flag(const void* flag, unsigned int epoch, unsigned int max_polls, khq_stream_t stream);
 int launch_khq_merge_slots_wait_gate_fp16(const void* partials, const void* flags, int n_flags, unsigned int epoch,
                                           int n_slots, const void* q_gate, void* out, int H_q, int d,
                                           unsigned int max_polls, khq_stream_t stream);

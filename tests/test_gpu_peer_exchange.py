@@ -50,6 +50,34 @@ def test_publish_then_merge_equals_gathered_merge(cuda_ops, world):
     assert cuda_ops.lib.khq_b200_device_status() == 0
 
 
+def test_publish_bytes_and_wait_flag(cuda_ops):
+    """The owner's q_gate travels the same way: bytes into every buffer, then a flag word; the
+    consumer queues a one-thread wait in front of the kernels that read it."""
+    import torch
+
+    world = 3
+    bufs = [torch.zeros(65536, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    flags = [torch.zeros(world + 1, dtype=torch.int32, device="cuda") for _ in range(world)]
+    peer_bufs = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device="cuda")
+    peer_flags = torch.tensor([f.data_ptr() for f in flags], dtype=torch.int64, device="cuda")
+    qg = torch.randn(H_Q * 2 * D, device="cuda").half()
+    assert cuda_ops.lib.khq_b200_device_status_clear() >= 0
+    cuda_ops.publish_bytes(qg, qg.numel() * 2, peer_bufs, 4096, peer_flags, world, world, 7)
+    for r in range(world):
+        cuda_ops.wait_flag(flags[r][world:], 7)
+        torch.cuda.synchronize()
+        assert torch.equal(bufs[r][4096:4096 + qg.numel() * 2].view(torch.float16), qg)
+        assert flags[r].tolist() == [0] * world + [7]
+    assert cuda_ops.lib.khq_b200_device_status() == 0
+    cuda_ops.wait_flag(flags[0][world:], 8, max_polls=1000)  # nothing publishes epoch 8
+    torch.cuda.synchronize()
+    assert cuda_ops.lib.khq_b200_device_status_clear() == 3
+    lib = cuda_ops.lib
+    assert lib.launch_khq_publish_bytes(0, 16, 16, 0, 16, 0, 2, 1, 0) == -100
+    assert lib.launch_khq_publish_bytes(16, 24, 16, 0, 16, 0, 2, 1, 0) == -104
+    assert lib.launch_khq_wait_flag(0, 1, 0, 0) == -100
+
+
 def test_wait_runs_out_and_reports(cuda_ops):
     """A producer that never publishes: the merge kernel gives up after its poll budget, records
     status 3 and returns; the context stays usable."""
