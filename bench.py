@@ -431,7 +431,10 @@ def run_prefill(args, rank, world, local_rank):
                                    "d 256, kernel %s" % (B, T, args.prefill_kernel),
                        "l2": "a 256 MB buffer is rewritten between timed launches", "world": world},
             "roofline": {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
-                         "traffic": None, "algorithmic_flops_per_launch": flops,
+                         # dram bytes of an ncu capture of 1 prompt x 8192 tokens (235.1 MB read + 73.8 MB written, the
+                         # tensors themselves: K/V tiles are re-read from L2), scaled by the tensor bytes of this run
+                         "traffic": 309.0e6 * (B * T) / 8192.0 if args.prefill_kernel == "tc5" else None,
+                         "algorithmic_flops_per_launch": flops,
                          "peak_source": "MEASURED_PEAKS.json bf16_tflops (burst)" if peaks else "fallback"},
             "gpu_launches": args.steps, "clocks": clocks, "device_status": status}), flush=True)
     if world > 1:
