@@ -150,3 +150,33 @@ def test_prefill_bf16_vs_torch_fp32(cuda_ops, T, mode):
     err = (out.float() - ref).abs()
     lim = 4e-3 + 2e-2 * ref.abs()
     assert bool((err <= lim).all()), f"T={T}: max abs {err.max().item():.3e}, worst excess {(err - lim).max().item():.3e}"
+
+
+@pytest.mark.parametrize("entry", ["launch_khq_gqa_prefill_tc5_fp16", "launch_khq_gqa_prefill_mma_fp16"])
+def test_prefill_honours_batch_strides(cuda_ops, oracle, entry):
+    """Batch strides larger than one prompt (each prompt sits in a max_seq-sized cache slab, as the
+    reference's KV cache rows do): rows past T of a slab must be neither read into the result nor
+    written."""
+    import torch
+
+    B, T, S = 3, 150, 256  # S = rows per slab
+    rng = np.random.default_rng(77)
+    qg = torch.from_numpy(rng.standard_normal((B, S, H_Q, 2 * D)).astype(np.float16)).cuda()
+    k = torch.from_numpy((rng.standard_normal((B, S, H_KV, D)) * 0.25).astype(np.float16)).cuda()
+    v = torch.from_numpy(rng.standard_normal((B, S, H_KV, D)).astype(np.float16)).cuda()
+    k[:, T:] = float("nan")  # anything read from beyond the prompt would poison the output
+    v[:, T:] = float("nan")
+    out = torch.full((B, S, H_Q, D), -7.0, dtype=torch.float16, device="cuda")
+    fn = getattr(cuda_ops.lib, entry)
+    rc = fn(qg.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, T, H_Q, H_KV, D, SCALE, S * H_Q * 2 * D,
+            S * H_KV * D, S * H_Q * D, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert cuda_ops.lib.khq_b200_prefill_status() == 0
+    assert bool((out[:, T:] == -7.0).all()), "rows past the prompt were written"
+    got = out[:, :T].float().cpu().numpy()
+    assert np.isfinite(got).all()
+    for b in range(B):
+        ref = oracle.gqa_prefill(qg[b, :T].cpu().numpy(), k[b, :T].cpu().numpy(), v[b, :T].cpu().numpy(), T, H_Q, H_KV, D, SCALE)
+        ok, mx, exc = cases.attention_close(got[b], ref)
+        assert ok, f"{entry} batch {b}: max abs {mx:.3e}, excess {exc:.3e}"
