@@ -519,6 +519,26 @@ def run_single(args, rank, world, local_rank):
     with torch.cuda.graph(graph, stream=side):
         step_with(ours, side.cuda_stream)
     us_graph = timed(graph.replay, n_it)
+    # the same step through the single-call entry (ring appends + both regions + merge + gate)
+    kr = torch.randn(1024, generator=g, device=dev).half()
+    vn = torch.randn(1024, generator=g, device=dev).half()
+    ku = torch.randn(1024, generator=g, device=dev).half()
+    ring_u = torch.zeros(256 * 1024, dtype=torch.float16, device=dev)
+    tabs = dict(cents_k=tab["cents_k"], cents_v=tab["cents_v"], vq=tab["vq"], rotor_k=tab["rotor_k"], rotor_v=tab["rotor_v"],
+                d_k=tab["d_k"], d_v=tab["d_v"])
+
+    def fused_step():
+        ops.decode_step(qg, kr, vn, ku, ring_k, ring_v, ring_u, kv, tabs, ac, ap, out, c_len, win_start, win_len, 256, 1,
+                        1.0 / 16.0, tb.alpha_k, tb.alpha_v, 1e7)
+
+    us_fused = timed(fused_step, n_it)
+    graph2 = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        fused_step()
+    torch.cuda.synchronize()
+    with torch.cuda.graph(graph2, stream=side):
+        fused_step()
+    us_fused_graph = timed(graph2.replay, n_it)
     ref_us = None
     ref_path = ROOT / "oracle" / "_ref" / "libbonsai_ref_sm100a.so"
     if ref_path.exists():
@@ -540,7 +560,8 @@ def run_single(args, rank, world, local_rank):
             "config": {"workload": "BASELINE configs[0]: one sequence, 384 compressed + 128 raw tokens, 1 layer, splits 1, "
                                    "three drop-in launches per step", "l2": "862 KB working set: L2-resident by nature (a "
                        "latency case, not a bandwidth one)"},
-            "graph_replay_us": us_graph, "reference_kernels_sm100a_us": ref_us,
+            "graph_replay_us": us_graph, "fused_entry_us": us_fused, "fused_entry_graph_replay_us": us_fused_graph,
+            "reference_kernels_sm100a_us": ref_us,
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
                          "algorithmic_bytes_per_step": b_alg, "note": "launch-latency bound at this size"},
             "gpu_launches": 3 * n_it, "clocks": clocks, "device_status": ours.khq_b200_device_status()}), flush=True)

@@ -436,10 +436,14 @@ __global__ void __launch_bounds__(D) khq_attn_reduce_kernel(const float* __restr
 // ------------------------------------------------------------------------------------------
 // Window tokens s = first, first+step, ... < win_hi of this warp: slot (win_start + s) % ring_cap,
 // rows token-major (slot*H_kv + kv)*D, K already RoPE'd.
+// When new_s >= 0, window token new_s is read from new_k / new_v (one token, H_kv*D halfs each)
+// instead of its ring slot: the fused step kernel appends it to the ring while the window runs.
 __device__ __forceinline__ void window_range(const __half* __restrict__ q, const __half* __restrict__ ring_k,
                                              const __half* __restrict__ ring_v, int win_start, int first,
                                              int step, int win_hi, int ring_cap, float scale, int kvh,
-                                             int lane, WarpState& st) {
+                                             int lane, WarpState& st, int new_s = -1,
+                                             const __half* __restrict__ new_k = nullptr,
+                                             const __half* __restrict__ new_v = nullptr) {
     float qv[NREP][8];
 #pragma unroll
     for (int h = 0; h < NREP; ++h) {
@@ -452,8 +456,9 @@ __device__ __forceinline__ void window_range(const __half* __restrict__ q, const
     for (int s = first; s < win_hi; s += step) {
         const int slot = (win_start + s) % ring_cap;
         const size_t off = ((size_t)slot * HKV + kvh) * D + lane * 8;
-        const uint4 kr = *reinterpret_cast<const uint4*>(ring_k + off);
-        const uint4 vr = *reinterpret_cast<const uint4*>(ring_v + off);
+        const bool fresh = (s == new_s);
+        const uint4 kr = *reinterpret_cast<const uint4*>(fresh ? new_k + (size_t)kvh * D + lane * 8 : ring_k + off);
+        const uint4 vr = *reinterpret_cast<const uint4*>(fresh ? new_v + (size_t)kvh * D + lane * 8 : ring_v + off);
         const __half* hk = reinterpret_cast<const __half*>(&kr);
         const __half* hv = reinterpret_cast<const __half*>(&vr);
         float sc[NREP];
@@ -598,6 +603,68 @@ khq_batched_merge_gate_kernel(const KhqSeqDesc* __restrict__ descs, const float*
     const float val = num / (den + 1e-8f);
     const float g = __half2float(d.q_gate[(size_t)h * 2 * D + D + dd]);
     d.out[(size_t)h * D + dd] = __float2half(val * (1.0f / (1.0f + __expf(-g))));
+}
+
+// Fused tail of a decode step for one sequence: appends the step's token to the three rings (K
+// RoPE'd, V, K un-RoPE'd; CTA 0, while every CTA reads that token straight from the inputs), runs
+// the raw-window attention over win_len tokens (the new one is the last), then the cluster's rank-0
+// CTA merges the window partial with the compressed-region partial attn_c (when has_c), divides by
+// (den + 1e-8), applies the sigmoid gate and stores fp16 -- the math of khq_window_attn_kernel +
+// khq_merge_gate_kernel in one launch.
+__global__ void __launch_bounds__(DEC_THREADS, 1)
+khq_window_step_kernel(const __half* __restrict__ q, __half* __restrict__ ring_k, __half* __restrict__ ring_v,
+                       __half* __restrict__ ring_u, const __half* __restrict__ new_k, const __half* __restrict__ new_v,
+                       const __half* __restrict__ new_u, const float* __restrict__ attn_c, __half* __restrict__ out,
+                       int win_start, int win_len, int ring_cap, float scale, int has_c) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kvh = warp & 3, sub = warp >> 2;
+    const int csize = (int)cluster.num_blocks(), crank = (int)cluster.block_rank();
+    const int new_s = win_len - 1;
+    if (crank == 0) {  // ring appends: 3 rows of H_kv*D halfs = 3 x 128 sixteen-byte chunks
+        const int slot = (win_start + new_s) % ring_cap;
+        const size_t row = (size_t)slot * HKV * D;
+        for (int c = tid; c < 3 * (HKV * D / 8); c += DEC_THREADS) {
+            const int which = c / (HKV * D / 8), i = c % (HKV * D / 8);
+            const __half* src = which == 0 ? new_k : (which == 1 ? new_v : new_u);
+            __half* dst = which == 0 ? ring_k : (which == 1 ? ring_v : ring_u);
+            if (src != nullptr && dst != nullptr)
+                reinterpret_cast<uint4*>(dst + row)[i] = reinterpret_cast<const uint4*>(src)[i];
+        }
+    }
+    WarpState st;
+    st.init();
+    window_range(q, ring_k, ring_v, win_start, crank * DEC_WPK + sub, csize * DEC_WPK, win_len, ring_cap, scale, kvh,
+                 lane, st, new_s, new_k, new_v);
+    merge_cta_and_cluster(st, reinterpret_cast<float*>(smem), kvh, sub, lane);
+    if (crank == 0 && sub == 0) {
+#pragma unroll
+        for (int h = 0; h < NREP; ++h) {
+            const int head = kvh * NREP + h;
+            float wsc = 1.0f, csc = 0.0f, den = st.l[h];
+            const float* cc = attn_c + (size_t)head * PART;
+            if (has_c) {
+                const float mc = cc[D], mw = st.m[h];
+                const float M = fmaxf(mc, mw);
+                csc = __expf(mc - M);
+                wsc = __expf(mw - M);
+                den = cc[D + 1] * csc + st.l[h] * wsc;
+            }
+            const float inv = 1.0f / (den + 1e-8f);
+            const uint4 gr = *reinterpret_cast<const uint4*>(q + (size_t)head * 2 * D + D + lane * 8);
+            const __half* hg = reinterpret_cast<const __half*>(&gr);
+            __half o8[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float num = st.acc[h][j] * wsc;
+                if (has_c) num = cc[lane * 8 + j] * csc + num;
+                const float g = __half2float(hg[j]);
+                o8[j] = __float2half(num * inv * (1.0f / (1.0f + __expf(-g))));
+            }
+            *reinterpret_cast<uint4*>(out + (size_t)head * D + lane * 8) = *reinterpret_cast<const uint4*>(o8);
+        }
+    }
 }
 
 // LSE merge of the two regions, /(den + 1e-8), sigmoid gate, fp16 store.
@@ -778,6 +845,7 @@ static cudaError_t ensure_smem_attrs() {
     if ((e = cudaFuncSetAttribute(khq_attn_compressed_mma_kernel, attr, M2_SM_TOTAL)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(khq_window_attn_kernel, attr, 2 * HKV * MERGE_FLOATS * 4)) != cudaSuccess)
         return e;
+    if ((e = cudaFuncSetAttribute(khq_window_step_kernel, attr, 2 * HKV * MERGE_FLOATS * 4)) != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) done[dev] = true;
     return cudaSuccess;
 }
@@ -955,6 +1023,44 @@ extern "C" int launch_khq_merge_gate_fp16(const void* attn_c, const void* attn_w
         static_cast<const float*>(attn_c), static_cast<const float*>(attn_w),
         static_cast<const __half*>(q_gate), static_cast<__half*>(out), H_q, d, has_w);
     const cudaError_t err = cudaGetLastError();
+    return (err == cudaSuccess) ? 0 : static_cast<int>(err);
+}
+
+// One decode step of one sequence in two or three launches: compressed-region attention over
+// c_len tokens (launch_khq_attn_fp16 with its arguments; skipped when c_len == 0), then the fused
+// ring append + window attention + merge + gate kernel.  win_len counts the step's own token,
+// which is appended at slot (win_start + win_len - 1) % ring_cap.
+extern "C" int launch_khq_decode_step_fp16(
+    const void* q_gate, const void* k_roped, const void* v_new, const void* k_unroped, void* ring_k, void* ring_v,
+    void* ring_u, const void* k_payload, const void* v_payload, const void* v_shared_meta, const void* k_mask,
+    const void* k_norms, const void* k_r_norms, const void* v_norms, const void* v_r_norms, const void* centroids_k,
+    const void* centroids_v, const void* vq_centroids, const void* k_rotor, const void* v_rotor, const void* d_vec_k,
+    const void* d_vec_v, void* attn_c, void* attn_partial, void* out, int c_len, int win_start, int win_len, int ring_cap,
+    int num_splits, float scale, float alpha_k, float alpha_v, float rope_base, cudaStream_t stream) {
+    if (!q_gate || !k_roped || !v_new || !ring_k || !ring_v || !attn_c || !out || win_len <= 0 || c_len < 0) return -100;
+    if (ring_cap <= 0 || win_len > ring_cap) return -103;
+    const void* al[] = {q_gate, k_roped, v_new, k_unroped, ring_k, ring_v, ring_u, out};
+    for (const void* p : al)
+        if (p && !aligned(p, 16)) return -104;
+    if (!aligned(attn_c, 8)) return -104;
+    if (c_len > 0) {
+        const int rc = launch_khq_attn_fp16(q_gate, k_payload, v_payload, v_shared_meta, k_mask, k_norms, k_r_norms, v_norms,
+                                            v_r_norms, centroids_k, centroids_v, vq_centroids, k_rotor, v_rotor, d_vec_k,
+                                            d_vec_v, attn_c, attn_partial, HQ, HQ, 1, c_len, c_len, NREP, scale, alpha_k,
+                                            alpha_v, rope_base, 0, num_splits, stream);
+        if (rc != 0) return rc;
+    }
+    cudaError_t err = ensure_smem_attrs();
+    if (err != cudaSuccess) return static_cast<int>(err);
+    int cluster = (win_len + DEC_WPK * 4 - 1) / (DEC_WPK * 4);
+    if (cluster < 1) cluster = 1;
+    if (cluster > 8) cluster = 8;
+    err = launch_cluster(khq_window_step_kernel, (unsigned)cluster, (unsigned)cluster, (size_t)(2 * HKV * MERGE_FLOATS * 4),
+                         stream, (unsigned)DEC_THREADS, static_cast<const __half*>(q_gate), static_cast<__half*>(ring_k),
+                         static_cast<__half*>(ring_v), static_cast<__half*>(ring_u), static_cast<const __half*>(k_roped),
+                         static_cast<const __half*>(v_new), static_cast<const __half*>(k_unroped),
+                         static_cast<const float*>(attn_c), static_cast<__half*>(out), win_start, win_len, ring_cap, scale,
+                         c_len > 0 ? 1 : 0);
     return (err == cudaSuccess) ? 0 : static_cast<int>(err);
 }
 

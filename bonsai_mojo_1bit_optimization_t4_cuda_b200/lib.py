@@ -34,6 +34,7 @@ SIGNATURES = {
     "launch_khq_attn_static_fp16": (
         c_int, [_P] * 17 + [c_int] * 5 + [c_float, c_float, c_float, c_float, c_int, c_int, _P]),
     "launch_khq_merge_slots_gate_fp16": (c_int, [_P, c_int, _P, _P, c_int, c_int, _P]),
+    "launch_khq_decode_step_fp16": (c_int, [_P] * 25 + [c_int] * 5 + [c_float] * 4 + [_P]),
     "launch_khq_gqa_prefill_fp16": (
         c_int, [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_longlong, c_longlong, c_longlong, _P]),
     "launch_khq_gqa_prefill_tc5_fp16": (

@@ -65,6 +65,20 @@ class CudaOps:
                                                        int(H_q), int(d), current_stream())
         check("launch_khq_merge_slots_gate_fp16", rc)
 
+    # -- launch_khq_decode_step_fp16: ring appends + both regions + merge + gate, one call ----------
+    def decode_step(self, q_gate, k_roped, v_new, k_unroped, ring_k, ring_v, ring_u, kv, tables, attn_c, attn_partial, out,
+                    c_len, win_start, win_len, ring_cap, num_splits, scale, alpha_k, alpha_v, rope_base):
+        """kv: dict of the eight payload arrays (k_payload, v_payload, v_shared_meta, k_mask, k_norms,
+        k_r_norms, v_norms, v_r_norms); tables: dict (cents_k, cents_v, vq, rotor_k, rotor_v, d_k, d_v)."""
+        rc = self.lib.launch_khq_decode_step_fp16(
+            ptr(q_gate), ptr(k_roped), ptr(v_new), ptr(k_unroped), ptr(ring_k), ptr(ring_v), ptr(ring_u),
+            ptr(kv["k_payload"]), ptr(kv["v_payload"]), ptr(kv["v_shared_meta"]), ptr(kv["k_mask"]), ptr(kv["k_norms"]),
+            ptr(kv["k_r_norms"]), ptr(kv["v_norms"]), ptr(kv["v_r_norms"]), ptr(tables["cents_k"]), ptr(tables["cents_v"]),
+            ptr(tables["vq"]), ptr(tables["rotor_k"]), ptr(tables["rotor_v"]), ptr(tables["d_k"]), ptr(tables["d_v"]),
+            ptr(attn_c), ptr(attn_partial), ptr(out), int(c_len), int(win_start), int(win_len), int(ring_cap),
+            int(num_splits), float(scale), float(alpha_k), float(alpha_v), float(rope_base), current_stream())
+        check("launch_khq_decode_step_fp16", rc)
+
     # -- peer-memory exchange of context-parallel partials ----------------------------------------
     def publish_partials(self, src, n_records, peer_slots, peer_flags, world, rank, first_slot, parity_offset_records, epoch):
         rc = self.lib.launch_khq_publish_partials_fp32(ptr(src), int(n_records), ptr(peer_slots), ptr(peer_flags), int(world),

@@ -297,6 +297,36 @@ class KhqRuntime:
         self._tock(KHQ_P_MERGE, t0)
         return True
 
+    # ------------------------------------------------------------------ fused step (addition)
+    def khq_step_fused(self, layer_idx: int, q_gate_dev, k_unroped_dev, k_roped_dev, v_dev, out_dev, scale: float) -> bool:
+        """``khq_capture_unroped`` + ``khq_step`` of one token through ``launch_khq_decode_step_fp16``:
+        the three ring appends, both attention regions, the merge and the gate in two or three
+        launches (and one host call) instead of seven.  A step on which a compression event is due
+        takes the classic sequence (the event sits between the append and the attention).  The state
+        afterwards is the one the classic calls leave."""
+        if not self.active or not self.ready or layer_idx < 0 or layer_idx >= KHQ_MAX_LAYERS:
+            return False
+        L = self.layers[layer_idx]
+        if not L.ready:
+            return False
+        window_after = L.write_pos + 1 - L.boundary
+        event_due = window_after >= KHQ_WATERMARK and L.boundary + KHQ_CHUNK <= L.cap
+        if event_due or not hasattr(self.ops, "decode_step"):
+            self.khq_capture_unroped(layer_idx, k_unroped_dev)
+            return self.khq_step(layer_idx, q_gate_dev, k_roped_dev, v_dev, out_dev, scale)
+        T = L.t
+        c_len = L.boundary
+        kv = dict(k_payload=T["kpay"], v_payload=T["vpay"], v_shared_meta=T["vsm"], k_mask=T["kmask"], k_norms=T["knorm"],
+                  k_r_norms=T["krn"], v_norms=T["vnorm"], v_r_norms=T["vrn"])
+        tab = dict(cents_k=T["ck"], cents_v=T["cv"], vq=T["vq"], rotor_k=T["rk"], rotor_v=T["rv"], d_k=T["dk"], d_v=T["dv"])
+        t0 = self._tick()
+        self.ops.decode_step(q_gate_dev, k_roped_dev, v_dev, k_unroped_dev, T["ring_k"], T["ring_v"], T["ring_u"], kv, tab,
+                             T["ac"], T["ap"], out_dev, c_len, c_len % KHQ_RING, window_after, KHQ_RING,
+                             self._khq_split_count(c_len) if c_len > 0 else 1, scale, L.alpha_k, L.alpha_v, ROPE_BASE)
+        self._tock(KHQ_P_ATTN, t0)
+        L.write_pos += 1
+        return True
+
     # ------------------------------------------------------------------ prompt prefill (addition)
     def khq_prefill(self, layer_idx: int, q_gate_dev, k_unroped_dev, k_roped_dev, v_dev, out_dev, scale: float) -> bool:
         """Whole-prompt path for one layer: causal GQA attention of all T prompt rows at once

@@ -189,6 +189,26 @@ int launch_khq_prestep_fp16(void* q_gate, void* k, const void* v, const void* q_
                             int H_q, int H_kv, int d, int rotary_dim, int pos, float rope_theta,
                             float rms_eps, int has_norms, khq_stream_t stream);
 
+/* ---- One decode step of one sequence in two or three launches ------------------------------
+ * What khq_step does between two compression events (src/khq/runtime.mojo:503-612: three ring
+ * appends, launch_khq_attn_fp16 (+ its split reduce), launch_khq_window_attn_fp16,
+ * launch_khq_merge_gate_fp16: seven launches there) as one call: the compressed-region attention over
+ * c_len tokens with `num_splits` splits (skipped when c_len == 0; attn_c (24, 258) fp32 and
+ * attn_partial (24, num_splits, 258) fp32 are the caller's scratch), then ONE kernel that appends
+ * the step's token (k_roped, v_new, k_unroped: 4*256 halfs each; k_unroped / ring_u may be null) to
+ * the rings at slot (win_start + win_len - 1) % ring_cap, runs the raw-window attention over the
+ * win_len newest tokens (the step's own token included), merges with attn_c, divides by
+ * (den + 1e-8), applies the sigmoid gate and writes out (24, 256) fp16.  Shapes are Bonsai-27B's
+ * (24 / 4 heads, d 256).  Returns -100 (bad arguments), -103 (win_len > ring_cap), -104 (alignment)
+ * or launch_khq_attn_fp16's codes. */
+int launch_khq_decode_step_fp16(
+    const void* q_gate, const void* k_roped, const void* v_new, const void* k_unroped, void* ring_k, void* ring_v,
+    void* ring_u, const void* k_payload, const void* v_payload, const void* v_shared_meta, const void* k_mask,
+    const void* k_norms, const void* k_r_norms, const void* v_norms, const void* v_r_norms, const void* centroids_k,
+    const void* centroids_v, const void* vq_centroids, const void* k_rotor, const void* v_rotor, const void* d_vec_k,
+    const void* d_vec_v, void* attn_c, void* attn_partial, void* out, int c_len, int win_start, int win_len, int ring_cap,
+    int num_splits, float scale, float alpha_k, float alpha_v, float rope_base, khq_stream_t stream);
+
 /* ---- Prefill: causal GQA attention + sigmoid gate over a whole prompt --------------------
  * The math of the reference's fp16-KV attention kernel (gqa_attention_sm75_gpu,
  * src/kernels/elementwise_sm75.mojo:1091-1231), which the reference launches once per prompt

@@ -191,3 +191,60 @@ def test_checkpoint_resume_is_bit_identical(cuda_ops, tmp_path, monkeypatch):
     for key, rb in KhqRuntime._STATE_ROW_ARRAYS:
         a, b = rt.layers[3].t[key].view(torch.uint8)[:rows * rb], rt2.layers[3].t[key].view(torch.uint8)[:rows * rb]
         assert torch.equal(a, b), key
+
+
+def test_fused_step_matches_the_classic_sequence(cuda_ops, monkeypatch):
+    """khq_step_fused (launch_khq_decode_step_fp16: appends + both regions + merge + gate in one
+    call) against khq_capture_unroped + khq_step on the same inputs, 420 steps across three
+    compression events: outputs within the attention bar (the merge is fused into the window kernel,
+    so the last fp32 roundings differ), rings and code words bit-identical, same bookkeeping."""
+    import torch
+
+    from bonsai_mojo_1bit_optimization_t4_cuda_b200.runtime import KhqRuntime
+
+    monkeypatch.setenv("BONSAI_KHQ_SPLITS", "8")
+    n = 420
+    case = cases.make_case(cases.synth.seed_for(1, 21), n, "calib", layer_id=3)
+    rts = []
+    for _ in range(2):
+        rt = KhqRuntime(cuda_ops, device="cuda")
+        assert rt.khq_activate([case["tables"]], max_seq=1024)
+        rt.khq_init_layer(3, H_Q, H_KV, D)
+        rts.append(rt)
+    classic, fused = rts
+    worst = 0.0
+    for t in range(n):
+        qg = torch.from_numpy(cases.synth.make_q_gate(np.random.default_rng(9000 + t), t)).cuda()
+        ku = torch.from_numpy(case["k_unroped"][t]).cuda()
+        kr = torch.from_numpy(case["k_roped"][t]).cuda()
+        v = torch.from_numpy(case["v"][t]).cuda()
+        oa = torch.zeros(H_Q * D, dtype=torch.float16, device="cuda")
+        ob = torch.full((H_Q * D,), float("nan"), dtype=torch.float16, device="cuda")
+        classic.khq_capture_unroped(3, ku)
+        assert classic.khq_step(3, qg, kr, v, oa, SCALE)
+        assert fused.khq_step_fused(3, qg, ku, kr, v, ob, SCALE)
+        if t % 7 == 0 or t > 380:
+            torch.cuda.synchronize()
+            ok, mx, exc = cases.attention_close(ob.float().cpu().numpy(), oa.float().cpu().numpy())
+            assert ok, f"step {t}: max abs {mx:.3e}, excess {exc:.3e}"
+            worst = max(worst, mx)
+    torch.cuda.synchronize()
+    A, B = classic.layers[3], fused.layers[3]
+    assert (A.boundary, A.write_pos) == (B.boundary, B.write_pos) == (256, n)
+    assert [(e.boundary, e.write_pos) for e in classic.events] == [(e.boundary, e.write_pos) for e in fused.events]
+    for key in ("ring_k", "ring_v", "ring_u", "kmask", "kpay", "knorm", "krn", "vpay", "vnorm", "vrn", "vsm"):
+        assert torch.equal(A.t[key].view(torch.uint8), B.t[key].view(torch.uint8)), key
+    assert cuda_ops.lib.khq_b200_device_status() == 0
+    print(f"fused step: worst |difference| to the classic sequence {worst:.2e}")
+
+
+def test_decode_step_error_codes(cuda_ops):
+    fn = cuda_ops.lib.launch_khq_decode_step_fp16
+    z = [0] * 25
+    assert fn(*z, 0, 0, 1, 256, 1, 0.0625, 1.0, 1.0, 1e7, 0) == -100          # null pointers
+    a = [16] * 25
+    assert fn(*a, 0, 0, 0, 256, 1, 0.0625, 1.0, 1.0, 1e7, 0) == -100          # empty window
+    assert fn(*a, 0, 0, 300, 256, 1, 0.0625, 1.0, 1.0, 1e7, 0) == -103        # window larger than the ring
+    b = list(a)
+    b[1] = 8
+    assert fn(*b, 0, 0, 1, 256, 1, 0.0625, 1.0, 1.0, 1e7, 0) == -104          # misaligned token
