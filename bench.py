@@ -39,9 +39,9 @@ N_LAYERS = 16
 LAYER_IDS = [4 * i + 3 for i in range(N_LAYERS)]  # Bonsai-27B's full-attention layers
 
 
-# dram bytes per algorithmic byte of the batched decode kernel, from the ncu capture summarised
-# in profiles/khq_decode_batched_mma_kernel__8seq_1layer.md (117.0 MB read + 0.4 MB written for
-# 116 604 928 algorithmic bytes); the ratio does not depend on the number of rows
+# dram bytes per algorithmic byte of the batched decode kernel, from one ncu capture of an
+# 8-sequence launch (117.0 MB read + 0.4 MB written for 116 604 928 algorithmic bytes); the ratio
+# does not depend on the number of rows
 NCU_TRAFFIC_RATIO = 1.0034
 
 
@@ -359,7 +359,7 @@ def run_long(args, rank, world, local_rank):
                          "traffic": None, "algorithmic_bytes_per_step": b_alg},
             "gpu_launches": 5 * args.steps, "device_status": khqlib.load().khq_b200_device_status()}), flush=True)
     if cp.peer is not None:
-        cp.peer.close()
+        cp.close()
     dist.destroy_process_group()
 
 

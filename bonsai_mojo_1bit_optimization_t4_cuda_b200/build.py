@@ -43,7 +43,6 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if not force and not needs_build():
         return LIB_PATH
     cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(PKG_DIR.parent / "include")]
-    cmd += os.environ.get("KHQ_NVCC_EXTRA", "").split()  # e.g. -DKHQ_ABLATE=.. for timing experiments
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += ["-o", str(LIB_PATH)] + [str(CSRC / s) for s in SOURCES]

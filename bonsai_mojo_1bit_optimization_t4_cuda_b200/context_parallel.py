@@ -177,6 +177,33 @@ class ContextParallelDecode:
         self._neutral[:, D] = -1e20
         assert exchange in ("collective", "peer")
         self.peer = PeerExchange(ops, group, per_rank=2, device=device) if exchange == "peer" and self.world > 1 else None
+        # In peer mode a bounded wait that runs out (a slow or lost peer) only sets the library's
+        # device status word; it is read back every `status_every` steps and at close().
+        self.status_every = 64
+        self._steps = 0
+
+    def check_status(self) -> None:
+        """Read and clear the library's device status word (a blocking 4-byte copy) and raise if a
+        bounded wait of the peer exchange ran out: the outputs since the last check may then have
+        been merged from stale slots."""
+        lib = getattr(self.ops, "lib", None)
+        if lib is None or self.peer is None:
+            return
+        st = int(lib.khq_b200_device_status_clear())
+        if st == 3:
+            raise RuntimeError("context-parallel exchange: a wait for a peer's flag ran out (device status 3); "
+                               "outputs since the last check are not trustworthy")
+        if st < 0:
+            raise RuntimeError(f"context-parallel exchange: reading the device status failed ({st})")
+
+    def close(self) -> None:
+        """Final status check, then release the peer mappings (collective call)."""
+        try:
+            self.check_status()
+        finally:
+            if self.peer is not None:
+                self.peer.close()
+                self.peer = None
 
     def split_count(self, n_tok: int) -> int:
         return int(min(max(n_tok // 8, 1), self.splits))
@@ -210,6 +237,9 @@ class ContextParallelDecode:
         if self.peer is not None:
             self.peer.publish(self.mine)
             self.peer.merge(q_gate, self.out)
+            self._steps += 1
+            if self.status_every > 0 and self._steps % self.status_every == 0:
+                self.check_status()
             return self.out
         if self.world > 1:
             dist.all_gather_into_tensor(self.all.view(-1), self.mine.view(-1), group=self.group)

@@ -1082,6 +1082,18 @@ extern "C" size_t khq_b200_decode_workspace_bytes(int n_slots_total) {
     return 256 + (size_t)n_slots_total * HQ * PART * sizeof(float);
 }
 
+// SM count for the planner's default item size.  The planner itself makes no CUDA call that can
+// fail the plan: when no device is current or the query fails it plans for 148 SMs.
+static int plan_sm_count() {
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) {
+        (void)cudaGetLastError();
+        return 148;
+    }
+    return v;
+}
+
 // Host planner: cuts every problem's compressed region into items of about tokens_per_item
 // tokens (a multiple of the staging tile) plus one item for its raw window, in problem order.
 extern "C" int khq_b200_plan_decode(const int* c_len, const int* win_len, int n_desc, int tokens_per_item,
@@ -1090,7 +1102,7 @@ extern "C" int khq_b200_plan_decode(const int* c_len, const int* win_len, int n_
     if (tokens_per_item <= 0) {
         long long total = 0;
         for (int i = 0; i < n_desc; ++i) total += c_len[i] > 0 ? c_len[i] : 0;
-        long long t = total / (4LL * 148);
+        long long t = total / (4LL * plan_sm_count());
         if (t < 48) t = 48;
         if (t > 2048) t = 2048;
         tokens_per_item = (int)t;
@@ -1338,6 +1350,16 @@ extern "C" int launch_khq_merge_slots_wait_gate_fp16(const void* partials, const
         static_cast<const __half*>(q_gate), static_cast<__half*>(out), max_polls ? max_polls : (1u << 22));
     const cudaError_t err = cudaGetLastError();
     return (err == cudaSuccess) ? 0 : static_cast<int>(err);
+}
+
+// The library keeps process-wide cells (the state slots below, cached symbol addresses, per-device
+// attribute caches).  Like the reference library (src/csrc/qmv_sm75_kernel.cu:17-22) it pins itself
+// at load time so that a host that dlcloses it between calls finds them again.
+#include <dlfcn.h>
+__attribute__((constructor)) static void khq_b200_pin_self() {
+    Dl_info info;
+    if (dladdr(reinterpret_cast<const void*>(&khq_b200_pin_self), &info) && info.dli_fname)
+        (void)dlopen(info.dli_fname, RTLD_NOW | RTLD_GLOBAL | RTLD_NODELETE);
 }
 
 static void* g_khq_slots[3] = {nullptr, nullptr, nullptr};

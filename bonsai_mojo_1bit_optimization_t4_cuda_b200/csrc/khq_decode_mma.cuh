@@ -24,10 +24,6 @@
 #pragma once
 #include "khq_kdecode.cuh"
 
-#ifndef KHQ_ABLATE
-#define KHQ_ABLATE 0  // timing experiments only: 1 skip V side, 2 skip rotary part, 4 fake K decode, 8 skip rope table
-#endif
-
 namespace khq {
 
 constexpr int M2_THREADS = 256;
@@ -69,12 +65,6 @@ static_assert(8 * NREP * D * 4 <= M2_NSTAGE * M2_STAGE_BYTES, "prologue scratch 
 static_assert(M2_STAGE_BYTES % 16 == 0 && M2_OFF_KPAY % 16 == 0 && M2_OFF_VPAY % 16 == 0 && M2_OFF_KN % 16 == 0 &&
                   M2_OFF_VSM % 16 == 0, "bulk copy alignment");
 
-// low-order ("what fp16 lost") products; compiled out only in timing experiments
-#if KHQ_ABLATE & 16
-#define m2_mma_lo(c, a, b0, b1) ((void)0)
-#else
-#define m2_mma_lo(c, a, b0, b1) m2_mma(c, a, b0, b1)
-#endif
 __device__ __forceinline__ void m2_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -86,6 +76,8 @@ __device__ __forceinline__ uint32_t m2_movmatrix_t(uint32_t x) {
     asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(x));
     return r;
 }
+// low-order ("what fp16 lost") products go through the same instruction
+#define m2_mma_lo(c, a, b0, b1) m2_mma(c, a, b0, b1)
 __device__ __forceinline__ uint32_t m2_pack(float lo, float hi) {
     const __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&h);
@@ -143,9 +135,6 @@ __device__ __forceinline__ void m2_stage_tile(const CompressedKV& P, unsigned ch
 }
 
 __device__ __forceinline__ void m2_fill_rope(float2* tab, const float* freq, int pos0, int tid) {
-#if KHQ_ABLATE & 8
-    return;
-#endif
     for (int e = tid; e < M2_TT * 32; e += M2_THREADS) {
         const int t = e >> 5, m = e & 31;
         double th = (double)(pos0 + t) * (double)freq[m];
@@ -368,12 +357,8 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const int s = wi * 4 + q;
-#if KHQ_ABLATE & 4
-            const KdStep a = {kwa.E, kwa.O, kwa.X3, kwa.E ^ (uint32_t)q}, b = {kwb.E, kwb.O, kwb.X3, kwb.O ^ (uint32_t)q};
-#else
             const KdStep a = kd_step(kwa, q, wbase[0] + kd_prefix(kwa, q), kp[0], sg[0], lut);
             const KdStep b = kd_step(kwb, q, wbase[1] + kd_prefix(kwb, q), kp[1], sg[1], lut);
-#endif
             const uint32_t a1[4] = {a.t0, b.t0, a.t1, b.t1};
             const uint32_t ax[4] = {m2_hfma2(a.t0, neg1024, a.h0), m2_hfma2(b.t0, neg1024, b.h0),
                                     m2_hfma2(a.t1, neg1024, a.h1), m2_hfma2(b.t1, neg1024, b.h1)};  // sign*code, exact
@@ -400,9 +385,6 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
     }
     // ---- rotary part: rest of H64 over idx = 8j + 2t + e, /d, rotation, dot with the raw query ----
     float cr[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#if KHQ_ABLATE & 2
-    cr[0] = cu[0][0] + cu[7][3];
-#else
     {
         // index bits 0..2 were transformed inside the GEMM (folded into the rotor operand)
         // bits 3, 4, 5 (j)
@@ -444,7 +426,6 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
             m2_mma_lo(cr, al, Q.qr[kk][0], Q.qr[kk][1]);
         }
     }
-#endif
     // ================================ softmax over the block ====================================
     float sc[2][2], pw[2][2];  // [row x: g, g+8][head e: 2t, 2t+1]
     bool valid[2];
@@ -506,10 +487,6 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
             pl_[2][x] = m2_movmatrix_t(lo);
         }
     }
-#if KHQ_ABLATE & 1
-    st.o[0][0] += __uint_as_float(pb[0][0] ^ pb[1][1] ^ pb[2][0] ^ pl_[0][0] ^ pl_[1][0] ^ pl_[2][1]);
-    return;
-#endif
     // ================================ V side: O^T += V^T P^T ====================================
     // thread (g, t): patch group g of tokens 2t, 2t+1, 2t+8, 2t+9
     uint32_t vw[4][3], hb[4];

@@ -62,12 +62,12 @@ khq_prestep_kernel(__half* __restrict__ q_gate, __half* __restrict__ k, const __
     const int h = blockIdx.x, lane = threadIdx.x;
     if (h < H_q) {
         __half* x = q_gate + (size_t)h * 2 * d;
-        if (has_norms) norm_head(x, q_norm_w, d, eps, lane);
+        norm_head(x, has_norms ? q_norm_w : nullptr, d, eps, lane);
         rope_head(x, rotary_dim, pos, theta, lane);
     } else {
         const int g = h - H_q;
         __half* x = k + (size_t)g * d;
-        if (has_norms) norm_head(x, k_norm_w, d, eps, lane);
+        norm_head(x, has_norms ? k_norm_w : nullptr, d, eps, lane);
         if (ring_u) copy_head(ring_u + (size_t)g * d, x, d, lane);
         __syncwarp();
         rope_head(x, rotary_dim, pos, theta, lane);

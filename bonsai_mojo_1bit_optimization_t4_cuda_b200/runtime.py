@@ -302,8 +302,10 @@ class KhqRuntime:
         """``khq_capture_unroped`` + ``khq_step`` of one token through ``launch_khq_decode_step_fp16``:
         the three ring appends, both attention regions, the merge and the gate in two or three
         launches (and one host call) instead of seven.  A step on which a compression event is due
-        takes the classic sequence (the event sits between the append and the attention).  The state
-        afterwards is the one the classic calls leave."""
+        takes the classic sequence (the event sits between the append and the attention), and so does
+        a step whose window would exceed the ring (compressed capacity exhausted: the reference keeps
+        stepping with window > 256, ``README.md:259``, and so does ``khq_step``).  The state afterwards
+        is the one the classic calls leave."""
         if not self.active or not self.ready or layer_idx < 0 or layer_idx >= KHQ_MAX_LAYERS:
             return False
         L = self.layers[layer_idx]
@@ -311,7 +313,7 @@ class KhqRuntime:
             return False
         window_after = L.write_pos + 1 - L.boundary
         event_due = window_after >= KHQ_WATERMARK and L.boundary + KHQ_CHUNK <= L.cap
-        if event_due or not hasattr(self.ops, "decode_step"):
+        if event_due or window_after > KHQ_RING or not hasattr(self.ops, "decode_step"):
             self.khq_capture_unroped(layer_idx, k_unroped_dev)
             return self.khq_step(layer_idx, q_gate_dev, k_roped_dev, v_dev, out_dev, scale)
         T = L.t
@@ -447,6 +449,11 @@ class KhqRuntime:
             if i >= KHQ_MAX_LAYERS or not self.layers[i].has_tables:
                 raise ValueError(f"khq_state: layer {i} has no tables in this runtime")
             L = self.layers[i]
+            # the only shape the library's kernels serve; checked before anything is allocated from it
+            if (H_q, H_kv, D) != (24, 4, 256):
+                raise ValueError(f"khq_state: layer {i}: unsupported shape H_q={H_q} H_kv={H_kv} D={D}")
+            if cap > L.cap:
+                raise ValueError(f"khq_state: layer {i}: saved capacity {cap} exceeds this runtime's {L.cap}")
             if boundary > L.cap or boundary % KHQ_CHUNK != 0 or write_pos < boundary or write_pos - boundary > KHQ_RING:
                 raise ValueError(f"khq_state: layer {i}: boundary {boundary} / write_pos {write_pos} do not fit cap {L.cap}")
             self.khq_init_layer(i, H_q, H_kv, D)

@@ -180,8 +180,9 @@ int launch_khq_decode_batched_fp16(const void* descs, const void* tables, const 
  * (runtime.mojo:486).  In place: q_gate (H_q, 2*d) fp16 (query half normed + RoPE'd, gate half
  * untouched), k (H_kv, d) fp16 (normed + RoPE'd).  The three ring slot pointers address this
  * token's row of ring_u (K normed, un-RoPE'd), ring_k (K RoPE'd) and ring_v (V); any of them may
- * be NULL.  q_norm_w / k_norm_w: fp32 (d) or NULL; has_norms == 0 skips the norm as the
- * reference does.  Half-split RoPE pairs (i, i + rotary_dim/2), freq = exp(log(theta) *
+ * be NULL.  q_norm_w / k_norm_w: fp32 (d) or NULL.  The RMS normalisation always runs; has_norms == 0
+ * (or a NULL weight) only drops the learned weight, as the reference's launcher does
+ * (src/ops.mojo:1397-1411, the HAS_WEIGHT=False variant).  Half-split RoPE pairs (i, i + rotary_dim/2), freq = exp(log(theta) *
  * (-2i/rotary_dim)), fp32 angle pos*freq.  Returns -100 (bad arguments), -103 (shape), -104
  * (pointers not 16-byte aligned). */
 int launch_khq_prestep_fp16(void* q_gate, void* k, const void* v, const void* q_norm_w,
@@ -275,7 +276,8 @@ int launch_khq_merge_slots_gate_fp16(const void* partials, int n_slots, const vo
  * `out_partial` and `stride_s`; restricted to L_q == 1, num_queries == 24, num_splits <= 32,
  * anything larger returns -106.  It calls no allocating routine.  The first call on a device
  * looks up the array's device address (cudaGetSymbolAddress) and caches it, so make that first
- * call outside any stream capture.  Every call on a device shares the one array: calls that may
+ * call outside any stream capture, and from one host thread (the per-device caches are plain
+ * statics: first calls racing from several host threads on one device are not supported).  Every call on a device shares the one array: calls that may
  * overlap on the GPU (different streams) race on it; calls on one stream do not.  Nothing in the
  * array has to be cleared between calls: every split writes its whole record, empty splits
  * included. */

@@ -29,8 +29,25 @@ def build(force: bool = False) -> Path:
     src = _DIR / "khq_oracle.c"
     if force or not _LIB.exists() or _LIB.stat().st_mtime < src.stat().st_mtime:
         subprocess.run(["make", "-C", str(_DIR), "libkhq_oracle.so"], check=True, capture_output=True)
-    subprocess.run(["make", "-C", str(_DIR), "ref"], check=False, capture_output=True)
+    ref_root = _reference_root()
+    if ref_root:
+        subprocess.run(["make", "-C", str(_DIR), "ref", "REF_ROOT=" + ref_root], check=False, capture_output=True)
     return _LIB
+
+
+def _reference_root() -> str:
+    """Where the reference checkout lies, if anywhere: $KHQ_REF_ROOT, else the ``reference_path``
+    the repository's BASELINE.json records.  Empty when neither names an existing directory."""
+    import json
+    import os
+
+    cand = os.environ.get("KHQ_REF_ROOT", "")
+    if not cand:
+        try:
+            cand = json.loads((_DIR.parent / "BASELINE.json").read_text()).get("reference_path", "")
+        except (OSError, ValueError):
+            cand = ""
+    return cand if cand and Path(cand).is_dir() else ""
 
 
 def load() -> ctypes.CDLL:
@@ -248,9 +265,9 @@ class OracleOps:
     def prestep(self, q_gate, k, v, q_norm_w, k_norm_w, ring_k_slot, ring_v_slot, ring_u_slot, H_q, H_kv, d,
                 rotary_dim, pos, rope_theta, rms_eps, has_norms):
         """q/k head RMSNorm, K capture, partial RoPE, ring appends (CPU torch tensors, in place)."""
-        if has_norms:
-            head_rmsnorm(q_gate, H_q, d, 2 * d, q_norm_w, rms_eps)
-            head_rmsnorm(k, H_kv, d, d, k_norm_w, rms_eps)
+        # the norm always runs; has_norms == 0 only drops the learned weight (src/ops.mojo:1397-1411)
+        head_rmsnorm(q_gate, H_q, d, 2 * d, q_norm_w if has_norms else None, rms_eps)
+        head_rmsnorm(k, H_kv, d, d, k_norm_w if has_norms else None, rms_eps)
         if ring_u_slot is not None:
             ring_u_slot.copy_(k.reshape(ring_u_slot.shape))
         lib = load()
