@@ -70,7 +70,7 @@ def parse():
     ap.add_argument("--exchange", default="peer", choices=["peer", "collective"],
                     help="--workload long on N>1 GPUs: partials stored into the peers' buffers over NVLink (peer) or "
                          "one NCCL all-gather (collective)")
-    ap.add_argument("--kernel", default="auto", choices=["auto", "cuda-core", "mma"],
+    ap.add_argument("--kernel", default="auto", choices=["auto", "cuda-core", "mma", "tc5"],
                     help="generation of the batched decode kernel")
     return ap.parse_args()
 
@@ -679,7 +679,7 @@ def main():
     tables = make_tables(args.layers)
     t_setup = time.perf_counter()
     eng = BatchEngine(tables, c_len, win, device=f"cuda:{local_rank}",
-                      codebook_in_smem={"auto": -1, "cuda-core": 1, "mma": 2}[args.kernel])
+                      codebook_in_smem={"auto": -1, "cuda-core": 1, "mma": 2, "tc5": 3}[args.kernel])
     eng.fill_synthetic(20260914 + 1000 * 3 + rank)
     torch.cuda.synchronize()
     setup_s = time.perf_counter() - t_setup
@@ -772,7 +772,8 @@ def main():
                                            "116.6 MB algorithmic), scaled by payload rows: nothing is re-read",
                          "peak_source": peak_src,
                          "kernel": "%s (+ its merge kernel and a 256 B memset, inside the same events)" % (
-                             "khq_decode_batched_kernel" if args.kernel == "cuda-core" else "khq_decode_batched_mma_kernel"),
+                             {"cuda-core": "khq_decode_batched_kernel", "mma": "khq_decode_batched_mma_kernel",
+                              "tc5": "khq_decode_batched_tc5_kernel", "auto": "khq_decode_batched_mma_kernel"}[args.kernel]),
                          "algorithmic_bytes_per_launch": bytes_layer, "avg_launch_ms": avg_launch_ms},
             "us_per_layer_step_per_sequence": 1e3 * avg_launch_ms / args.seqs,
             "clocks": clocks, "device_status": status, "setup_s": setup_s,

@@ -17,6 +17,14 @@ namespace khq {
 
 constexpr int CMP_WARPS = 4;  // rows per block
 
+// One run of rows of a batched launch: source rows (fp16, D per row, contiguous) and the first
+// output row in the launch's output arrays (mirrored in include/khq_b200.h).
+struct KhqCompressSeg {
+    const __half* x;
+    long long row0;
+};
+static_assert(sizeof(KhqCompressSeg) == 16, "ABI");
+
 struct CompressScratch {
     float a[D];             // x as float, then per-dim |proj| contributions
     float b[D];             // per-dim centroid contributions
@@ -31,17 +39,27 @@ khq_compress_kernel(const __half* __restrict__ x, const __half* __restrict__ d_v
                     __half* __restrict__ out_norms, __half* __restrict__ out_r_norms,
                     unsigned char* __restrict__ out_payload,
                     unsigned char* __restrict__ out_shared_meta, int d_val, int n, float ts,
-                    float alpha, int is_v) {
+                    float alpha, int is_v, const KhqCompressSeg* __restrict__ segs, int rows_per_seg) {
     __shared__ CompressScratch scratch[CMP_WARPS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     CompressScratch& S = scratch[warp];
     // The reference computes this factor at run time from the dimension argument.
     const float f_s = rsqrtf((float)d_val);
 
-    for (long long row = (long long)blockIdx.x * CMP_WARPS + warp; row < n;
-         row += (long long)gridDim.x * CMP_WARPS) {
+    for (long long lrow = (long long)blockIdx.x * CMP_WARPS + warp; lrow < n;
+         lrow += (long long)gridDim.x * CMP_WARPS) {
+        // One launch over one contiguous run of rows (segs == nullptr: input row = output row), or
+        // over many runs of rows_per_seg rows, each with its own source and first output row.
+        long long row = lrow;
+        const __half* xrow = x + lrow * D;
+        if (segs != nullptr) {
+            const KhqCompressSeg sg = segs[lrow / rows_per_seg];
+            const long long rr = lrow % rows_per_seg;
+            row = sg.row0 + rr;
+            xrow = sg.x + rr * D;
+        }
         // ---- load: lane owns dims 8*lane .. 8*lane+7 ---------------------------------------
-        const uint4 raw = *reinterpret_cast<const uint4*>(x + row * D + lane * 8);
+        const uint4 raw = *reinterpret_cast<const uint4*>(xrow + lane * 8);
         const __half* hx = reinterpret_cast<const __half*>(&raw);
         float xv[8];
 #pragma unroll
@@ -367,7 +385,32 @@ extern "C" int launch_khq_compress_fp16(const void* x, const void* d_vec, const 
         static_cast<const __half*>(vq_centroids), static_cast<unsigned int*>(out_mask),
         static_cast<__half*>(out_norms), static_cast<__half*>(out_r_norms),
         static_cast<unsigned char*>(out_payload), static_cast<unsigned char*>(out_shared_meta), d,
-        n, threshold_scale, alpha, is_v);
+        n, threshold_scale, alpha, is_v, nullptr, 1);
+    const cudaError_t err = cudaGetLastError();
+    return (err == cudaSuccess) ? 0 : static_cast<int>(err);
+}
+
+// Many compression events in one launch: `n_seg` runs of `rows_per_seg` rows (512 = the 128 oldest
+// tokens of one sequence's ring), run i read from segs[i].x and written to rows segs[i].row0 .. of
+// the output arrays.  `segs` is a device array.  Same arithmetic, row by row, as the single launch.
+extern "C" int launch_khq_compress_batched_fp16(const void* segs, int n_seg, int rows_per_seg, const void* d_vec,
+                                                const void* rotor, const void* centroids, const void* vq_centroids,
+                                                void* out_mask, void* out_norms, void* out_r_norms, void* out_payload,
+                                                void* out_shared_meta, int d, float threshold_scale, float alpha,
+                                                int is_v, cudaStream_t stream) {
+    using namespace khq;
+    if (n_seg <= 0 || rows_per_seg <= 0 || d != D || !segs) return -100;
+    const long long n = (long long)n_seg * rows_per_seg;
+    if (n > 0x7FFFFFFFLL) return -100;
+    long long blocks = (n + CMP_WARPS - 1) / CMP_WARPS;
+    const long long cap = 148LL * 64;
+    if (blocks > cap) blocks = cap;
+    khq_compress_kernel<<<(unsigned)blocks, CMP_WARPS * 32, 0, stream>>>(
+        nullptr, static_cast<const __half*>(d_vec), static_cast<const __half*>(rotor),
+        static_cast<const __half*>(centroids), static_cast<const __half*>(vq_centroids),
+        static_cast<unsigned int*>(out_mask), static_cast<__half*>(out_norms), static_cast<__half*>(out_r_norms),
+        static_cast<unsigned char*>(out_payload), static_cast<unsigned char*>(out_shared_meta), d, (int)n,
+        threshold_scale, alpha, is_v, static_cast<const KhqCompressSeg*>(segs), rows_per_seg);
     const cudaError_t err = cudaGetLastError();
     return (err == cudaSuccess) ? 0 : static_cast<int>(err);
 }

@@ -582,6 +582,7 @@ khq_decode_batched_kernel(const KhqSeqDesc* __restrict__ descs, const KhqTablesD
 
 }  // namespace khq
 #include "khq_decode_mma.cuh"
+#include "khq_decode_tc5.cuh"
 namespace khq {
 
 // Per problem and query head: LSE merge of the problem's partial slots, /(den+1e-8), sigmoid
@@ -843,6 +844,7 @@ static cudaError_t ensure_smem_attrs() {
     if ((e = cudaFuncSetAttribute(khq_decode_batched_kernel<true>, attr, SM_TOTAL_VQ)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(khq_decode_batched_mma_kernel, attr, M2_SM_TOTAL)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(khq_attn_compressed_mma_kernel, attr, M2_SM_TOTAL)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(m3::khq_decode_batched_tc5_kernel, attr, m3::SM_TOTAL)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(khq_window_attn_kernel, attr, 2 * HKV * MERGE_FLOATS * 4)) != cudaSuccess)
         return e;
     if ((e = cudaFuncSetAttribute(khq_window_step_kernel, attr, 2 * HKV * MERGE_FLOATS * 4)) != cudaSuccess) return e;
@@ -1107,7 +1109,7 @@ extern "C" int khq_b200_plan_decode(const int* c_len, const int* win_len, int n_
         if (t > 2048) t = 2048;
         tokens_per_item = (int)t;
     }
-    tokens_per_item = ((tokens_per_item + TT - 1) / TT) * TT;
+    tokens_per_item = ((tokens_per_item + 95) / 96) * 96;  // a multiple of every generation's staging tile (24, 32 tokens)
     KhqWorkItem* items = static_cast<KhqWorkItem*>(items_out);
     int n = 0;
     for (int i = 0; i < n_desc; ++i) {
@@ -1154,7 +1156,11 @@ extern "C" int launch_khq_decode_batched_fp16(const void* descs, const void* tab
     float* partials = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + 256);
     const int grid = n_items < sm_count() ? n_items : sm_count();
     const bool vqs = codebook_in_smem != 0;
-    if (codebook_in_smem == 2 || codebook_in_smem < 0)
+    if (codebook_in_smem == 3)
+        m3::khq_decode_batched_tc5_kernel<<<grid, m3::THREADS, m3::SM_TOTAL, stream>>>(
+            static_cast<const KhqSeqDesc*>(descs), static_cast<const KhqTablesDesc*>(tables),
+            static_cast<const KhqWorkItem*>(items), n_items, counter, partials, scale, rope_base, ring_cap);
+    else if (codebook_in_smem == 2 || codebook_in_smem < 0)
         khq_decode_batched_mma_kernel<<<grid, M2_THREADS, M2_SM_TOTAL, stream>>>(
             static_cast<const KhqSeqDesc*>(descs), static_cast<const KhqTablesDesc*>(tables),
             static_cast<const KhqWorkItem*>(items), n_items, counter, partials, scale, rope_base, ring_cap);
@@ -1170,6 +1176,39 @@ extern "C" int launch_khq_decode_batched_fp16(const void* descs, const void* tab
     if (err != cudaSuccess) return static_cast<int>(err);
     khq_batched_merge_gate_kernel<<<n_desc * HQ, D, 0, stream>>>(static_cast<const KhqSeqDesc*>(descs), partials);
     err = cudaGetLastError();
+    return (err == cudaSuccess) ? 0 : static_cast<int>(err);
+}
+
+// Per-sequence state of a batch engine that changes every step and is the same for all layers
+// (mirrored in include/khq_b200.h).
+struct KhqSeqDyn {
+    int c_len, start_pos, win_start, win_len, first_slot, n_slots, r0, r1;
+};
+static_assert(sizeof(KhqSeqDyn) == 32, "ABI");
+
+// descs: layer-major (layer * n_seq + sequence); the pointers stay, the eight ints follow dyn[sequence].
+__global__ void khq_update_descs_kernel(khq::KhqSeqDesc* __restrict__ descs, const KhqSeqDyn* __restrict__ dyn, int n_seq,
+                                        int n_layers) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_seq * n_layers) return;
+    const KhqSeqDyn d = dyn[idx % n_seq];
+    khq::KhqSeqDesc* o = descs + idx;
+    o->c_len = d.c_len;
+    o->start_pos = d.start_pos;
+    o->win_start = d.win_start;
+    o->win_len = d.win_len;
+    o->first_slot = d.first_slot;
+    o->n_slots = d.n_slots;
+}
+
+// After a decode step has moved the sequences on (tokens appended, compression events fired), one
+// launch rewrites the step-dependent fields of every layer's descriptors from one small table.
+extern "C" int launch_khq_update_descs(void* descs, const void* dyn, int n_seq, int n_layers, cudaStream_t stream) {
+    if (!descs || !dyn || n_seq <= 0 || n_layers <= 0) return -100;
+    const int total = n_seq * n_layers;
+    khq_update_descs_kernel<<<(total + 255) / 256, 256, 0, stream>>>(static_cast<khq::KhqSeqDesc*>(descs),
+                                                                    static_cast<const KhqSeqDyn*>(dyn), n_seq, n_layers);
+    const cudaError_t err = cudaGetLastError();
     return (err == cudaSuccess) ? 0 : static_cast<int>(err);
 }
 

@@ -76,6 +76,35 @@ khq_prestep_kernel(__half* __restrict__ q_gate, __half* __restrict__ k, const __
     }
 }
 
+// The same work for B sequences in one launch: grid = B * (H_q + H_kv) warps.  Sequence b reads
+// q_gate + b * 2 * H_q * d, k / v + b * H_kv * d, appends to ring slot slots[b] of its own rings
+// (ring base + b * ring_seq_stride halfs) and rotates at position positions[b].
+__global__ void __launch_bounds__(32)
+khq_prestep_batched_kernel(__half* __restrict__ q_gate, __half* __restrict__ k, const __half* __restrict__ v,
+                           const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w,
+                           __half* __restrict__ ring_k, __half* __restrict__ ring_v, __half* __restrict__ ring_u,
+                           long long ring_seq_stride, const int* __restrict__ slots, const int* __restrict__ positions,
+                           int H_q, int H_kv, int d, int rotary_dim, float theta, float eps, int has_norms) {
+    const int per = H_q + H_kv;
+    const int b = blockIdx.x / per, h = blockIdx.x % per, lane = threadIdx.x;
+    const int pos = positions[b];
+    if (h < H_q) {
+        __half* x = q_gate + ((size_t)b * H_q + h) * 2 * d;
+        norm_head(x, has_norms ? q_norm_w : nullptr, d, eps, lane);
+        rope_head(x, rotary_dim, pos, theta, lane);
+    } else {
+        const int g = h - H_q;
+        __half* x = k + ((size_t)b * H_kv + g) * d;
+        const size_t slot_off = (size_t)b * ring_seq_stride + ((size_t)slots[b] * H_kv + g) * d;
+        norm_head(x, has_norms ? k_norm_w : nullptr, d, eps, lane);
+        if (ring_u) copy_head(ring_u + slot_off, x, d, lane);
+        __syncwarp();
+        rope_head(x, rotary_dim, pos, theta, lane);
+        if (ring_k) copy_head(ring_k + slot_off, x, d, lane);
+        if (ring_v) copy_head(ring_v + slot_off, v + ((size_t)b * H_kv + g) * d, d, lane);
+    }
+}
+
 }  // namespace khq_prestep
 
 extern "C" int launch_khq_prestep_fp16(void* q_gate, void* k, const void* v, const void* q_norm_w,
@@ -92,6 +121,29 @@ extern "C" int launch_khq_prestep_fp16(void* q_gate, void* k, const void* v, con
         static_cast<const float*>(q_norm_w), static_cast<const float*>(k_norm_w), static_cast<__half*>(ring_k_slot),
         static_cast<__half*>(ring_v_slot), static_cast<__half*>(ring_u_slot), H_q, d, rotary_dim, pos, rope_theta,
         rms_eps, has_norms);
+    const cudaError_t err = cudaGetLastError();
+    return (err == cudaSuccess) ? 0 : static_cast<int>(err);
+}
+
+// launch_khq_prestep_fp16 for `batch` sequences at once (no counterpart in the reference, which
+// serves one sequence).  slots / positions: device int32 arrays of `batch` entries (ring slot of
+// the new token, its absolute position); ring_seq_stride: halfs between two sequences' rings.
+extern "C" int launch_khq_prestep_batched_fp16(void* q_gate, void* k, const void* v, const void* q_norm_w,
+                                               const void* k_norm_w, void* ring_k, void* ring_v, void* ring_u,
+                                               long long ring_seq_stride, const void* slots, const void* positions,
+                                               int batch, int H_q, int H_kv, int d, int rotary_dim, float rope_theta,
+                                               float rms_eps, int has_norms, cudaStream_t stream) {
+    if (batch <= 0 || H_q <= 0 || H_kv <= 0 || d <= 0 || !q_gate || !k || !v || !slots || !positions) return -100;
+    if (d % 8 != 0 || rotary_dim <= 0 || rotary_dim > 64 || rotary_dim > d || (rotary_dim & 1)) return -103;
+    const void* ptrs[] = {q_gate, k, v, ring_k, ring_v, ring_u};
+    for (const void* p : ptrs)
+        if ((reinterpret_cast<uintptr_t>(p) & 15) != 0) return -104;
+    if ((ring_seq_stride & 7) != 0) return -104;
+    khq_prestep::khq_prestep_batched_kernel<<<(unsigned)(batch * (H_q + H_kv)), 32, 0, stream>>>(
+        static_cast<__half*>(q_gate), static_cast<__half*>(k), static_cast<const __half*>(v),
+        static_cast<const float*>(q_norm_w), static_cast<const float*>(k_norm_w), static_cast<__half*>(ring_k),
+        static_cast<__half*>(ring_v), static_cast<__half*>(ring_u), ring_seq_stride, static_cast<const int*>(slots),
+        static_cast<const int*>(positions), H_q, H_kv, d, rotary_dim, rope_theta, rms_eps, has_norms);
     const cudaError_t err = cudaGetLastError();
     return (err == cudaSuccess) ? 0 : static_cast<int>(err);
 }

@@ -10,7 +10,7 @@ from cases import D, H_KV, H_Q, SCALE
 pytestmark = pytest.mark.gpu
 
 
-def drive(rt, torch, device, case, n_steps, layer_ids, collect_at):
+def drive(rt, torch, device, case, n_steps, layer_ids, collect_at, fused=False):
     outs = {}
     for li in layer_ids:
         rt.khq_init_layer(li, H_Q, H_KV, D)
@@ -22,8 +22,11 @@ def drive(rt, torch, device, case, n_steps, layer_ids, collect_at):
             k_r = torch.from_numpy(case["k_roped"][t]).to(device)
             v = torch.from_numpy(case["v"][t]).to(device)
             out = torch.zeros(H_Q * D, dtype=torch.float16, device=device)
-            rt.khq_capture_unroped(li, k_u)
-            assert rt.khq_step(li, qg, k_r, v, out, SCALE)
+            if fused:
+                assert rt.khq_step_fused(li, qg, k_u, k_r, v, out, SCALE)
+            else:
+                rt.khq_capture_unroped(li, k_u)
+                assert rt.khq_step(li, qg, k_r, v, out, SCALE)
             if t in collect_at:
                 outs[(li, t)] = out.float().cpu().numpy()
     return outs
@@ -56,6 +59,47 @@ def test_decode_loop_matches_oracle_backend(cuda_ops, oracle, monkeypatch):
     for k in sorted(g_out):
         ok, mx, exc = cases.attention_close(g_out[k], c_out[k])
         assert ok, f"step {k}: max abs {mx:.3e} excess {exc:.3e}"
+
+
+@pytest.mark.parametrize("fused", [False, True])
+def test_full_decode_loop_two_layers_three_events(cuda_ops, oracle, monkeypatch, fused):
+    """The loop the reference's own measurement runs (README.md:27-47): a 56-token prompt plus 512
+    decode steps, 8 splits, here over two attention layers with their own tables, through
+    khq_step and through khq_step_fused.  Compression events must fire at tokens 256, 384 and 512
+    on every layer, the code words of all 384 compressed tokens must be bit-identical to those the
+    same state machine writes through the oracle backend, and the outputs at steps around every
+    event and at the end must agree with it."""
+    import torch
+
+    from bonsai_mojo_1bit_optimization_t4_cuda_b200.runtime import KhqRuntime
+
+    monkeypatch.setenv("BONSAI_KHQ_SPLITS", "8")
+    n_steps = 56 + 512
+    case = cases.make_case(cases.synth.seed_for(1, 3), n_steps, "calib", layer_id=3)
+    other = cases.make_case(cases.synth.seed_for(1, 7), 64, "n01_idrot", layer_id=7)
+    layers = [3, 7]
+    collect = {0, 55, 56, 255, 256, 257, 383, 384, 511, 512, 567}
+    res = {}
+    for name, ops, device in (("gpu", cuda_ops, "cuda"), ("cpu", oracle.OracleOps(), "cpu")):
+        rt = KhqRuntime(ops, device=device)
+        assert rt.khq_activate([case["tables"], other["tables"]], max_seq=1024)
+        res[name] = (drive(rt, torch, device, case, n_steps, layers, collect, fused=fused and name == "gpu"), rt)
+    (g_out, g_rt), (c_out, c_rt) = res["gpu"], res["cpu"]
+    want_events = [(li, b, w) for w, b in ((256, 128), (384, 256), (512, 384)) for li in layers]
+    assert sorted((e.layer, e.boundary, e.write_pos) for e in g_rt.events) == sorted(want_events)
+    assert sorted((e.layer, e.boundary, e.write_pos) for e in c_rt.events) == sorted(want_events)
+    for li in layers:
+        assert g_rt.layers[li].boundary == c_rt.layers[li].boundary == 384
+        assert g_rt.layers[li].write_pos == c_rt.layers[li].write_pos == n_steps
+        for key in ("kmask", "kpay", "knorm", "krn", "vpay", "vnorm", "vrn", "vsm"):
+            n = 384 * H_KV * {"kmask": 16, "kpay": 40, "vpay": 104, "vsm": 4}.get(key, 1)
+            a = g_rt.layers[li].t[key].cpu()[:n].view(torch.uint8)
+            b = c_rt.layers[li].t[key][:n].view(torch.uint8)
+            assert torch.equal(a, b), f"layer {li}: code words differ in {key}"
+    assert len(g_out) == len(collect) * len(layers)
+    for k in sorted(g_out):
+        ok, mx, exc = cases.attention_close(g_out[k], c_out[k])
+        assert ok, f"layer/step {k}: max abs {mx:.3e} excess {exc:.3e}"
 
 
 def test_decode_loop_with_fused_prestep(cuda_ops, oracle, monkeypatch):
