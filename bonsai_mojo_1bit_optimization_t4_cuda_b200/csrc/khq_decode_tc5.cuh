@@ -519,25 +519,19 @@ __device__ __forceinline__ void compressed_range(unsigned char* smem, uint32_t t
                 const float smv7 = valid ? reinterpret_cast<const float*>(stage + ST_VSM)[rr] * (1.0f / 7.0f) : 0.0f;
                 const uint32_t hb = (reinterpret_cast<const uint32_t*>(vrow)[24 + (grp >> 1)] >> (16 * (grp & 1))) & 0xFFFFu;
                 unsigned char* dst = smem + SM_V + b * V_CHUNK + grp * V_GROUP + lane * 128;
-                uint32_t wv[6];
-#pragma unroll
-                for (int e = 0; e < 3; ++e) {
-                    const uint2 w2 = *reinterpret_cast<const uint2*>(vrow + 24 * grp + 8 * e);
-                    wv[2 * e] = w2.x;
-                    wv[2 * e + 1] = w2.y;
-                }
-#pragma unroll
+#pragma unroll 1
                 for (int g8 = 0; g8 < 2; ++g8) {
+                    const uint32_t* wp = reinterpret_cast<const uint32_t*>(vrow) + 6 * grp + 3 * g8;
                     uint32_t f[8];
-                    khq3::v3_fields(wv[3 * g8], wv[3 * g8 + 1], wv[3 * g8 + 2], f);
+                    khq3::v3_fields(wp[0], wp[1], wp[2], f);
 #pragma unroll
                     for (int u = 0; u < 8; u += 2) {
                         uint32_t ow[4];
 #pragma unroll
                         for (int e = 0; e < 2; ++e) {
-                            const int pl = 8 * g8 + u + e, p = 16 * grp + pl;
+                            const int p = 16 * grp + 8 * g8 + u + e;
                             const uint32_t fld = f[u + e];
-                            const uint32_t hbit = (pl <= 7) ? ((hb << (7 - pl)) & 0x80u) : ((hb >> (pl - 7)) & 0x80u);
+                            const uint32_t hbit = ((hb >> (8 * g8)) << (7 - (u + e))) & 0x80u;
                             const uint32_t code = (fld & 0x7Fu) | hbit;
                             const uint32_t e01 = *reinterpret_cast<const uint32_t*>(vqa + code * (VQA_STRIDE * 4) + p * 4);
                             const uint32_t e2 = *reinterpret_cast<const unsigned short*>(vqb + code * VQB_STRIDE + p * 2);
@@ -564,18 +558,12 @@ __device__ __forceinline__ void compressed_range(unsigned char* smem, uint32_t t
                 // ---------------- K decode of tile t + 1: code words -> A operand in tensor memory -------
                 wait_bar(&bars[B_KFULL], g & 1u, abortf);
                 const uint32_t* kp = reinterpret_cast<const uint32_t*>(stage + ST_KPAY + r * K_PAY);
-                uint32_t mw[8];
+                const uint32_t* mrow = reinterpret_cast<const uint32_t*>(stage + ST_MASK + r * 64);
                 uint32_t ob = 0;
-                {
-                    const uint4* mrow = reinterpret_cast<const uint4*>(stage + ST_MASK + r * 64);
-                    if (half) {  // outliers of the row's first 128 dims come before this thread's
-                        const uint4 a = mrow[0], b4 = mrow[1];
-                        ob = khq3::k3_count(a.x) + khq3::k3_count(a.y) + khq3::k3_count(a.z) + khq3::k3_count(a.w) +
-                             khq3::k3_count(b4.x) + khq3::k3_count(b4.y) + khq3::k3_count(b4.z) + khq3::k3_count(b4.w);
-                    }
-                    const uint4 a = mrow[2 * half], b4 = mrow[2 * half + 1];
-                    mw[0] = a.x; mw[1] = a.y; mw[2] = a.z; mw[3] = a.w;
-                    mw[4] = b4.x; mw[5] = b4.y; mw[6] = b4.z; mw[7] = b4.w;
+                if (half) {  // outliers of the row's first 128 dims come before this thread's
+                    const uint4 a = reinterpret_cast<const uint4*>(mrow)[0], b4 = reinterpret_cast<const uint4*>(mrow)[1];
+                    ob = khq3::k3_count(a.x) + khq3::k3_count(a.y) + khq3::k3_count(a.z) + khq3::k3_count(a.w) +
+                         khq3::k3_count(b4.x) + khq3::k3_count(b4.y) + khq3::k3_count(b4.z) + khq3::k3_count(b4.w);
                 }
                 float mult = (float)kp[0] / 1000.0f;
                 if (mult < 0.1f || mult > 10.0f || isnan(mult)) mult = 1.0f;
@@ -589,10 +577,15 @@ __device__ __forceinline__ void compressed_range(unsigned char* smem, uint32_t t
                 const __half2 rh = __float2half2_rn(rsc / mult);
                 const uint32_t ratio2 = *reinterpret_cast<const uint32_t*>(&rh);
                 const uint32_t neg1024 = 0xE400E400u;
-#pragma unroll
-                for (int w = 0; w < 8; ++w) {
+#ifndef M3_WORD_UNROLL
+#define M3_WORD_UNROLL 2
+#endif
+#define M3_STR2(x) #x
+#define M3_STR(x) M3_STR2(x)
+_Pragma(M3_STR(unroll M3_WORD_UNROLL))
+                for (int w = 0; w < 8; ++w) {  // not fully unrolled: the loop body is large and the instruction cache is not
                     uint32_t t2[8], h2[8], a2[8];
-                    ob += khq3::k3_word(mw[w], ob, kp, t2, h2);
+                    ob += khq3::k3_word(mrow[8 * half + w], ob, kp, t2, h2);
                     const int col0 = 8 * (8 * half + w);
 #pragma unroll
                     for (int j = 0; j < 8; j += 2) {

@@ -128,7 +128,13 @@ KHQ3_HD uint32_t k3_word(uint32_t w, uint32_t ob, const uint32_t* kp, uint32_t (
     const uint32_t e3 = E & (E >> 1) & 0x11111111u, o3 = O & (O >> 1) & 0x11111111u;
     const uint32_t cnt = k3_popc(e3 | (o3 << 1));
     if (cnt > 8u || ob + cnt > 50u) {
-        k3_word_slow(w, ob, kp, t2, h2);
+        uint32_t ts[8], hs[8];  // only these have their address taken: t2 / h2 stay in registers
+        k3_word_slow(w, ob, kp, ts, hs);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            t2[j] = ts[j];
+            h2[j] = hs[j];
+        }
         return cnt;
     }
     uint32_t g[4] = {0u, 0u, 0u, 0u};  // per dim: code | negative << 4, zero off the outliers
