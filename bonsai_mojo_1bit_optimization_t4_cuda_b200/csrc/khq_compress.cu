@@ -39,7 +39,8 @@ khq_compress_kernel(const __half* __restrict__ x, const __half* __restrict__ d_v
                     __half* __restrict__ out_norms, __half* __restrict__ out_r_norms,
                     unsigned char* __restrict__ out_payload,
                     unsigned char* __restrict__ out_shared_meta, int d_val, int n, float ts,
-                    float alpha, int is_v, const KhqCompressSeg* __restrict__ segs, int rows_per_seg) {
+                    float alpha, int is_v, const KhqCompressSeg* __restrict__ segs, int rows_per_seg,
+                    long long x_byte_offset) {
     __shared__ CompressScratch scratch[CMP_WARPS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     CompressScratch& S = scratch[warp];
@@ -56,7 +57,7 @@ khq_compress_kernel(const __half* __restrict__ x, const __half* __restrict__ d_v
             const KhqCompressSeg sg = segs[lrow / rows_per_seg];
             const long long rr = lrow % rows_per_seg;
             row = sg.row0 + rr;
-            xrow = sg.x + rr * D;
+            xrow = reinterpret_cast<const __half*>(reinterpret_cast<const char*>(sg.x) + x_byte_offset) + rr * D;
         }
         // ---- load: lane owns dims 8*lane .. 8*lane+7 ---------------------------------------
         const uint4 raw = *reinterpret_cast<const uint4*>(xrow + lane * 8);
@@ -385,21 +386,24 @@ extern "C" int launch_khq_compress_fp16(const void* x, const void* d_vec, const 
         static_cast<const __half*>(vq_centroids), static_cast<unsigned int*>(out_mask),
         static_cast<__half*>(out_norms), static_cast<__half*>(out_r_norms),
         static_cast<unsigned char*>(out_payload), static_cast<unsigned char*>(out_shared_meta), d,
-        n, threshold_scale, alpha, is_v, nullptr, 1);
+        n, threshold_scale, alpha, is_v, nullptr, 1, 0);
     const cudaError_t err = cudaGetLastError();
     return (err == cudaSuccess) ? 0 : static_cast<int>(err);
 }
 
 // Many compression events in one launch: `n_seg` runs of `rows_per_seg` rows (512 = the 128 oldest
 // tokens of one sequence's ring), run i read from segs[i].x and written to rows segs[i].row0 .. of
-// the output arrays.  `segs` is a device array.  Same arithmetic, row by row, as the single launch.
+// the output arrays.  `segs` is a device array; x_byte_offset is added to every run's source address
+// (a host that keeps K and V rings at a fixed distance uses one table for both launches).  Same
+// arithmetic, row by row, as the single launch.
 extern "C" int launch_khq_compress_batched_fp16(const void* segs, int n_seg, int rows_per_seg, const void* d_vec,
                                                 const void* rotor, const void* centroids, const void* vq_centroids,
                                                 void* out_mask, void* out_norms, void* out_r_norms, void* out_payload,
                                                 void* out_shared_meta, int d, float threshold_scale, float alpha,
-                                                int is_v, cudaStream_t stream) {
+                                                int is_v, long long x_byte_offset, cudaStream_t stream) {
     using namespace khq;
     if (n_seg <= 0 || rows_per_seg <= 0 || d != D || !segs) return -100;
+    if ((x_byte_offset & 15) != 0) return -104;
     const long long n = (long long)n_seg * rows_per_seg;
     if (n > 0x7FFFFFFFLL) return -100;
     long long blocks = (n + CMP_WARPS - 1) / CMP_WARPS;
@@ -410,7 +414,7 @@ extern "C" int launch_khq_compress_batched_fp16(const void* segs, int n_seg, int
         static_cast<const __half*>(centroids), static_cast<const __half*>(vq_centroids),
         static_cast<unsigned int*>(out_mask), static_cast<__half*>(out_norms), static_cast<__half*>(out_r_norms),
         static_cast<unsigned char*>(out_payload), static_cast<unsigned char*>(out_shared_meta), d, (int)n,
-        threshold_scale, alpha, is_v, static_cast<const KhqCompressSeg*>(segs), rows_per_seg);
+        threshold_scale, alpha, is_v, static_cast<const KhqCompressSeg*>(segs), rows_per_seg, x_byte_offset);
     const cudaError_t err = cudaGetLastError();
     return (err == cudaSuccess) ? 0 : static_cast<int>(err);
 }

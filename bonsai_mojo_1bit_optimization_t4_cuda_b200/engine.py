@@ -2,30 +2,47 @@
 
 This is the public entry a serving host calls once per generated token: hand it this step's
 projections for every sequence (host buffers), get the gated attention outputs back (host
-buffers).  Per layer it appends the new token to the raw rings and runs ONE batched launch
-(``launch_khq_decode_batched_fp16``) over all sequences.  Sequences are independent, so B
-sequences shard across GPUs by sequence with no collective (one engine per rank).
+buffers).  Sequences are independent, so they shard across GPUs by sequence with no collective
+(one engine per rank).
 
-The reference runtime (``src/khq/runtime.mojo``) keeps exactly this state per layer for a single
-sequence; here it is laid out for many: one contiguous device buffer per payload array and per
-layer, each sequence's slice starting on a 256-byte boundary.
+Per step and sequence the engine does what the reference's ``khq_step`` does for its single
+sequence (``src/khq/runtime.mojo:454-613``): the new token goes to ring slot ``write_pos % 256``
+and ``write_pos`` advances; when the raw window has reached 256 tokens (and the compressed
+capacity allows) the 128 oldest tokens are compressed and ``boundary`` moves on by 128; the
+attention then runs over ``c_len = boundary`` compressed tokens and the ``write_pos - boundary``
+raw ones.  Per layer that is one launch for the q/k head norms, K capture, RoPE and the three
+ring appends of ALL sequences (``launch_khq_prestep_batched_fp16``), one K and one V compress
+launch over the sequences whose event is due (``launch_khq_compress_batched_fp16``), and one
+batched attention launch (``launch_khq_decode_batched_fp16``); the work items are re-planned
+on the host every step and the step-dependent descriptor fields of every layer are rewritten by
+one small launch (``launch_khq_update_descs``).
+
+State layout: one contiguous device buffer per payload array and per layer, each sequence's
+slice sized for its capacity and starting on a 128-row boundary.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from typing import Optional, Sequence
 
 import numpy as np
 import torch
 
 from . import lib as _lib
-from .batched import BatchedDecode
+from .batched import SEQ_DESC, TABLES_DESC, WORK_ITEM
 from .calib import KhqLayerTables
 from .lib import check, current_stream
 from .synth import H_KV, H_Q
 
 D = 256
 RING = 256
+CHUNK = 128
+WATERMARK = 256
 KV = H_KV * D  # halfs per token row group
+ROTARY_DIM = 64
+SEQ_DYN = np.dtype([("c_len", "<i4"), ("start_pos", "<i4"), ("win_start", "<i4"), ("win_len", "<i4"),
+                    ("first_slot", "<i4"), ("n_slots", "<i4"), ("r0", "<i4"), ("r1", "<i4")])
+COMPRESS_SEG = np.dtype([("x", "<u8"), ("row0", "<i8")])
+assert SEQ_DYN.itemsize == 32 and COMPRESS_SEG.itemsize == 16
 
 
 def _align(n: int, a: int = 256) -> int:
@@ -34,16 +51,26 @@ def _align(n: int, a: int = 256) -> int:
 
 class BatchEngine:
     def __init__(self, tables: Sequence[KhqLayerTables], c_len: Sequence[int], win_len: Sequence[int],
-                 device="cuda", tokens_per_item: int = 0, codebook_in_smem: int = -1):
+                 device="cuda", tokens_per_item: int = 0, codebook_in_smem: int = -1, grow_tokens: int = 1024,
+                 norm_weights: Optional[Sequence] = None, rope_theta: float = 1e7, rms_eps: float = 1e-6):
+        """``c_len`` / ``win_len``: compressed and raw tokens each sequence starts with (``c_len`` a
+        multiple of 128, as the state machine leaves it).  ``grow_tokens``: compressed capacity kept
+        free behind every sequence's initial prefix.  ``norm_weights``: per layer ``(q_w, k_w)`` fp32
+        (256,) arrays for the head RMS norms, or None for the unweighted norm."""
         self.lib = _lib.load()
         self.device = torch.device(device)
         self.L = len(tables)
         self.B = len(c_len)
-        self.c_len = np.asarray(c_len, np.int64)
-        self.win_len = np.asarray(win_len, np.int64)
-        assert (self.win_len >= 0).all() and (self.win_len <= RING).all()
+        self.boundary = np.asarray(c_len, np.int64).copy()
+        self.write_pos = self.boundary + np.asarray(win_len, np.int64)
+        assert (self.boundary % CHUNK == 0).all(), "compressed prefixes are whole 128-token chunks"
+        assert ((self.write_pos - self.boundary) <= RING).all() and (np.asarray(win_len) >= 0).all()
+        self.cap = self.boundary + _align(max(int(grow_tokens), 0), CHUNK)
+        self.codebook_in_smem = codebook_in_smem
+        self.rope_theta, self.rms_eps = float(rope_theta), float(rms_eps)
         self.host_tables = list(tables)
         dev = self.device
+        z = lambda n, dt: torch.zeros(max(int(n), 1), dtype=dt, device=dev)
         # ---- tables ------------------------------------------------------------------------
         self.tables = []
         for tb in tables:
@@ -54,66 +81,129 @@ class BatchEngine:
                 v_rotor=torch.from_numpy(f["rotor_v"]).to(dev), d_k=torch.from_numpy(f["d_k"]).to(dev),
                 d_v=torch.from_numpy(f["d_v"]).to(dev), alpha_k=tb.alpha_k, alpha_v=tb.alpha_v,
                 ts_k=tb.ts_k, ts_v=tb.ts_v))
+        t = np.zeros(self.L, TABLES_DESC)
+        for i, tb in enumerate(self.tables):
+            for k in ("cents_k", "cents_v", "vq", "k_rotor", "v_rotor", "d_k", "d_v"):
+                t[k][i] = tb[k].data_ptr()
+            t["alpha_k"][i], t["alpha_v"][i] = tb["alpha_k"], tb["alpha_v"]
+        self.d_tables = torch.from_numpy(t.view(np.uint8).reshape(-1).copy()).to(dev)
+        self.norm_w = None
+        if norm_weights is not None:
+            self.norm_w = [(torch.as_tensor(np.asarray(q, np.float32)).to(dev), torch.as_tensor(np.asarray(k, np.float32)).to(dev))
+                           for q, k in norm_weights]
         # ---- payload arrays: per layer one buffer per array, sequences at aligned row offsets --
-        rows = self.c_len * H_KV
+        rows = self.cap * H_KV
         self.row_off = np.zeros(self.B + 1, np.int64)  # in rows, multiples of 128 rows
         for i in range(self.B):
             self.row_off[i + 1] = self.row_off[i] + _align(int(rows[i]), 128)
         R = int(self.row_off[-1])
-        z = lambda n, dt: torch.zeros(max(n, 1), dtype=dt, device=dev)
         self.pay = [dict(k_mask=z(R * 16, torch.int32), k_payload=z(R * 40, torch.uint8),
                          v_payload=z(R * 104, torch.uint8), v_shared_meta=z(R * 4, torch.uint8),
                          k_norms=z(R, torch.float16), k_r_norms=z(R, torch.float16),
                          v_norms=z(R, torch.float16), v_r_norms=z(R, torch.float16)) for _ in range(self.L)]
-        self.ring_k = [z(self.B * RING * KV, torch.float16).view(self.B, RING, KV) for _ in range(self.L)]
-        self.ring_v = [z(self.B * RING * KV, torch.float16).view(self.B, RING, KV) for _ in range(self.L)]
-        self.ring_u = [z(self.B * RING * KV, torch.float16).view(self.B, RING, KV) for _ in range(self.L)]
+        ring = lambda: z(self.B * RING * KV, torch.float16).view(self.B, RING, KV)
+        self.ring_k = [ring() for _ in range(self.L)]
+        self.ring_v = [ring() for _ in range(self.L)]
+        self.ring_u = [ring() for _ in range(self.L)]
         self.q_gate = [z(self.B * H_Q * 2 * D, torch.float16).view(self.B, H_Q * 2 * D) for _ in range(self.L)]
         self.out = [z(self.B * H_Q * D, torch.float16).view(self.B, H_Q * D) for _ in range(self.L)]
-        # ring slot of the newest token of each sequence: the window is [c_len, c_len+win_len)
-        self.win_start = (self.c_len % RING).astype(np.int64)
-        self.new_slot = torch.from_numpy(((self.c_len + np.maximum(self.win_len, 1) - 1) % RING)).to(dev)
-        self.bidx = torch.arange(self.B, device=dev)
-        # ---- descriptors -------------------------------------------------------------------
-        self.bd: List[BatchedDecode] = []
+        self.d_k = z(self.B * KV, torch.float16).view(self.B, KV)
+        self.d_v = z(self.B * KV, torch.float16).view(self.B, KV)
+        # ---- descriptors: layer-major, pointers fixed, the step-dependent ints rewritten per step
+        d = np.zeros(self.L * self.B, SEQ_DESC)
         for l in range(self.L):
-            probs = []
             P = self.pay[l]
             for i in range(self.B):
                 r0 = int(self.row_off[i])
-                probs.append(dict(
-                    q_gate=self.q_gate[l][i], out=self.out[l][i], ring_k=self.ring_k[l][i], ring_v=self.ring_v[l][i],
-                    k_mask=P["k_mask"][r0 * 16:], k_payload=P["k_payload"][r0 * 40:],
-                    v_payload=P["v_payload"][r0 * 104:], v_shared_meta=P["v_shared_meta"][r0 * 4:],
-                    k_norms=P["k_norms"][r0:], k_r_norms=P["k_r_norms"][r0:], v_norms=P["v_norms"][r0:],
-                    v_r_norms=P["v_r_norms"][r0:], table_id=0, c_len=int(self.c_len[i]), start_pos=0,
-                    win_start=int(self.win_start[i]), win_len=int(self.win_len[i])))
-            self.bd.append(BatchedDecode(probs, [self.tables[l]], tokens_per_item=tokens_per_item,
-                                         codebook_in_smem=codebook_in_smem))
-        # ---- pinned host staging for the end-to-end path ------------------------------------
-        pin = lambda *shape: torch.zeros(*shape, dtype=torch.float16).pin_memory() if dev.type == "cuda" \
-            else torch.zeros(*shape, dtype=torch.float16)
+                e = d[l * self.B + i]
+                e["q_gate"], e["out"] = self.q_gate[l][i].data_ptr(), self.out[l][i].data_ptr()
+                e["ring_k"], e["ring_v"] = self.ring_k[l][i].data_ptr(), self.ring_v[l][i].data_ptr()
+                e["k_mask"], e["k_payload"] = P["k_mask"][r0 * 16:].data_ptr(), P["k_payload"][r0 * 40:].data_ptr()
+                e["v_payload"], e["v_shared_meta"] = P["v_payload"][r0 * 104:].data_ptr(), P["v_shared_meta"][r0 * 4:].data_ptr()
+                e["k_norms"], e["k_r_norms"] = P["k_norms"][r0:].data_ptr(), P["k_r_norms"][r0:].data_ptr()
+                e["v_norms"], e["v_r_norms"] = P["v_norms"][r0:].data_ptr(), P["v_r_norms"][r0:].data_ptr()
+                e["table_id"] = l
+        self.d_descs = torch.from_numpy(d.view(np.uint8).reshape(-1).copy()).to(dev)
+        # ---- planning ----------------------------------------------------------------------
+        if tokens_per_item <= 0:
+            sms = torch.cuda.get_device_properties(dev).multi_processor_count if dev.type == "cuda" else 148
+            tokens_per_item = int(min(max(int(self.cap.sum()) // (4 * sms), 96), 2048))
+        self.tokens_per_item = (tokens_per_item + 95) // 96 * 96
+        self.max_items = int(sum((int(c) + self.tokens_per_item - 1) // self.tokens_per_item + 2 for c in self.cap))
+        self.ws_bytes = int(self.lib.khq_b200_decode_workspace_bytes(self.max_items))
+        self.workspace = z(self.ws_bytes, torch.uint8)
+        self.d_items = z(self.max_items * WORK_ITEM.itemsize, torch.uint8)
+        self.d_dyn = z(self.B * SEQ_DYN.itemsize, torch.uint8)
+        self.d_slots = z(self.B, torch.int32)
+        self.d_pos = z(self.B, torch.int32)
+        self.d_segs = z(self.L * self.B * COMPRESS_SEG.itemsize, torch.uint8)
+        # ---- pinned host staging: two parities of the control block, one set of data buffers ----
+        cuda = dev.type == "cuda"
+        pin = lambda *shape, dt=torch.float16: (torch.zeros(*shape, dtype=dt).pin_memory() if cuda else torch.zeros(*shape, dtype=dt))
         self.h_q = pin(self.L, self.B, H_Q * 2 * D)
-        self.h_kr = pin(self.L, self.B, KV)
-        self.h_ku = pin(self.L, self.B, KV)
+        self.h_k = pin(self.L, self.B, KV)
         self.h_v = pin(self.L, self.B, KV)
         self.h_out = pin(self.L, self.B, H_Q * D)
-        self.d_kr = z(self.B * KV, torch.float16).view(self.B, KV)
-        self.d_ku = z(self.B * KV, torch.float16).view(self.B, KV)
-        self.d_v = z(self.B * KV, torch.float16).view(self.B, KV)
+        self._ctl = [dict(items=pin(self.max_items * WORK_ITEM.itemsize, dt=torch.uint8), dyn=pin(self.B * SEQ_DYN.itemsize, dt=torch.uint8),
+                          slots=pin(self.B, dt=torch.int32), pos=pin(self.B, dt=torch.int32),
+                          segs=pin(self.L * self.B * COMPRESS_SEG.itemsize, dt=torch.uint8),
+                          done=(torch.cuda.Event() if cuda else None)) for _ in range(2)]
+        self._step = 0
+        self.n_items = 0
+        self.events_fired = 0
+        self._plan_and_upload(self._ctl[0])
 
     # ---------------------------------------------------------------------------------- sizes
     @property
+    def c_len(self) -> np.ndarray:
+        return self.boundary
+
+    @property
+    def win_len(self) -> np.ndarray:
+        return self.write_pos - self.boundary
+
+    @property
+    def win_start(self) -> np.ndarray:
+        return self.boundary % RING
+
+    @property
     def algorithmic_bytes_per_layer(self) -> int:
-        return int(H_KV * (220 * self.c_len + 1024 * self.win_len).sum())
+        return int(H_KV * (220 * self.boundary + 1024 * (self.write_pos - self.boundary)).sum())
 
     @property
     def h2d_bytes_per_step(self) -> int:
-        return self.L * self.B * (H_Q * 2 * D + 3 * KV) * 2
+        """Projections of one step for every layer and sequence plus the step's control block
+        (work items, per-sequence state, ring slots, positions)."""
+        return self.L * self.B * (H_Q * 2 * D + 2 * KV) * 2 + self.n_items * WORK_ITEM.itemsize + self.B * (SEQ_DYN.itemsize + 8)
 
     @property
     def d2h_bytes_per_step(self) -> int:
         return self.L * self.B * H_Q * D * 2
+
+    # ---------------------------------------------------------------------------------- planning
+    def _plan_and_upload(self, ctl) -> None:
+        """Cut the current compressed prefixes and windows into work items (host planner of the
+        library), and send items + per-sequence state to the device; one launch then rewrites the
+        step-dependent fields of all L x B descriptors."""
+        c = np.ascontiguousarray(self.boundary, np.int32)
+        w = np.ascontiguousarray(self.write_pos - self.boundary, np.int32)
+        first = np.zeros(self.B, np.int32)
+        cnt = np.zeros(self.B, np.int32)
+        items = ctl["items"].numpy().view(WORK_ITEM)
+        n = self.lib.khq_b200_plan_decode(c.ctypes.data, w.ctypes.data, self.B, self.tokens_per_item, items.ctypes.data,
+                                          self.max_items, first.ctypes.data, cnt.ctypes.data)
+        if n < 0 or n > self.max_items:
+            raise _lib.KhqLaunchError("khq_b200_plan_decode", n)
+        self.n_items = int(n)
+        dyn = ctl["dyn"].numpy().view(SEQ_DYN)
+        dyn["c_len"], dyn["start_pos"], dyn["win_start"], dyn["win_len"] = c, 0, (self.boundary % RING).astype(np.int32), w
+        dyn["first_slot"], dyn["n_slots"] = first, cnt
+        nb = self.n_items * WORK_ITEM.itemsize
+        self.d_items[:nb].copy_(ctl["items"][:nb], non_blocking=True)
+        self.d_dyn.copy_(ctl["dyn"], non_blocking=True)
+        if self.device.type == "cuda":
+            check("launch_khq_update_descs", self.lib.launch_khq_update_descs(self.d_descs.data_ptr(), self.d_dyn.data_ptr(), self.B,
+                                                                              self.L, current_stream()))
 
     # ---------------------------------------------------------------------------------- loading
     def compress_into(self, layer: int, seq: int, k_unroped: torch.Tensor, v: torch.Tensor, tok0: int = 0) -> None:
@@ -137,12 +227,13 @@ class BatchEngine:
             rows, D, float(tb["ts_v"]), float(tb["alpha_v"]), 1, st)
         check("launch_khq_compress_fp16", rc)
 
-    def load_window(self, layer: int, seq: int, k_roped: torch.Tensor, v: torch.Tensor) -> None:
-        """Place win_len raw tokens (fp16 (win_len, 4, 256)) into the ring slots of the window."""
-        ws, wl = int(self.win_start[seq]), int(self.win_len[seq])
+    def load_window(self, layer: int, seq: int, k_roped: torch.Tensor, v: torch.Tensor, k_unroped: Optional[torch.Tensor] = None) -> None:
+        """Place the sequence's raw tokens (fp16 (win_len, 4, 256)) into the ring slots of its window."""
+        ws, wl = int(self.boundary[seq] % RING), int(self.write_pos[seq] - self.boundary[seq])
         slots = (ws + torch.arange(wl, device=self.device)) % RING
         self.ring_k[layer][seq, slots] = k_roped.reshape(wl, KV)
         self.ring_v[layer][seq, slots] = v.reshape(wl, KV)
+        self.ring_u[layer][seq, slots] = (k_unroped if k_unroped is not None else k_roped).reshape(wl, KV)
 
     def fill_synthetic(self, seed: int, chunk_tokens: int = 16384) -> None:
         """Seeded synthetic state: per layer and kv-head channel scales exp(0.5 N(0,1)) with four x8
@@ -156,13 +247,13 @@ class BatchEngine:
                     idx = torch.randperm(D, generator=g, device=self.device)[:4]
                     sc[kv, h, idx] *= 8.0
             for i in range(self.B):
-                n = int(self.c_len[i])
+                n = int(self.boundary[i])
                 for t0 in range(0, n, chunk_tokens):
                     m = min(chunk_tokens, n - t0)
                     k = (torch.randn(m, H_KV, D, generator=g, device=self.device) * sc[0]).half()
                     v = (torch.randn(m, H_KV, D, generator=g, device=self.device) * sc[1]).half()
                     self.compress_into(l, i, k, v, t0)
-                wl = int(self.win_len[i])
+                wl = int(self.write_pos[i] - self.boundary[i])
                 if wl:
                     k = (torch.randn(wl, H_KV, D, generator=g, device=self.device) * sc[0]).half()
                     v = (torch.randn(wl, H_KV, D, generator=g, device=self.device) * sc[1]).half()
@@ -171,22 +262,80 @@ class BatchEngine:
 
     # ---------------------------------------------------------------------------------- stepping
     def attention_resident(self, layer: int, scale: float = 1.0 / 16.0) -> None:
-        """The hot path alone: one batched launch for `layer`, inputs already in HBM."""
-        self.bd[layer].launch(scale, 1e7)
+        """The hot path alone: one batched attention launch for `layer` over the current state,
+        inputs already in HBM."""
+        rc = self.lib.launch_khq_decode_batched_fp16(
+            self.d_descs.data_ptr() + layer * self.B * SEQ_DESC.itemsize, self.d_tables.data_ptr(), self.d_items.data_ptr(),
+            self.B, self.n_items, self.workspace.data_ptr(), self.ws_bytes, self.n_items, float(scale), self.rope_theta, RING,
+            int(self.codebook_in_smem), current_stream())
+        check("launch_khq_decode_batched_fp16", rc)
 
     def decode_step(self, scale: float = 1.0 / 16.0) -> torch.Tensor:
-        """End-to-end token step from HOST buffers: for every layer copy this step's q_gate,
-        K (RoPE'd and raw) and V from pinned host memory (``h_q, h_kr, h_ku, h_v``), append them to
-        the rings at each sequence's newest slot, run the batched attention, and copy the gated
-        output back to ``h_out`` (returned; valid after the stream synchronises)."""
+        """End-to-end token step from HOST buffers.  ``h_q`` (L, B, 24*512: query and gate halves, the
+        query not yet normed or rotated), ``h_k`` and ``h_v`` (L, B, 4*256) hold this step's projections
+        in pinned host memory.  Every sequence advances by one token: append, compression event if
+        due, attention.  The gated outputs land in ``h_out`` (returned; valid once the stream has
+        synchronised)."""
+        ctl = self._ctl[self._step & 1]
+        if ctl["done"] is not None:
+            ctl["done"].synchronize()  # the copies that last read this parity's host block have finished
+        self._step += 1
+        # ---- host state machine (src/khq/runtime.mojo:486-553, for every sequence) -----------------
+        slots = (self.write_pos % RING).astype(np.int32)
+        pos = self.write_pos.astype(np.int32)
+        self.write_pos += 1
+        window = self.write_pos - self.boundary
+        due = np.nonzero((window >= WATERMARK) & (self.boundary + CHUNK <= self.cap))[0]
+        if (window[np.setdiff1d(np.arange(self.B), due)] > RING).any():
+            raise RuntimeError("a sequence's compressed capacity is exhausted (raise grow_tokens)")
+        ctl["slots"].numpy()[:] = slots
+        ctl["pos"].numpy()[:] = pos
+        n_ev = len(due)
+        if n_ev:
+            segs = ctl["segs"].numpy().view(COMPRESS_SEG).reshape(self.L, self.B)
+            for l in range(self.L):
+                base_u, base_v = self.ring_u[l].data_ptr(), self.ring_v[l].data_ptr()
+                s0 = (self.boundary[due] % RING)
+                off = (due * RING + s0) * KV * 2
+                segs["x"][l, :n_ev] = base_u + off
+                segs["row0"][l, :n_ev] = self.row_off[due] + self.boundary[due] * H_KV
+            # the V launch reads ring_v at the same offsets: keep the byte distance per layer
+            self._v_minus_u = [self.ring_v[l].data_ptr() - self.ring_u[l].data_ptr() for l in range(self.L)]
+        self.boundary[due] += CHUNK
+        self.events_fired += n_ev
+        st = current_stream()
+        self.d_slots.copy_(ctl["slots"], non_blocking=True)
+        self.d_pos.copy_(ctl["pos"], non_blocking=True)
+        if n_ev:
+            self.d_segs.copy_(ctl["segs"], non_blocking=True)
+        self._plan_and_upload(ctl)
+        if ctl["done"] is not None:
+            ctl["done"].record()
+        seg_bytes = self.B * COMPRESS_SEG.itemsize
         for l in range(self.L):
             self.q_gate[l].copy_(self.h_q[l], non_blocking=True)
-            self.d_kr.copy_(self.h_kr[l], non_blocking=True)
-            self.d_ku.copy_(self.h_ku[l], non_blocking=True)
+            self.d_k.copy_(self.h_k[l], non_blocking=True)
             self.d_v.copy_(self.h_v[l], non_blocking=True)
-            self.ring_k[l][self.bidx, self.new_slot] = self.d_kr
-            self.ring_u[l][self.bidx, self.new_slot] = self.d_ku
-            self.ring_v[l][self.bidx, self.new_slot] = self.d_v
-            self.bd[l].launch(scale, 1e7)
+            qw, kw = self.norm_w[l] if self.norm_w is not None else (None, None)
+            rc = self.lib.launch_khq_prestep_batched_fp16(
+                self.q_gate[l].data_ptr(), self.d_k.data_ptr(), self.d_v.data_ptr(), _lib.ptr(qw), _lib.ptr(kw),
+                self.ring_k[l].data_ptr(), self.ring_v[l].data_ptr(), self.ring_u[l].data_ptr(), RING * KV, self.d_slots.data_ptr(),
+                self.d_pos.data_ptr(), self.B, H_Q, H_KV, D, ROTARY_DIM, self.rope_theta, self.rms_eps, 1 if qw is not None else 0, st)
+            check("launch_khq_prestep_batched_fp16", rc)
+            if n_ev:
+                tb, P = self.tables[l], self.pay[l]
+                seg_ptr = self.d_segs.data_ptr() + l * seg_bytes
+                rc = self.lib.launch_khq_compress_batched_fp16(
+                    seg_ptr, n_ev, CHUNK * H_KV, tb["d_k"].data_ptr(), tb["k_rotor"].data_ptr(), tb["cents_k"].data_ptr(),
+                    tb["cents_k"].data_ptr(), P["k_mask"].data_ptr(), P["k_norms"].data_ptr(), P["k_r_norms"].data_ptr(),
+                    P["k_payload"].data_ptr(), P["v_shared_meta"].data_ptr(), D, float(tb["ts_k"]), float(tb["alpha_k"]), 0, 0, st)
+                check("launch_khq_compress_batched_fp16", rc)
+                rc = self.lib.launch_khq_compress_batched_fp16(
+                    seg_ptr, n_ev, CHUNK * H_KV, tb["d_v"].data_ptr(), tb["v_rotor"].data_ptr(), tb["cents_v"].data_ptr(),
+                    tb["vq"].data_ptr(), P["k_mask"].data_ptr(), P["v_norms"].data_ptr(), P["v_r_norms"].data_ptr(),
+                    P["v_payload"].data_ptr(), P["v_shared_meta"].data_ptr(), D, float(tb["ts_v"]), float(tb["alpha_v"]), 1,
+                    self._v_minus_u[l], st)
+                check("launch_khq_compress_batched_fp16", rc)
+            self.attention_resident(l, scale)
             self.h_out[l].copy_(self.out[l], non_blocking=True)
         return self.h_out

@@ -47,6 +47,11 @@ SIGNATURES = {
     "khq_b200_prefill_tc5_items_per_cta": (c_int, [c_int]),
     "khq_b200_prefill_status": (c_int, []),
     "launch_khq_prestep_fp16": (c_int, [_P] * 8 + [c_int] * 5 + [c_float, c_float, c_int, _P]),
+    "launch_khq_prestep_batched_fp16": (
+        c_int, [_P] * 8 + [c_longlong, _P, _P] + [c_int] * 5 + [c_float, c_float, c_int, _P]),
+    "launch_khq_compress_batched_fp16": (
+        c_int, [_P, c_int, c_int] + [_P] * 9 + [c_int, c_float, c_float, c_int, c_longlong, _P]),
+    "launch_khq_update_descs": (c_int, [_P, _P, c_int, c_int, _P]),
     "khq_b200_version": (c_char_p, []),
     "khq_b200_device_status": (c_int, []),
     "khq_b200_device_status_clear": (c_int, []),

@@ -164,8 +164,10 @@ size_t khq_b200_decode_workspace_bytes(int n_slots_total);
  * problems: a persistent kernel (one CTA per SM pulling items off an atomic counter in the
  * workspace) followed by a merge kernel.  descs/tables/items are DEVICE arrays; workspace is a
  * 256-byte-aligned device buffer of at least khq_b200_decode_workspace_bytes(n_slots_total).
- * codebook_in_smem: 1 stage each layer's V codebook in shared memory, 0 gather it from global
- * memory, -1 let the library choose.  Allocates nothing; the only non-kernel call is a 256-byte
+ * codebook_in_smem selects the kernel generation: 1 / 0 = CUDA-core kernel with each layer's V
+ * codebook staged in shared memory / gathered from global memory, 2 = warp-level tensor-core kernel
+ * (mma.sync), 3 = tcgen05 kernel (tensor-memory accumulators, code words decoded one payload row
+ * per thread), -1 let the library choose.  Allocates nothing; the only non-kernel call is a 256-byte
  * cudaMemsetAsync on `stream`.  Returns -100 (empty/NULL arguments), -104 (alignment), -105
  * (workspace too small). */
 int launch_khq_decode_batched_fp16(const void* descs, const void* tables, const void* items, int n_desc,
@@ -189,6 +191,42 @@ int launch_khq_prestep_fp16(void* q_gate, void* k, const void* v, const void* q_
                             const void* k_norm_w, void* ring_k_slot, void* ring_v_slot, void* ring_u_slot,
                             int H_q, int H_kv, int d, int rotary_dim, int pos, float rope_theta,
                             float rms_eps, int has_norms, khq_stream_t stream);
+
+/* ---- The same pre-step for `batch` sequences in one launch (no counterpart in the reference, which
+ * serves one sequence).  q_gate (batch, H_q, 2*d), k and v (batch, H_kv, d) fp16, in place as above.
+ * ring_k / ring_v / ring_u: base of the first sequence's ring; sequence b's rings start
+ * ring_seq_stride halfs further per b; its new token goes to slot slots[b] and is rotated at
+ * position positions[b] (device int32 arrays of `batch` entries).  Same return codes. */
+int launch_khq_prestep_batched_fp16(void* q_gate, void* k, const void* v, const void* q_norm_w,
+                                    const void* k_norm_w, void* ring_k, void* ring_v, void* ring_u,
+                                    long long ring_seq_stride, const void* slots, const void* positions,
+                                    int batch, int H_q, int H_kv, int d, int rotary_dim, float rope_theta,
+                                    float rms_eps, int has_norms, khq_stream_t stream);
+
+/* ---- Many compression events in one launch (no counterpart in the reference).
+ * launch_khq_compress_fp16 (src/csrc/qmv_sm75_kernel.cu:4279-4310) over `n_seg` runs of
+ * `rows_per_seg` rows: run i reads its fp16 rows from segs[i].x + x_byte_offset and writes rows
+ * segs[i].row0 .. segs[i].row0 + rows_per_seg - 1 of the output arrays.  `segs` is a device array
+ * of khq_compress_seg.  Row by row the arithmetic and the code words are those of the single
+ * launch.  Returns -100 (bad arguments), -104 (x_byte_offset not a multiple of 16). */
+typedef struct khq_compress_seg {
+    const void* x;      /* first source row of the run (fp16, d per row, contiguous) */
+    long long row0;     /* first output row of the run */
+} khq_compress_seg;
+int launch_khq_compress_batched_fp16(const void* segs, int n_seg, int rows_per_seg, const void* d_vec,
+                                     const void* rotor, const void* centroids, const void* vq_centroids,
+                                     void* out_mask, void* out_norms, void* out_r_norms, void* out_payload,
+                                     void* out_shared_meta, int d, float threshold_scale, float alpha,
+                                     int is_v, long long x_byte_offset, khq_stream_t stream);
+
+/* ---- Step-dependent descriptor fields of a batch engine (no counterpart in the reference).
+ * `descs`: n_layers * n_seq khq_seq_desc, layer-major; `dyn`: n_seq khq_seq_dyn, the state that
+ * moves every step and is the same for all layers of a sequence.  One launch copies dyn[s] into
+ * the eight ints of descs[l * n_seq + s] for every layer l; the pointers stay.  Returns -100. */
+typedef struct khq_seq_dyn {
+    int c_len, start_pos, win_start, win_len, first_slot, n_slots, reserved0, reserved1;
+} khq_seq_dyn;
+int launch_khq_update_descs(void* descs, const void* dyn, int n_seq, int n_layers, khq_stream_t stream);
 
 /* ---- One decode step of one sequence in two or three launches ------------------------------
  * What khq_step does between two compression events (src/khq/runtime.mojo:503-612: three ring

@@ -226,11 +226,11 @@ def test_prefill_full_length_vs_fp64_twin(cuda_ops, oracle, dtype):
     torch.cuda.synchronize()
     assert cuda_ops.lib.khq_b200_prefill_status() == 0
     rows = sorted({0, 1, 127, 128, 129, 8063, 8064, 8190, 8191} | set(np.random.default_rng(3).integers(0, T, 57).tolist()))
-    kh = k[0].half().cpu().numpy().reshape(T, H_KV * D)
-    vh = v[0].half().cpu().numpy().reshape(T, H_KV * D)
+    kh = np.ascontiguousarray(k[0].float().cpu().numpy().reshape(T, H_KV * D))  # the twin takes fp32 arrays
+    vh = np.ascontiguousarray(v[0].float().cpu().numpy().reshape(T, H_KV * D))
     worst = 0.0
     for r in rows:
-        want = oracle.gqa_attention_f32(qg[0, r].half().cpu().numpy(), kh, vh, r + 1, H_Q, H_KV, D, SCALE)
+        want = oracle.gqa_attention_f32(np.ascontiguousarray(qg[0, r].float().cpu().numpy()), kh, vh, r + 1, H_Q, H_KV, D, SCALE)
         got = out[0, r].float().cpu().numpy()
         if dtype == "fp16":
             ok, mx, exc = cases.attention_close(got, want)
