@@ -352,6 +352,13 @@ class KhqRuntime:
         H_q, H_kv, d = L.H_q, L.H_kv, L.D
         kv = H_kv * d
         T = int(k_roped_dev.shape[0])
+        # the prompt length comes from the leading dimension: refuse tensors whose sizes do not agree
+        # with it before any kernel is given their addresses
+        want = {"q_gate": T * H_q * 2 * d, "k_unroped": T * kv, "k_roped": T * kv, "v": T * kv, "out": T * H_q * d}
+        have = {"q_gate": q_gate_dev.numel(), "k_unroped": k_unroped_dev.numel(), "k_roped": k_roped_dev.numel(),
+                "v": v_dev.numel(), "out": out_dev.numel()}
+        if T <= 0 or any(have[k] != want[k] for k in want):
+            raise ValueError(f"khq_prefill: tensors do not hold T={T} rows of (H_q={H_q}, H_kv={H_kv}, d={d}): {have} vs {want}")
         ops.gqa_prefill(q_gate_dev, k_roped_dev, v_dev, out_dev, 1, T, H_q, H_kv, d, scale)
         # the per-token path compresses chunk c when write_pos reaches 128*(c+2), capped by `cap`
         n_chunks = 0
