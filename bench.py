@@ -70,6 +70,8 @@ def parse():
     ap.add_argument("--exchange", default="peer", choices=["peer", "collective"],
                     help="--workload long on N>1 GPUs: partials stored into the peers' buffers over NVLink (peer) or "
                          "one NCCL all-gather (collective)")
+    ap.add_argument("--partition", default="contiguous", choices=["contiguous", "cyclic"],
+                    help="--workload long / long_context: contiguous context ranges, or 128-token chunks dealt cyclically")
     ap.add_argument("--kernel", default="auto", choices=["auto", "cuda-core", "mma", "tc5"],
                     help="generation of the batched decode kernel")
     return ap.parse_args()
@@ -283,7 +285,8 @@ def long_measure(args, rank, world, dev, steps, warm):
     import torch.distributed as dist
 
     from bonsai_mojo_1bit_optimization_t4_cuda_b200 import lib as khqlib
-    from bonsai_mojo_1bit_optimization_t4_cuda_b200.context_parallel import ContextParallelDecode, partition_context
+    from bonsai_mojo_1bit_optimization_t4_cuda_b200.context_parallel import (ContextParallelDecode, cyclic_local_tokens,
+                                                                             partition_context)
     from bonsai_mojo_1bit_optimization_t4_cuda_b200.ops import CudaOps
 
     ops = CudaOps()
@@ -292,7 +295,10 @@ def long_measure(args, rank, world, dev, steps, warm):
     tab = {k: torch.from_numpy(v).to(dev) for k, v in dict(cents_k=f["cents_k"], cents_v=f["cents_v"], vq=f["vq"],
                                                             rotor_k=f["rotor_k"], rotor_v=f["rotor_v"], d_k=f["d_k"],
                                                             d_v=f["d_v"]).items()}
-    lo, hi = partition_context(args.long_ctx, world)[rank]
+    if args.partition == "cyclic":
+        lo, hi = 0, cyclic_local_tokens(args.long_ctx, world, rank)
+    else:
+        lo, hi = partition_context(args.long_ctx, world)[rank]
     n = hi - lo
     rows = max(n, 1) * 4
     g = torch.Generator(device=dev).manual_seed(20260914 + 2000 + rank)
@@ -315,12 +321,12 @@ def long_measure(args, rank, world, dev, steps, warm):
     owner = world - 1
     exchange = args.exchange if world > 1 else "collective"
     cp = ContextParallelDecode(ops, dist.group.WORLD, kv, tab, lo, hi, tb.alpha_k, tb.alpha_v, ring_k, ring_v, owner=owner,
-                               splits=args.splits, device=dev, exchange=exchange)
+                               splits=args.splits, device=dev, exchange=exchange, partition=args.partition)
     checked = None
     if world > 1 and exchange == "peer":
         # the two exchanges must give the same answer
         ref = ContextParallelDecode(ops, dist.group.WORLD, kv, tab, lo, hi, tb.alpha_k, tb.alpha_v, ring_k, ring_v, owner=owner,
-                                    splits=args.splits, device=dev, exchange="collective")
+                                    splits=args.splits, device=dev, exchange="collective", partition=args.partition)
         qg0 = torch.randn(24 * 512, generator=g, device=dev).half()
         a = cp.step(qg0.clone(), args.long_ctx % 256, 256).clone()
         b = ref.step(qg0.clone(), args.long_ctx % 256, 256).clone()
@@ -350,7 +356,8 @@ def long_measure(args, rank, world, dev, steps, warm):
     return {"us_per_layer_step": us, "algorithmic_bytes_per_step": b_alg, "achieved_gbs": b_alg / (us * 1e-6) / 1e9,
             "exchange": ("peer stores over NVLink, the merge kernel waits for the producers' flags" if exchange == "peer" and world > 1
                          else "one NCCL all-gather of the (24, 258) partials" if world > 1 else "none (one rank)"),
-            "partition": "contiguous context ranges cut on 128-token chunks", "tokens": args.long_ctx, "raw_tokens": win_len,
+            "partition": ("128-token chunks dealt cyclically (chunk c on rank c mod N)" if args.partition == "cyclic"
+                          else "contiguous context ranges cut on 128-token chunks"), "tokens": args.long_ctx, "raw_tokens": win_len,
             "splits": args.splits, "steps": steps, "warmup": warm, "checked": checked, "device_status": status,
             "gpu_launches_per_step": 5}
 

@@ -15,7 +15,7 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_NAME = "libbonsai_khq_b200.so"
 LIB_PATH = PKG_DIR / LIB_NAME
-SOURCES = ["khq_compress.cu", "khq_decode.cu", "khq_prefill.cu", "khq_prefill_tc5.cu", "khq_prestep.cu"]
+SOURCES = ["khq_compress.cu", "khq_decode.cu", "khq_prefill.cu", "khq_prefill_tc5.cu", "khq_prestep.cu", "khq_calib.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",

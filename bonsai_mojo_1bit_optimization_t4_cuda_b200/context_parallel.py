@@ -39,6 +39,22 @@ def partition_context(c_len: int, world: int, chunk: int = CHUNK) -> List[Tuple[
     return out
 
 
+def partition_context_cyclic(c_len: int, world: int, chunk: int = CHUNK) -> List[List[int]]:
+    """Chunk-cyclic partition: chunk c (tokens [c * chunk, (c + 1) * chunk)) goes to rank c mod world,
+    so the chunks a growing context appends keep the ranks balanced to within one chunk.  Returns, per
+    rank, its chunk indices in ascending order.  A rank's local arrays hold its chunks back to back;
+    local token s then sits at absolute position rank * chunk + (s // chunk) * world * chunk + s % chunk,
+    which is what ``launch_khq_attn_strided_fp16`` takes.  Only the last chunk of the context may be
+    partial, and it is then the last local chunk of its rank."""
+    n_chunks = (c_len + chunk - 1) // chunk
+    return [list(range(r, n_chunks, world)) for r in range(world)]
+
+
+def cyclic_local_tokens(c_len: int, world: int, rank: int, chunk: int = CHUNK) -> int:
+    """How many of the c_len tokens a rank holds under the chunk-cyclic partition."""
+    return sum(min(chunk, c_len - c * chunk) for c in partition_context_cyclic(c_len, world, chunk)[rank])
+
+
 class PeerExchange:
     """Slot buffers and flags of a context-parallel group, mapped into every process with CUDA IPC
     (the library's ``khq_b200_peer_*`` helpers: plain ``cudaMalloc`` memory, opened by each peer on
@@ -155,10 +171,13 @@ class ContextParallelDecode:
     """
 
     def __init__(self, ops, group, kv: dict, tables: dict, lo: int, hi: int, alpha_k: float, alpha_v: float,
-                 ring_k=None, ring_v=None, owner: int = 0, splits: int = 32, device="cuda", exchange: str = "collective"):
+                 ring_k=None, ring_v=None, owner: int = 0, splits: int = 32, device="cuda", exchange: str = "collective",
+                 partition: str = "contiguous"):
         """``exchange``: "collective" = one all-gather of the partials (NCCL / gloo), "peer" = every
         rank stores its partials into the peers' buffers over NVLink and the merge kernel waits for
-        the flags (``PeerExchange``; CUDA only)."""
+        the flags (``PeerExchange``; CUDA only).  ``partition``: "contiguous" = ``kv`` holds the rows of
+        tokens ``[lo, hi)``; "cyclic" = ``kv`` holds this rank's chunks of the chunk-cyclic partition
+        back to back (``hi - lo`` local tokens; ``lo`` is ignored)."""
         self.ops, self.group = ops, group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
@@ -167,6 +186,8 @@ class ContextParallelDecode:
         self.alpha_k, self.alpha_v = alpha_k, alpha_v
         self.ring_k, self.ring_v, self.owner = ring_k, ring_v, owner
         self.splits = splits
+        assert partition in ("contiguous", "cyclic")
+        self.partition = partition
         dev = torch.device(device)
         # slot-major partials: [rank][0 = compressed slice, 1 = raw window]
         self.mine = torch.zeros(2, H_Q, PART, dtype=torch.float32, device=dev)
@@ -222,7 +243,13 @@ class ContextParallelDecode:
         elif broadcast_q and self.world > 1:
             dist.broadcast(q_gate, src=dist.get_global_rank(self.group, self.owner), group=self.group)
         n = self.hi - self.lo
-        if n > 0:
+        if n > 0 and self.partition == "cyclic":
+            ops.attn_strided(q_gate, kv["k_payload"], kv["v_payload"], kv["v_shared_meta"], kv["k_mask"], kv["k_norms"],
+                             kv["k_r_norms"], kv["v_norms"], kv["v_r_norms"], tb["cents_k"], tb["cents_v"], tb["vq"],
+                             tb["rotor_k"], tb["rotor_v"], tb["d_k"], tb["d_v"], self.mine[0], self.scratch, H_Q, H_Q, 1, n,
+                             H_Q // H_KV, scale, self.alpha_k, self.alpha_v, rope_base, self.rank * CHUNK, self.split_count(n),
+                             CHUNK, self.world * CHUNK)
+        elif n > 0:
             ops.attn(q_gate, kv["k_payload"], kv["v_payload"], kv["v_shared_meta"], kv["k_mask"], kv["k_norms"],
                      kv["k_r_norms"], kv["v_norms"], kv["v_r_norms"], tb["cents_k"], tb["cents_v"], tb["vq"],
                      tb["rotor_k"], tb["rotor_v"], tb["d_k"], tb["d_v"], self.mine[0], self.scratch, H_Q, H_Q, 1, n,

@@ -57,12 +57,12 @@ __device__ __forceinline__ void stage_tile(const CompressedKV& P, unsigned char*
     }
 }
 
-// RoPE cos/sin of one tile: entry (t, m) for position start_pos + tok0 + t and pair m < 32.
+// RoPE cos/sin of one tile: entry (t, m) for the position of token tok0 + t and pair m < 32.
 // The angle is formed in double so that it stays exact at positions beyond 1e5.
-__device__ __forceinline__ void fill_rope(float2* tab, const float* freq, int pos0, int tid) {
+__device__ __forceinline__ void fill_rope(float2* tab, const float* freq, const CompressedKV& P, int tok0, int tid) {
     for (int e = tid; e < TT * 32; e += DEC_THREADS) {
         const int t = e >> 5, m = e & 31;
-        double th = (double)(pos0 + t) * (double)freq[m];
+        double th = (double)token_pos(P, tok0 + t) * (double)freq[m];
         th -= rint(th * 0.15915494309189535) * 6.283185307179586;
         float s, c;
         __sincosf((float)th, &s, &c);
@@ -129,7 +129,7 @@ __device__ __forceinline__ void compressed_range(unsigned char* smem, const __ha
 
     const int base = my_lo & ~1;
     const int ntiles = (my_hi > my_lo) ? (my_hi - base + TT - 1) / TT : 0;
-    if (ntiles > 0) fill_rope(rope_tab, freq_s, P.start_pos + base, tid);
+    if (ntiles > 0) fill_rope(rope_tab, freq_s, P, base, tid);
 
     // per-lane constants
     float cbase[8], dinv[8], qv[NREP][8], c3[2][2];
@@ -184,7 +184,7 @@ __device__ __forceinline__ void compressed_range(unsigned char* smem, const __ha
             }
         }
         if (i + 1 < ntiles)
-            fill_rope(rope_tab + ((i + 1) & 1) * TT * 32, freq_s, P.start_pos + base + (i + 1) * TT, tid);
+            fill_rope(rope_tab + ((i + 1) & 1) * TT * 32, freq_s, P, base + (i + 1) * TT, tid);
         mbar_wait_bounded(&bars[stg], (uint32_t)((g / NSTAGE) & 1), &g_status);
 
         const unsigned char* S = smem + SM_STAGES + stg * STAGE_BYTES;
@@ -562,7 +562,7 @@ khq_decode_batched_kernel(const KhqSeqDesc* __restrict__ descs, const KhqTablesD
             P.cents_k = t.cents_k; P.cents_v = t.cents_v; P.vq = t.vq; P.k_rotor = t.k_rotor;
             P.v_rotor = t.v_rotor; P.d_k = t.d_k; P.d_v = t.d_v;
             P.alpha_k = t.alpha_k; P.alpha_v = t.alpha_v; P.rope_base = rope_base;
-            P.start_pos = d.start_pos; P.c_len = d.c_len; P.bulk_ok = 1;
+            P.start_pos = d.start_pos; P.c_len = d.c_len; P.bulk_ok = 1; P.pos_chunk = 0; P.pos_stride = 0;
             if (d.table_id != cur_table) {
                 setup_tables(smem, P, tid);
                 if (VQS) load_codebook(reinterpret_cast<unsigned short*>(smem + SM_VQ), P.vq, tid);
@@ -899,16 +899,16 @@ static int max_clusters(bool mma, int c) {
 
 using namespace khq;
 
-extern "C" int launch_khq_attn_fp16(const void* q, const void* k_payload, const void* v_payload,
-                                    const void* v_shared_meta, const void* k_mask, const void* k_norms,
-                                    const void* k_r_norms, const void* v_norms, const void* v_r_norms,
-                                    const void* centroids_k, const void* centroids_v,
-                                    const void* vq_centroids, const void* k_rotor, const void* v_rotor,
-                                    const void* d_vec_k, const void* d_vec_v, void* out_attn,
-                                    void* out_partial, int num_queries, int num_heads, int L_q, int c_len,
-                                    int stride_s, int n_rep, float scale, float alpha_k, float alpha_v,
-                                    float rope_base, int start_pos, int num_splits, cudaStream_t stream) {
-    (void)stride_s;
+static int attn_launch_impl(const void* q, const void* k_payload, const void* v_payload,
+                            const void* v_shared_meta, const void* k_mask, const void* k_norms,
+                            const void* k_r_norms, const void* v_norms, const void* v_r_norms,
+                            const void* centroids_k, const void* centroids_v,
+                            const void* vq_centroids, const void* k_rotor, const void* v_rotor,
+                            const void* d_vec_k, const void* d_vec_v, void* out_attn,
+                            void* out_partial, int num_queries, int num_heads, int L_q, int c_len,
+                            int n_rep, float scale, float alpha_k, float alpha_v,
+                            float rope_base, int start_pos, int num_splits, int pos_chunk, int pos_stride,
+                            cudaStream_t stream) {
     if (num_queries <= 0 || c_len <= 0) return -100;
     if (num_splits < 1) num_splits = 1;
     if (num_splits > 1 && out_partial == nullptr) return -101;
@@ -948,6 +948,8 @@ extern "C" int launch_khq_attn_fp16(const void* q, const void* k_payload, const 
     P.start_pos = start_pos;
     P.c_len = c_len;
     P.bulk_ok = bulk_ok ? 1 : 0;
+    P.pos_chunk = pos_chunk;
+    P.pos_stride = pos_stride;
 
     for (int l = 0; l < L_q; ++l) {
         const int s_limit = (L_q > 1) ? (c_len < l + 1 ? c_len : l + 1) : c_len;
@@ -997,6 +999,43 @@ extern "C" int launch_khq_attn_fp16(const void* q, const void* k_payload, const 
         if (err != cudaSuccess) return static_cast<int>(err);
     }
     return 0;
+}
+
+extern "C" int launch_khq_attn_fp16(const void* q, const void* k_payload, const void* v_payload,
+                                    const void* v_shared_meta, const void* k_mask, const void* k_norms,
+                                    const void* k_r_norms, const void* v_norms, const void* v_r_norms,
+                                    const void* centroids_k, const void* centroids_v,
+                                    const void* vq_centroids, const void* k_rotor, const void* v_rotor,
+                                    const void* d_vec_k, const void* d_vec_v, void* out_attn,
+                                    void* out_partial, int num_queries, int num_heads, int L_q, int c_len,
+                                    int stride_s, int n_rep, float scale, float alpha_k, float alpha_v,
+                                    float rope_base, int start_pos, int num_splits, cudaStream_t stream) {
+    (void)stride_s;
+    return attn_launch_impl(q, k_payload, v_payload, v_shared_meta, k_mask, k_norms, k_r_norms, v_norms, v_r_norms,
+                            centroids_k, centroids_v, vq_centroids, k_rotor, v_rotor, d_vec_k, d_vec_v, out_attn, out_partial,
+                            num_queries, num_heads, L_q, c_len, n_rep, scale, alpha_k, alpha_v, rope_base, start_pos,
+                            num_splits, 0, 0, stream);
+}
+
+// launch_khq_attn_fp16 over a slice that holds every G-th `pos_chunk`-token chunk of a longer context
+// (chunk-cyclic context partition over G GPUs): token s of the arrays sits at absolute position
+// start_pos + (s / pos_chunk) * pos_stride + s % pos_chunk.  pos_chunk must be even and positive,
+// pos_stride >= pos_chunk; -103 otherwise.  No counterpart in the reference (it serves one GPU).
+extern "C" int launch_khq_attn_strided_fp16(const void* q, const void* k_payload, const void* v_payload,
+                                            const void* v_shared_meta, const void* k_mask, const void* k_norms,
+                                            const void* k_r_norms, const void* v_norms, const void* v_r_norms,
+                                            const void* centroids_k, const void* centroids_v,
+                                            const void* vq_centroids, const void* k_rotor, const void* v_rotor,
+                                            const void* d_vec_k, const void* d_vec_v, void* out_attn,
+                                            void* out_partial, int num_queries, int num_heads, int L_q, int c_len,
+                                            int n_rep, float scale, float alpha_k, float alpha_v, float rope_base,
+                                            int start_pos, int num_splits, int pos_chunk, int pos_stride,
+                                            cudaStream_t stream) {
+    if (pos_chunk <= 0 || (pos_chunk & 1) || pos_stride < pos_chunk) return -103;
+    return attn_launch_impl(q, k_payload, v_payload, v_shared_meta, k_mask, k_norms, k_r_norms, v_norms, v_r_norms,
+                            centroids_k, centroids_v, vq_centroids, k_rotor, v_rotor, d_vec_k, d_vec_v, out_attn, out_partial,
+                            num_queries, num_heads, L_q, c_len, n_rep, scale, alpha_k, alpha_v, rope_base, start_pos,
+                            num_splits, pos_chunk, pos_stride, stream);
 }
 
 extern "C" int launch_khq_window_attn_fp16(const void* q, const void* ring_k, const void* ring_v,

@@ -103,7 +103,16 @@ struct CompressedKV {  // device pointers of one sequence-layer's compressed reg
     int start_pos;  // absolute position of compressed token 0
     int c_len;      // valid tokens in the arrays
     int bulk_ok;    // all eight arrays 16-byte aligned
+    // Positions of a slice that holds every G-th chunk of a longer context (chunk-cyclic context
+    // partition): token s of the arrays sits at start_pos + (s / pos_chunk) * pos_stride + s % pos_chunk.
+    // pos_chunk == 0: consecutive positions.
+    int pos_chunk, pos_stride;
 };
+
+// Absolute position of token `tok` of the arrays.
+__device__ __forceinline__ int token_pos(const CompressedKV& P, int tok) {
+    return P.start_pos + (P.pos_chunk > 0 ? (tok / P.pos_chunk) * P.pos_stride + tok % P.pos_chunk : tok);
+}
 
 // Per-warp running state: 6 query heads x the lane's 8 dims.
 struct WarpState {

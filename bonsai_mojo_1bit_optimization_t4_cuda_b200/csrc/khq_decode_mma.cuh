@@ -134,10 +134,10 @@ __device__ __forceinline__ void m2_stage_tile(const CompressedKV& P, unsigned ch
     }
 }
 
-__device__ __forceinline__ void m2_fill_rope(float2* tab, const float* freq, int pos0, int tid) {
+__device__ __forceinline__ void m2_fill_rope(float2* tab, const float* freq, const CompressedKV& P, int tok0, int tid) {
     for (int e = tid; e < M2_TT * 32; e += M2_THREADS) {
         const int t = e >> 5, m = e & 31;
-        double th = (double)(pos0 + t) * (double)freq[m];
+        double th = (double)token_pos(P, tok0 + t) * (double)freq[m];
         th -= rint(th * 0.15915494309189535) * 6.283185307179586;
         float s, c;
         __sincosf((float)th, &s, &c);
@@ -600,7 +600,7 @@ __device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const _
     const int ntiles = (my_hi > my_lo) ? (my_hi - base + M2_TT - 1) / M2_TT : 0;
     const unsigned t0 = tiles_done;
     if (ntiles > 0) {
-        m2_fill_rope(rope_tab, freq_s, P.start_pos + base, tid);
+        m2_fill_rope(rope_tab, freq_s, P, base, tid);
         m2_stage_tile(P, smem + M2_SM_STAGES + (t0 % M2_NSTAGE) * M2_STAGE_BYTES, &bars[t0 % M2_NSTAGE], base,
                       min(M2_TT, P.c_len - base), tid);
     }
@@ -615,7 +615,7 @@ __device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const _
             const int tok0 = base + (i + 1) * M2_TT;
             m2_stage_tile(P, smem + M2_SM_STAGES + ((gi + 1) % M2_NSTAGE) * M2_STAGE_BYTES, &bars[(gi + 1) % M2_NSTAGE],
                           tok0, min(M2_TT, P.c_len - tok0), tid);
-            m2_fill_rope(rope_tab + ((i + 1) & 1) * M2_TT * 32, freq_s, P.start_pos + tok0, tid);
+            m2_fill_rope(rope_tab + ((i + 1) & 1) * M2_TT * 32, freq_s, P, tok0, tid);
         }
         mbar_wait_bounded(&bars[stg], (uint32_t)((gi / M2_NSTAGE) & 1), &g_status);
         const int blk0 = base + i * M2_TT + 16 * sub;
@@ -697,7 +697,7 @@ khq_decode_batched_mma_kernel(const KhqSeqDesc* __restrict__ descs, const KhqTab
             P.cents_k = tb.cents_k; P.cents_v = tb.cents_v; P.vq = tb.vq; P.k_rotor = tb.k_rotor;
             P.v_rotor = tb.v_rotor; P.d_k = tb.d_k; P.d_v = tb.d_v;
             P.alpha_k = tb.alpha_k; P.alpha_v = tb.alpha_v; P.rope_base = rope_base;
-            P.start_pos = d.start_pos; P.c_len = d.c_len; P.bulk_ok = 1;
+            P.start_pos = d.start_pos; P.c_len = d.c_len; P.bulk_ok = 1; P.pos_chunk = 0; P.pos_stride = 0;
             if (d.table_id != cur_table) {
                 m2_setup_tables(smem, P, tid);
                 cur_table = d.table_id;

@@ -135,10 +135,12 @@ __device__ __forceinline__ void tc_before() { asm volatile("tcgen05.fence::befor
 __device__ __forceinline__ void tc_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tm_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tm_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// Tensor-memory stores carry no "memory" clobber: they do not touch ordinary memory, and the clobber would stop
+// the compiler from overlapping the shared-memory loads of one mask word with the stores of the previous one.
+// They stay ordered among themselves and with the waits and fences (all asm volatile).
 __device__ __forceinline__ void tm_st8(uint32_t taddr, const uint32_t (&r)[8]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%8], {%0,%1,%2,%3,%4,%5,%6,%7};" ::"r"(r[0]), "r"(r[1]), "r"(r[2]),
-                 "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(taddr)
-                 : "memory");
+                 "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(taddr));
 }
 __device__ __forceinline__ void tm_ld16(uint32_t taddr, uint32_t* r) {
     asm volatile(
@@ -156,8 +158,7 @@ __device__ __forceinline__ void tm_st16(uint32_t taddr, const uint32_t* r) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15};" ::"r"(r[0]),
         "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
-        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(taddr)
-        : "memory");
+        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(taddr));
 }
 __device__ __forceinline__ float ex2f(float x) {
     float y;
@@ -847,7 +848,7 @@ khq_decode_batched_tc5_kernel(const KhqSeqDesc* __restrict__ descs, const KhqTab
             P.cents_k = tb.cents_k; P.cents_v = tb.cents_v; P.vq = tb.vq; P.k_rotor = tb.k_rotor;
             P.v_rotor = tb.v_rotor; P.d_k = tb.d_k; P.d_v = tb.d_v;
             P.alpha_k = tb.alpha_k; P.alpha_v = tb.alpha_v; P.rope_base = rope_base;
-            P.start_pos = d.start_pos; P.c_len = d.c_len; P.bulk_ok = 1;
+            P.start_pos = d.start_pos; P.c_len = d.c_len; P.bulk_ok = 1; P.pos_chunk = 0; P.pos_stride = 0;
             if (d.table_id != cur_table) {
                 if (tid == 0) soft->all_alpha = 1;
                 __syncthreads();

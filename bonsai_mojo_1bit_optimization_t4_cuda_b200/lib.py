@@ -24,6 +24,10 @@ SIGNATURES = {
         c_int,
         [_P] * 18 + [c_int] * 5 + [c_int, c_float, c_float, c_float, c_float, c_int, c_int, _P],
     ),
+    "launch_khq_attn_strided_fp16": (
+        c_int,
+        [_P] * 18 + [c_int] * 4 + [c_int, c_float, c_float, c_float, c_float, c_int, c_int, c_int, c_int, _P],
+    ),
     "launch_khq_window_attn_fp16": (c_int, [_P] * 4 + [c_int] * 6 + [c_float, _P]),
     "launch_khq_merge_gate_fp16": (c_int, [_P] * 4 + [c_int, c_int, c_int, _P]),
     "launch_khq_gather_q_fp16": (c_int, [_P, _P, c_int, c_int, _P]),
@@ -52,6 +56,7 @@ SIGNATURES = {
     "launch_khq_compress_batched_fp16": (
         c_int, [_P, c_int, c_int] + [_P] * 9 + [c_int, c_float, c_float, c_int, c_longlong, _P]),
     "launch_khq_update_descs": (c_int, [_P, _P, c_int, c_int, _P]),
+    "launch_khq_cal_kstatic_fp32": (c_int, [_P, c_int, _P, _P, _P, _P]),
     "khq_b200_version": (c_char_p, []),
     "khq_b200_device_status": (c_int, []),
     "khq_b200_device_status_clear": (c_int, []),

@@ -42,6 +42,20 @@ class CudaOps:
             float(rope_base), int(start_pos), int(num_splits), current_stream())
         check("launch_khq_attn_fp16", rc)
 
+    # -- launch_khq_attn_strided_fp16: a slice holding every G-th chunk of a longer context ------------
+    def attn_strided(self, q, k_payload, v_payload, v_shared_meta, k_mask, k_norms, k_r_norms, v_norms,
+                     v_r_norms, centroids_k, centroids_v, vq_centroids, k_rotor, v_rotor, d_vec_k, d_vec_v,
+                     out_attn, out_partial, num_queries, num_heads, L_q, c_len, n_rep, scale, alpha_k, alpha_v,
+                     rope_base, start_pos, num_splits, pos_chunk, pos_stride):
+        rc = self.lib.launch_khq_attn_strided_fp16(
+            ptr(q), ptr(k_payload), ptr(v_payload), ptr(v_shared_meta), ptr(k_mask), ptr(k_norms),
+            ptr(k_r_norms), ptr(v_norms), ptr(v_r_norms), ptr(centroids_k), ptr(centroids_v),
+            ptr(vq_centroids), ptr(k_rotor), ptr(v_rotor), ptr(d_vec_k), ptr(d_vec_v),
+            ptr(out_attn), ptr(out_partial), int(num_queries), int(num_heads), int(L_q), int(c_len),
+            int(n_rep), float(scale), float(alpha_k), float(alpha_v), float(rope_base), int(start_pos),
+            int(num_splits), int(pos_chunk), int(pos_stride), current_stream())
+        check("launch_khq_attn_strided_fp16", rc)
+
     # -- launch_khq_window_attn_fp16 -----------------------------------------------------------
     def window_attn(self, q, ring_k, ring_v, out_attn, win_start, win_len, ring_cap, H_q, H_kv, d,
                     scale):
@@ -127,6 +141,11 @@ class CudaOps:
 
     # -- ring appends (khq_ring_dual_sm75_gpu / copy_vec_sm75_gpu,
     #    src/kernels/elementwise_sm75.mojo:277-312): device-to-device copies ------------------
+    # -- launch_khq_cal_kstatic_fp32: K-static fit (op 2 of the reference's launch_cal_op) -------------
+    def cal_kstatic(self, rot, rows, cents, out_ts, sigma_out=None):
+        rc = self.lib.launch_khq_cal_kstatic_fp32(ptr(rot), int(rows), ptr(cents), ptr(out_ts), ptr(sigma_out), current_stream())
+        check("launch_khq_cal_kstatic_fp32", rc)
+
     def ring_write(self, dst_row, src):
         dst_row.copy_(src.reshape(dst_row.shape), non_blocking=True)
 

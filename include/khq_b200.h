@@ -305,6 +305,23 @@ int khq_b200_prefill_status(void);
 int launch_khq_merge_slots_gate_fp16(const void* partials, int n_slots, const void* q_gate, void* out,
                                      int H_q, int d, khq_stream_t stream);
 
+/* No counterpart in the reference (it serves one GPU).  launch_khq_attn_fp16 over a slice that holds
+ * every G-th `pos_chunk`-token chunk of a longer context, which is what a GPU holds when the
+ * compressed region is partitioned chunk-cyclically over G GPUs (chunk c on GPU c mod G, so appended
+ * chunks keep the GPUs balanced): token s of the arrays sits at absolute position
+ * start_pos + (s / pos_chunk) * pos_stride + s % pos_chunk (GPU g of G: start_pos = g * 128,
+ * pos_chunk = 128, pos_stride = G * 128).  Same arguments otherwise, without `stride_s`.  pos_chunk
+ * must be positive and even, pos_stride >= pos_chunk, else -103. */
+int launch_khq_attn_strided_fp16(const void* q, const void* k_payload, const void* v_payload,
+                                 const void* v_shared_meta, const void* k_mask, const void* k_norms,
+                                 const void* k_r_norms, const void* v_norms, const void* v_r_norms,
+                                 const void* centroids_k, const void* centroids_v,
+                                 const void* vq_centroids, const void* k_rotor, const void* v_rotor,
+                                 const void* d_vec_k, const void* d_vec_v, void* out_attn, void* out_partial,
+                                 int num_queries, int num_heads, int L_q, int c_len, int n_rep, float scale,
+                                 float alpha_k, float alpha_v, float rope_base, int start_pos, int num_splits,
+                                 int pos_chunk, int pos_stride, khq_stream_t stream);
+
 /* No counterpart in the reference.  launch_khq_attn_fp16 for callers that cannot hand over a
  * partial buffer: the split partials go to a fixed array inside the library's device image
  * (24 heads x up to 32 splits x 258 floats = 792 576 bytes per GPU that loads the library)
@@ -328,6 +345,18 @@ int launch_khq_attn_static_fp16(const void* q, const void* k_payload, const void
                                 int num_queries, int num_heads, int L_q, int c_len, int n_rep,
                                 float scale, float alpha_k, float alpha_v, float rope_base,
                                 int start_pos, int num_splits, khq_stream_t stream);
+
+/* ---- Calibration: the K-static fit -----------------------------------------------------------
+ * cal_kstatic_p_kernel + cal_kstatic_f_kernel of the reference (src/csrc/qmv_sm75_kernel.cu:2645-2680;
+ * op 2 of launch_cal_op, :4634-4643): from the projected K sample `rot` (rows, 256) fp32 the per-dim
+ * sigma, the threshold scale ts = 16 / sqrt(sum_i 0.528756 (0.935 sigma_i)^2 + 0.464545 sigma_i^2)
+ * and the four base centroid rows {0, -cb, +cb, +cb}, cb_i = 0.935 sigma_i ts (`cents`, 4 x 256 fp32;
+ * `out_ts`, 1 fp32; `sigma_out`, 256 fp32 or NULL; all device memory).  Same summation order as the
+ * reference, so the tables are bit-identical; unlike it, nothing is allocated and the stream is not
+ * synchronised.  The other calibration operations are offline work outside this library.
+ * Returns -100 on bad arguments. */
+int launch_khq_cal_kstatic_fp32(const void* rot, int rows, void* cents, void* out_ts, void* sigma_out,
+                                khq_stream_t stream);
 
 /* Library identification: "khq-b200 <version> sm_100a". */
 const char* khq_b200_version(void);

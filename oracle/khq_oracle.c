@@ -752,3 +752,40 @@ void khq_oracle_head_rmsnorm(uint16_t* x, int num_heads, int head_dim, int strid
         }
     }
 }
+
+/* K-static calibration fit (src/csrc/qmv_sm75_kernel.cu:2645-2680, cal_kstatic_p_kernel +
+ * cal_kstatic_f_kernel): per-dim sigma of the projected sample rot (rows, 256) fp32 by a serial
+ * mean and a serial sum of squared deviations, ts = 16 / sqrt(sum_i 0.528756 (0.935 sigma_i)^2 +
+ * 0.464545 sigma_i^2) summed serially, centroid rows {0, -cb, cb, cb} with cb = 0.935 sigma ts.
+ * The device build of the reference fuses dv*dv into the running sum (-fmad=true), restated here
+ * with fmaf; which product of the two-term psum expression it fuses is the compiler's choice, so
+ * callers compare ts and the centroids within a few ulp. */
+void khq_oracle_cal_kstatic(const float* rot, int rows, float* cents, float* out_ts, float* sigma) {
+    float psum[256], sg_[256];
+    for (int i = 0; i < 256; ++i) {
+        float m = 0.0f;
+        for (int r = 0; r < rows; ++r) m += rot[(size_t)r * 256 + i];
+        m /= (float)rows;
+        float v = 0.0f;
+        for (int r = 0; r < rows; ++r) {
+            float dv = rot[(size_t)r * 256 + i] - m;
+            v = fmaf(dv, dv, v);
+        }
+        float sg = sqrtf(v / (float)rows);
+        sg_[i] = sg;
+        if (sigma) sigma[i] = sg;
+        float cb = 0.9350f * sg;
+        psum[i] = fmaf(0.464545f * sg, sg, 0.528756f * cb * cb);
+    }
+    float se = 0.0f;
+    for (int i = 0; i < 256; ++i) se += psum[i];
+    float ts = 16.0f / sqrtf(se);
+    for (int i = 0; i < 256; ++i) {
+        float cb = 0.9350f * sg_[i] * ts;
+        cents[0 * 256 + i] = 0.0f;
+        cents[1 * 256 + i] = -cb;
+        cents[2 * 256 + i] = cb;
+        cents[3 * 256 + i] = cb;
+    }
+    out_ts[0] = ts;
+}

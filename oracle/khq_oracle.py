@@ -201,6 +201,17 @@ def head_rmsnorm(x, num_heads, head_dim, stride, weight, eps):
     return x
 
 
+def cal_kstatic(rot):
+    """K-static fit of a projected sample (rows, 256) fp32 -> (cents (4, 256), ts, sigma (256,))."""
+    lib = load()
+    rot = np.ascontiguousarray(rot, np.float32)
+    cents = np.zeros((4, 256), np.float32)
+    ts = np.zeros(1, np.float32)
+    sigma = np.zeros(256, np.float32)
+    lib.khq_oracle_cal_kstatic(_p(rot), c_int(rot.shape[0]), _p(cents), _p(ts), _p(sigma))
+    return cents, float(ts[0]), sigma
+
+
 # ---------------------------------------------------------------------------- launch backend
 class OracleLaunchError(RuntimeError):
     def __init__(self, name, code):
@@ -231,6 +242,34 @@ class OracleOps:
                          alpha_k, alpha_v, rope_base, start_pos, num_splits)
         if rc:
             raise OracleLaunchError("attn", rc)
+
+    def attn_strided(self, q, k_payload, v_payload, v_shared_meta, k_mask, k_norms, k_r_norms, v_norms,
+                     v_r_norms, centroids_k, centroids_v, vq_centroids, k_rotor, v_rotor, d_vec_k, d_vec_v,
+                     out_attn, out_partial, num_queries, num_heads, L_q, c_len, n_rep, scale, alpha_k, alpha_v,
+                     rope_base, start_pos, num_splits, pos_chunk, pos_stride):
+        """A slice whose local chunk j sits at absolute position start_pos + j * pos_stride: one oracle
+        call per chunk at that position, then the oracle's own split reduce over the chunks."""
+        assert L_q == 1
+        np_ = lambda a: a if isinstance(a, np.ndarray) else a.numpy()
+        arrs = {"k_payload": (np_(k_payload), 40), "v_payload": (np_(v_payload), 104), "v_shared_meta": (np_(v_shared_meta), 4),
+                "k_mask": (np_(k_mask), 16), "k_norms": (np_(k_norms), 1), "k_r_norms": (np_(k_r_norms), 1),
+                "v_norms": (np_(v_norms), 1), "v_r_norms": (np_(v_r_norms), 1)}
+        n_chunks = (c_len + pos_chunk - 1) // pos_chunk
+        parts = np.zeros((num_heads, n_chunks, PART), np.float32)
+        for j in range(n_chunks):
+            t0, t1 = j * pos_chunk, min(c_len, (j + 1) * pos_chunk)
+            sl = {k: np.ascontiguousarray(a.reshape(-1)[t0 * 4 * w:t1 * 4 * w]) for k, (a, w) in arrs.items()}
+            one = np.zeros((num_heads, PART), np.float32)
+            rc = attn_launch(q, sl["k_payload"], sl["v_payload"], sl["v_shared_meta"], sl["k_mask"], sl["k_norms"], sl["k_r_norms"],
+                             sl["v_norms"], sl["v_r_norms"], centroids_k, centroids_v, vq_centroids, k_rotor, v_rotor, d_vec_k,
+                             d_vec_v, one, None, num_queries, num_heads, t1 - t0, n_rep, scale, alpha_k, alpha_v, rope_base,
+                             start_pos + j * pos_stride, 1)
+            if rc:
+                raise OracleLaunchError("attn_strided", rc)
+            parts[:, j] = one
+        merged = attn_reduce(parts, num_heads, n_chunks)
+        dst = out_attn if isinstance(out_attn, np.ndarray) else out_attn.numpy()
+        dst.reshape(num_heads, PART)[:] = merged
 
     def window_attn(self, q, ring_k, ring_v, out_attn, win_start, win_len, ring_cap, H_q, H_kv, d, scale):
         rc = window_attn(q, ring_k, ring_v, out_attn, win_start, win_len, ring_cap, H_q, H_kv, d, scale)

@@ -11,7 +11,8 @@ import torch.multiprocessing as mp
 
 import cases
 from cases import D, H_KV, H_Q, SCALE
-from bonsai_mojo_1bit_optimization_t4_cuda_b200.context_parallel import ContextParallelDecode, partition_context
+from bonsai_mojo_1bit_optimization_t4_cuda_b200.context_parallel import (ContextParallelDecode, cyclic_local_tokens, partition_context,
+                                                                         partition_context_cyclic)
 
 
 def test_partition_context():
@@ -25,6 +26,19 @@ def test_partition_context():
     assert all((lo % 128) == 0 for lo, _ in p)
 
 
+def test_partition_context_cyclic():
+    p = partition_context_cyclic(131072, 8)
+    assert [len(x) for x in p] == [128] * 8 and p[3][:3] == [3, 11, 19]
+    # a context that grows chunk by chunk stays balanced to within one chunk
+    for c_len in (128, 1000, 1152, 4096 + 128):
+        for world in (2, 3, 8):
+            parts = partition_context_cyclic(c_len, world)
+            assert sorted(c for x in parts for c in x) == list(range((c_len + 127) // 128))
+            n = [len(x) for x in parts]
+            assert max(n) - min(n) <= 1
+            assert sum(cyclic_local_tokens(c_len, world, r) for r in range(world)) == c_len
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -33,7 +47,7 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, c_len, win_len, q):
+def _worker(rank, world, port, c_len, win_len, q, partition="contiguous"):
     import sys
     from pathlib import Path
 
@@ -47,9 +61,15 @@ def _worker(rank, world, port, c_len, win_len, q):
     try:
         case = cases.make_case(4711, c_len + win_len, "calib")
         kv_full = cases.compress_with(O.compress, case, c_len)
-        lo, hi = partition_context(c_len, world)[rank]
-        rows = slice(lo * H_KV, hi * H_KV)
-        kv = {k: torch.from_numpy(np.ascontiguousarray(v[rows])) for k, v in kv_full.items() if k != "near_ties"}
+        if partition == "cyclic":  # this rank's chunks back to back
+            mine = partition_context_cyclic(c_len, world)[rank]
+            idx = np.concatenate([np.arange(c * 128 * H_KV, min(c_len, (c + 1) * 128) * H_KV) for c in mine]) if mine else np.zeros(0, np.int64)
+            lo, hi = 0, len(idx) // H_KV
+            kv = {k: torch.from_numpy(np.ascontiguousarray(v[idx])) for k, v in kv_full.items() if k != "near_ties"}
+        else:
+            lo, hi = partition_context(c_len, world)[rank]
+            rows = slice(lo * H_KV, hi * H_KV)
+            kv = {k: torch.from_numpy(np.ascontiguousarray(v[rows])) for k, v in kv_full.items() if k != "near_ties"}
         tb = {k: torch.from_numpy(v) for k, v in cases.tables_dict(case["f16"]).items()}
         ring_k = np.zeros((256, H_KV, D), np.float16)
         ring_v = np.zeros((256, H_KV, D), np.float16)
@@ -60,7 +80,7 @@ def _worker(rank, world, port, c_len, win_len, q):
         owner = world - 1
         cp = ContextParallelDecode(O.OracleOps(), dist.group.WORLD, kv, tb, lo, hi, case["tables"].alpha_k,
                                    case["tables"].alpha_v, torch.from_numpy(ring_k), torch.from_numpy(ring_v),
-                                   owner=owner, splits=4, device="cpu")
+                                   owner=owner, splits=4, device="cpu", partition=partition)
         qg = torch.from_numpy(case["q_gate"].copy()).reshape(-1)
         if rank != owner:
             qg.zero_()  # only the owner has this step's query: the broadcast must deliver it
@@ -89,12 +109,13 @@ def _worker(rank, world, port, c_len, win_len, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,c_len,win_len", [(2, 384, 128), (2, 128, 77), (3, 1000, 1)])
-def test_context_parallel_matches_single_rank(world, c_len, win_len):
+@pytest.mark.parametrize("world,c_len,win_len,partition", [(2, 384, 128, "contiguous"), (2, 128, 77, "contiguous"),
+                                                            (3, 1000, 1, "contiguous"), (2, 640, 128, "cyclic"), (3, 1000, 5, "cyclic")])
+def test_context_parallel_matches_single_rank(world, c_len, win_len, partition):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, c_len, win_len, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, c_len, win_len, q, partition)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:

@@ -281,3 +281,71 @@ def test_decode_step_vs_reference_golden(cuda_ops, variant):
     ok, mx, exc = cases.attention_close(out.cpu().numpy().reshape(H_Q, D).astype(np.float32),
                                         g["out"].astype(np.float32))
     assert ok, f"final output vs reference kernel: max abs {mx:.3e} excess {exc:.3e}"
+
+
+# ------------------------------------------------------------------------------ calibration: K-static
+def test_cal_kstatic_vs_oracle_and_reference_kernel(cuda_ops, oracle):
+    """launch_khq_cal_kstatic_fp32 against the oracle (a few ulp: the compiler chooses which product
+    of the two-term sum it fuses) and, where oracle/_ref was built, bit for bit against op 2 of the
+    reference's launch_cal_op."""
+    import ctypes
+
+    torch = _torch()
+    rng = np.random.default_rng(33)
+    k, _ = cases.synth.make_kv(rng, 200)
+    rot = cases.synth.project(k.reshape(-1, D), cases.synth.xorshift_signs(7, "k"), cases.synth.random_rotors(rng))
+    rows = rot.shape[0]
+    d_rot = dev(rot)
+    cents = torch.zeros(4 * D, dtype=torch.float32, device="cuda")
+    ts = torch.zeros(1, dtype=torch.float32, device="cuda")
+    sigma = torch.zeros(D, dtype=torch.float32, device="cuda")
+    cuda_ops.cal_kstatic(d_rot, rows, cents, ts, sigma)
+    torch.cuda.synchronize()
+    o_cents, o_ts, o_sigma = oracle.cal_kstatic(rot)
+    assert np.array_equal(sigma.cpu().numpy(), o_sigma)
+    assert abs(float(ts[0]) - o_ts) <= 4e-7 * o_ts
+    assert np.allclose(cents.cpu().numpy().reshape(4, D), o_cents, rtol=1e-6, atol=0)
+    if REF_SO.exists():
+        so = ctypes.CDLL(str(REF_SO))
+        so.launch_cal_op.restype = ctypes.c_int
+        so.launch_cal_op.argtypes = [ctypes.c_int] + [ctypes.c_void_p] * 7 + [ctypes.c_float] * 2 + [ctypes.c_int] * 4 + [ctypes.c_void_p]
+        r_cents = torch.zeros(4 * D, dtype=torch.float32, device="cuda")
+        r_ts = torch.zeros(1, dtype=torch.float32, device="cuda")
+        rc = so.launch_cal_op(2, d_rot.data_ptr(), None, None, None, None, r_cents.data_ptr(), r_ts.data_ptr(), 0.0, 0.0, rows, 0, 0, 0, None)
+        torch.cuda.synchronize()
+        assert rc == 0
+        assert torch.equal(r_ts.view(torch.int32), ts.view(torch.int32))
+        assert torch.equal(r_cents.view(torch.int32), cents.view(torch.int32))
+
+
+def test_attn_strided_positions_vs_oracle(cuda_ops, oracle):
+    """launch_khq_attn_strided_fp16: a slice that holds chunks 1, 4, 7, ... of a longer context (rank 1 of
+    3 under the chunk-cyclic partition, the last chunk partial) against the oracle run chunk by chunk
+    at the chunks' absolute positions; both kernel generations (few and many tokens per CTA)."""
+    torch = _torch()
+    for c_len, splits in ((1000, 4), (128 * 40 + 64, 2)):
+        world, rank = 3, 1
+        case = cases.make_case(5100 + c_len, c_len + 1, "calib")
+        kv_full = cases.compress_with(oracle.compress, case, c_len)
+        chunks = list(range(rank, (c_len + 127) // 128, world))
+        idx = np.concatenate([np.arange(c * 128 * H_KV, min(c_len, (c + 1) * 128) * H_KV) for c in chunks])
+        kv = {k: np.ascontiguousarray(v[idx]) for k, v in kv_full.items() if k != "near_ties"}
+        n = len(idx) // H_KV
+        f, tb = case["f16"], case["tables"]
+        want = np.zeros((H_Q, 258), np.float32)
+        oracle.OracleOps().attn_strided(case["q_gate"], kv["k_payload"], kv["v_payload"], kv["v_shared_meta"], kv["k_mask"],
+                                        kv["k_norms"], kv["k_r_norms"], kv["v_norms"], kv["v_r_norms"], f["cents_k"], f["cents_v"],
+                                        f["vq"], f["rotor_k"], f["rotor_v"], f["d_k"], f["d_v"], want, None, H_Q, H_Q, 1, n, 6,
+                                        SCALE, tb.alpha_k, tb.alpha_v, 1e7, rank * 128, 1, 128, world * 128)
+        arr = {k: dev(v) for k, v in kv.items()}
+        tab = {k: dev(v) for k, v in f.items()}
+        oa = torch.full((H_Q * 258,), float("nan"), dtype=torch.float32, device="cuda")
+        op = torch.full((H_Q * splits * 258,), float("nan"), dtype=torch.float32, device="cuda")
+        cuda_ops.attn_strided(dev(case["q_gate"]), arr["k_payload"], arr["v_payload"], arr["v_shared_meta"], arr["k_mask"],
+                              arr["k_norms"], arr["k_r_norms"], arr["v_norms"], arr["v_r_norms"], tab["cents_k"], tab["cents_v"],
+                              tab["vq"], tab["rotor_k"], tab["rotor_v"], tab["d_k"], tab["d_v"], oa, op, H_Q, H_Q, 1, n, 6, SCALE,
+                              tb.alpha_k, tb.alpha_v, 1e7, rank * 128, splits, 128, world * 128)
+        torch.cuda.synchronize()
+        check_partial(oa.cpu().numpy().reshape(H_Q, 258), want, f"strided c_len={c_len}")
+    assert cuda_ops.lib.launch_khq_attn_strided_fp16(*([0] * 18), 24, 24, 1, 64, 6, 0.0625, 1.0, 1.0, 1e7, 0, 1, 127, 256, 0) == -103
+    assert cuda_ops.lib.launch_khq_attn_strided_fp16(*([0] * 18), 24, 24, 1, 64, 6, 0.0625, 1.0, 1.0, 1e7, 0, 1, 128, 64, 0) == -103
