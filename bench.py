@@ -72,7 +72,7 @@ def parse():
                          "one NCCL all-gather (collective)")
     ap.add_argument("--partition", default="contiguous", choices=["contiguous", "cyclic"],
                     help="--workload long / long_context: contiguous context ranges, or 128-token chunks dealt cyclically")
-    ap.add_argument("--kernel", default="auto", choices=["auto", "cuda-core", "mma", "tc5"],
+    ap.add_argument("--kernel", default="auto", choices=["auto", "cuda-core", "mma", "tc5", "tc5w"],
                     help="generation of the batched decode kernel")
     return ap.parse_args()
 
@@ -937,7 +937,7 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    gen = {"auto": -1, "cuda-core": 1, "mma": 2, "tc5": 3}[args.kernel]
+    gen = {"auto": -1, "cuda-core": 1, "mma": 2, "tc5": 3, "tc5w": 4}[args.kernel]
     tables = make_tables(args.layers)
     stream = torch.cuda.current_stream()
 
@@ -1069,7 +1069,7 @@ def main():
         avg_launch_ms = float(np.mean(launch_ms))
         achieved = bytes_layer / (avg_launch_ms / 1e3) / 1e9
         kname = {"cuda-core": "khq_decode_batched_kernel", "mma": "khq_decode_batched_mma_kernel",
-                 "tc5": "khq_decode_batched_tc5_kernel", "auto": "khq_decode_batched_mma_kernel"}[args.kernel]
+                 "tc5": "khq_decode_batched_tc5_kernel", "tc5w": "khq_decode_batched_tc5w_kernel", "auto": "khq_decode_batched_mma_kernel"}[args.kernel]
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",

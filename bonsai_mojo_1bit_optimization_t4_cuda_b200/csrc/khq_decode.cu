@@ -583,6 +583,7 @@ khq_decode_batched_kernel(const KhqSeqDesc* __restrict__ descs, const KhqTablesD
 }  // namespace khq
 #include "khq_decode_mma.cuh"
 #include "khq_decode_tc5.cuh"
+#include "khq_decode_tc5w.cuh"
 namespace khq {
 
 // Per problem and query head: LSE merge of the problem's partial slots, /(den+1e-8), sigmoid
@@ -845,6 +846,7 @@ static cudaError_t ensure_smem_attrs() {
     if ((e = cudaFuncSetAttribute(khq_decode_batched_mma_kernel, attr, M2_SM_TOTAL)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(khq_attn_compressed_mma_kernel, attr, M2_SM_TOTAL)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(m3::khq_decode_batched_tc5_kernel, attr, m3::SM_TOTAL)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(m3::khq_decode_batched_tc5w_kernel, attr, m3::SM_TOTAL)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(khq_window_attn_kernel, attr, 2 * HKV * MERGE_FLOATS * 4)) != cudaSuccess)
         return e;
     if ((e = cudaFuncSetAttribute(khq_window_step_kernel, attr, 2 * HKV * MERGE_FLOATS * 4)) != cudaSuccess) return e;
@@ -1195,7 +1197,11 @@ extern "C" int launch_khq_decode_batched_fp16(const void* descs, const void* tab
     float* partials = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + 256);
     const int grid = n_items < sm_count() ? n_items : sm_count();
     const bool vqs = codebook_in_smem != 0;
-    if (codebook_in_smem == 3)
+    if (codebook_in_smem == 4)
+        m3::khq_decode_batched_tc5w_kernel<<<grid, m3::W_THREADS, m3::SM_TOTAL, stream>>>(
+            static_cast<const KhqSeqDesc*>(descs), static_cast<const KhqTablesDesc*>(tables),
+            static_cast<const KhqWorkItem*>(items), n_items, counter, partials, scale, rope_base, ring_cap);
+    else if (codebook_in_smem == 3)
         m3::khq_decode_batched_tc5_kernel<<<grid, m3::THREADS, m3::SM_TOTAL, stream>>>(
             static_cast<const KhqSeqDesc*>(descs), static_cast<const KhqTablesDesc*>(tables),
             static_cast<const KhqWorkItem*>(items), n_items, counter, partials, scale, rope_base, ring_cap);

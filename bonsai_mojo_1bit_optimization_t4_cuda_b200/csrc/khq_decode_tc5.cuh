@@ -209,7 +209,8 @@ __device__ __forceinline__ int kap_of_dim(int d) { return (d & ~15) + khq3::k3_i
 
 // ---- per-layer tables -------------------------------------------------------------------------
 // V codebook, rotary columns of B, beta / alpha tables, dim-3 centroids, RoPE constants.  All
-// THREADS threads; must be followed by a CTA barrier (and a proxy fence before the next MMA).
+// NT threads of the CTA; must be followed by a CTA barrier (and a proxy fence before the next MMA).
+template <int NT = THREADS>
 __device__ __forceinline__ void setup_layer(unsigned char* smem, const CompressedKV& P, int tid) {
     Soft* soft = reinterpret_cast<Soft*>(smem + SM_SOFT);
     unsigned short* vqa = reinterpret_cast<unsigned short*>(smem + SM_VQA);
@@ -218,7 +219,7 @@ __device__ __forceinline__ void setup_layer(unsigned char* smem, const Compresse
     // table (entry e starts at half 3e), and go to one word of the (d0, d1) table and one half of the d2 table
     {
         const unsigned int* src = reinterpret_cast<const unsigned int*>(P.vq);
-        for (int e = tid; e < NP * 256; e += THREADS) {
+        for (int e = tid; e < NP * 256; e += NT) {
             const int w = (3 * e) >> 1;
             const unsigned int a = __ldg(src + w), b = __ldg(src + w + 1);
             unsigned int d01, d2;
@@ -235,7 +236,7 @@ __device__ __forceinline__ void setup_layer(unsigned char* smem, const Compresse
         }
     }
     // rotary columns: B[kap(i)][32 + m] = ceff_i * dinv_m * sum_c' R[p][c'][k] * (-1)^popc(m & ((4p + c') & 63))
-    for (int e = tid; e < 64 * D; e += THREADS) {
+    for (int e = tid; e < 64 * D; e += NT) {
         const int m = e & 63, i = e >> 6;
         const int p = i >> 2, k = i & 3;
         float acc = 0.0f;
@@ -729,8 +730,9 @@ _Pragma(M3_STR(unroll M3_WORD_UNROLL))
                 if (g >= 1) wait_bar(&bars[B_PVDONE], (g - 1) & 1u, abortf);
 #pragma unroll
                 for (int j = 0; j < 3; ++j) {
-                    *reinterpret_cast<__half*>(smem + SM_P + p_off(h0 + j, r)) = __float2half(pw[j] * s1);
-                    *reinterpret_cast<__half*>(smem + SM_P + p_off(24 + h0 + j, r)) = __float2half(pw[j] * s2);
+                    // rows outside the item write an exact zero: their row scalars are whatever the staging area held
+                    *reinterpret_cast<__half*>(smem + SM_P + p_off(h0 + j, r)) = __float2half(valid ? pw[j] * s1 : 0.0f);
+                    *reinterpret_cast<__half*>(smem + SM_P + p_off(24 + h0 + j, r)) = __float2half(valid ? pw[j] * s2 : 0.0f);
                 }
                 fence_proxy_async();
                 __syncwarp();

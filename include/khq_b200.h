@@ -167,7 +167,8 @@ size_t khq_b200_decode_workspace_bytes(int n_slots_total);
  * codebook_in_smem selects the kernel generation: 1 / 0 = CUDA-core kernel with each layer's V
  * codebook staged in shared memory / gathered from global memory, 2 = warp-level tensor-core kernel
  * (mma.sync), 3 = tcgen05 kernel (tensor-memory accumulators, code words decoded one payload row
- * per thread), -1 let the library choose.  Allocates nothing; the only non-kernel call is a 256-byte
+ * per thread), 4 = the same formulation run by 32 light warps (two mask words or two patches per
+ * thread, CTA-wide step barriers), -1 let the library choose.  Allocates nothing; the only non-kernel call is a 256-byte
  * cudaMemsetAsync on `stream`.  Returns -100 (empty/NULL arguments), -104 (alignment), -105
  * (workspace too small). */
 int launch_khq_decode_batched_fp16(const void* descs, const void* tables, const void* items, int n_desc,

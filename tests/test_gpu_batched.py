@@ -30,7 +30,7 @@ def oracle_step(oracle, case, kv, c_len, win_start, win_len, start_pos=0):
     return out, ring_k, ring_v
 
 
-@pytest.mark.parametrize("codebook_in_smem", [1, 0, 2, 3])  # 2 = mma.sync generation, 3 = tcgen05 generation
+@pytest.mark.parametrize("codebook_in_smem", [1, 0, 2, 3, 4])  # 2 = mma.sync generation, 3 and 4 = tcgen05 generations
 @pytest.mark.parametrize("tokens_per_item", [0, 48, 1000])
 def test_batched_decode_vs_oracle(cuda_ops, oracle, codebook_in_smem, tokens_per_item):
     import torch

@@ -12,7 +12,7 @@ from cases import D, H_KV, H_Q, SCALE
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("generation", [2, 3])
+@pytest.mark.parametrize("generation", [2, 3, 4])
 def test_engine_decodes_like_independent_runtimes(cuda_ops, generation):
     import torch
 

@@ -125,7 +125,7 @@ def test_long_context_vs_oracle_and_reference_kernel(cuda_ops, oracle):
     oracle.merge_gate(ref, aw, q_gate, want, H_Q, D, 1)
     tables = [dict(cents_k=tab["cents_k"], cents_v=tab["cents_v"], vq=tab["vq"], k_rotor=tab["rotor_k"], v_rotor=tab["rotor_v"],
                    d_k=tab["d_k"], d_v=tab["d_v"], alpha_k=tb.alpha_k, alpha_v=tb.alpha_v)]
-    for gen in (1, 2, 3):
+    for gen in (1, 2, 3, 4):
         prob = dict(kv)
         prob.update(q_gate=qg, ring_k=torch.from_numpy(ring_k).cuda().reshape(-1), ring_v=torch.from_numpy(ring_v).cuda().reshape(-1),
                     out=torch.zeros(H_Q * D, dtype=torch.float16, device="cuda"), table_id=0, c_len=c_len, start_pos=0,
@@ -178,7 +178,7 @@ def test_batched_long_and_short_sequence_vs_oracle(cuda_ops, oracle):
         want = np.zeros((H_Q, D), np.float16)
         oracle.merge_gate(ref, aw, q_gate, want, H_Q, D, 1)
         wants.append(want.astype(np.float32))
-    for gen in (1, 2, 3):
+    for gen in (1, 2, 3, 4):
         problems, tables = [], []
         for i, ((c, w, _), (tb, tab, kv, host, q_gate, ring_k, ring_v)) in enumerate(zip(specs, states)):
             tables.append(dict(cents_k=tab["cents_k"], cents_v=tab["cents_v"], vq=tab["vq"], k_rotor=tab["rotor_k"],
