@@ -1137,47 +1137,156 @@ static int plan_sm_count() {
     return v;
 }
 
-// Host planner: cuts every problem's compressed region into items of about tokens_per_item
-// tokens (a multiple of the staging tile) plus one item for its raw window, in problem order.
+// ---- host planner -----------------------------------------------------------------------------
+// The CTAs of the persistent kernels pull items off one counter in array order, so a plan is judged
+// by the makespan of list scheduling on `sms` workers.  Costs are in compressed-token units: one
+// per compressed token, PLAN_WINDOW_COST per raw-window token (4 KB of fp16 against 880 B),
+// PLAN_ITEM_COST per item (query set-up, partial record).
+#include <algorithm>
+#include <functional>
+#include <queue>
+#include <vector>
+
+namespace {
+constexpr int PLAN_WINDOW_COST = 3, PLAN_ITEM_COST = 16;
+
+struct PlanRule {
+    int kind;   // 0: guided self-scheduling (cap, floor); 1: one piece count per problem (pieces)
+    int cap, floor_;
+    const std::vector<int>* pieces;
+};
+
+// Walks the items of a plan in launch order: fn(problem, kind, lo, hi).
+template <class F>
+void plan_walk(const PlanRule& rule, const int* c_len, const int* win_len, int n_desc, int sms, F fn) {
+    long long remaining = 0;
+    for (int i = 0; i < n_desc; ++i) remaining += c_len[i] > 0 ? c_len[i] : 0;
+    // every raw window first (they need no tables): the last items of a launch are then small pieces
+    for (int i = 0; i < n_desc; ++i)
+        if (win_len[i] > 0) fn(i, 1, 0, win_len[i]);
+    for (int i = 0; i < n_desc; ++i) {
+        const int cl = c_len[i] > 0 ? c_len[i] : 0;
+        if (rule.kind == 0) {
+            // tokens_per_item while more than 2 x SMs such items remain in the launch, then
+            // remaining / (2 x SMs), down to the floor: the last items handed out are small
+            for (int lo = 0; lo < cl;) {
+                long long size = remaining / (2LL * sms);
+                if (size > rule.cap) size = rule.cap;
+                size = (size / rule.floor_) * rule.floor_;
+                if (size < rule.floor_) size = rule.floor_;
+                const int left = cl - lo;
+                if (left < size + rule.floor_ / 2) size = left;  // a short remainder joins the last piece
+                fn(i, 0, lo, lo + (int)size);
+                lo += (int)size;
+                remaining -= size;
+            }
+        } else if (cl > 0) {
+            const int pieces = (*rule.pieces)[i];
+            const int per = (((cl + pieces - 1) / pieces) + 1) & ~1;  // equal pieces, each starting on an even token
+            for (int lo = 0; lo < cl; lo += per) fn(i, 0, lo, lo + per < cl ? lo + per : cl);
+        }
+    }
+}
+
+long long plan_makespan(const PlanRule& rule, const int* c_len, const int* win_len, int n_desc, int sms) {
+    std::priority_queue<long long, std::vector<long long>, std::greater<long long>> free_at;
+    for (int w = 0; w < sms; ++w) free_at.push(0);
+    long long end = 0;
+    plan_walk(rule, c_len, win_len, n_desc, sms, [&](int, int kind, int lo, int hi) {
+        const long long t = free_at.top() + (long long)(hi - lo) * (kind ? PLAN_WINDOW_COST : 1) + PLAN_ITEM_COST;
+        free_at.pop();
+        free_at.push(t);
+        if (t > end) end = t;
+    });
+    return end;
+}
+
+// `total` pieces over the problems such that the largest piece is as small as possible (every problem
+// with tokens gets one; the next piece always goes to the problem whose pieces are the largest now).
+bool plan_even_pieces(const int* c_len, int n_desc, int total, int max_piece, std::vector<int>& pieces) {
+    pieces.assign(n_desc, 0);
+    std::priority_queue<std::pair<double, int>> largest;
+    int used = 0;
+    for (int i = 0; i < n_desc; ++i)
+        if (c_len[i] > 0) {
+            pieces[i] = 1;
+            ++used;
+            largest.push({(double)c_len[i], i});
+        }
+    if (used == 0 || used > total) return false;
+    for (; used < total; ++used) {
+        const int i = largest.top().second;
+        if (c_len[i] / (pieces[i] + 1) < 24) break;  // nothing left worth cutting
+        largest.pop();
+        ++pieces[i];
+        largest.push({(double)c_len[i] / pieces[i], i});
+    }
+    return largest.top().first <= (double)max_piece;
+}
+}  // namespace
+
+// Cuts every problem into one item for its raw window and items of its compressed region.  Candidates: guided self-scheduling with a 96- or a 48-token floor, and one, two or three
+// waves of equal pieces (a launch small enough that every CTA gets one to three pieces is balanced
+// best by exactly that); the one with the shortest simulated makespan is written out.
 extern "C" int khq_b200_plan_decode(const int* c_len, const int* win_len, int n_desc, int tokens_per_item,
                                     void* items_out, int max_items, int* first_slot, int* n_slots) {
     if (n_desc < 0 || !c_len || !win_len) return -100;
-    if (tokens_per_item <= 0) {
-        long long total = 0;
-        for (int i = 0; i < n_desc; ++i) total += c_len[i] > 0 ? c_len[i] : 0;
-        long long t = total / (4LL * plan_sm_count());
+    const int sms = plan_sm_count();
+    long long total = 0;
+    for (int i = 0; i < n_desc; ++i) total += c_len[i] > 0 ? c_len[i] : 0;
+    const bool auto_size = tokens_per_item <= 0;
+    if (auto_size) {
+        long long t = total / (2LL * sms);  // the guided rule's own first size
         if (t < 48) t = 48;
         if (t > 2048) t = 2048;
         tokens_per_item = (int)t;
     }
     tokens_per_item = ((tokens_per_item + 95) / 96) * 96;  // a multiple of every generation's staging tile (24, 32 tokens)
-    KhqWorkItem* items = static_cast<KhqWorkItem*>(items_out);
-    int n = 0;
-    for (int i = 0; i < n_desc; ++i) {
-        const int cl = c_len[i] > 0 ? c_len[i] : 0, wl = win_len[i] > 0 ? win_len[i] : 0;
-        const int fs = n;
-        if (cl > 0) {
-            const int pieces = (cl + tokens_per_item - 1) / tokens_per_item;
-            // equal pieces, each a multiple of 2 tokens so that every piece starts 16-byte aligned
-            int per = (((cl + pieces - 1) / pieces) + 1) & ~1;
-            for (int lo = 0; lo < cl; lo += per) {
-                if (items && n < max_items) {
-                    KhqWorkItem w = {i, 0, lo, (lo + per < cl) ? lo + per : cl, n, 0, 0, 0};
-                    items[n] = w;
-                }
-                ++n;
+
+    std::vector<int> pieces[3];
+    PlanRule best = {0, tokens_per_item, 96, nullptr};
+    // A launch of many waves is planned by the guided rule as it stands (its tail is a fraction of a percent);
+    // smaller ones compare the candidates.
+    if (total <= 8LL * sms * tokens_per_item) {
+        long long best_t = plan_makespan(best, c_len, win_len, n_desc, sms);
+        auto consider = [&](const PlanRule& r) {
+            const long long t = plan_makespan(r, c_len, win_len, n_desc, sms);
+            if (t < best_t) {
+                best_t = t;
+                best = r;
             }
-        }
-        if (wl > 0) {
-            if (items && n < max_items) {
-                KhqWorkItem w = {i, 1, 0, wl, n, 0, 0, 0};
-                items[n] = w;
-            }
-            ++n;
-        }
-        if (first_slot) first_slot[i] = fs;
-        if (n_slots) n_slots[i] = n - fs;
+        };
+        consider(PlanRule{0, tokens_per_item, 48, nullptr});
+        // an explicit tokens_per_item stays an upper bound on every piece
+        const int max_piece = auto_size ? 2112 : tokens_per_item;
+        for (int k = 1; k <= 3; ++k)
+            if (plan_even_pieces(c_len, n_desc, k * sms, max_piece, pieces[k - 1])) consider(PlanRule{1, 0, 0, &pieces[k - 1]});
     }
+
+    // slots are numbered problem by problem (a problem's partial records are contiguous, its window first);
+    // the array order is the launch order: all windows, then the pieces in problem order
+    std::vector<int> count(n_desc, 0), next(n_desc, 0);
+    int n = 0;
+    plan_walk(best, c_len, win_len, n_desc, sms, [&](int i, int, int, int) {
+        ++count[i];
+        ++n;
+    });
+    for (int i = 0, at = 0; i < n_desc; ++i) {
+        next[i] = at;
+        if (first_slot) first_slot[i] = at;
+        if (n_slots) n_slots[i] = count[i];
+        at += count[i];
+    }
+    KhqWorkItem* items = static_cast<KhqWorkItem*>(items_out);
+    int pos = 0;
+    plan_walk(best, c_len, win_len, n_desc, sms, [&](int i, int kind, int lo, int hi) {
+        if (items && pos < max_items) {
+            KhqWorkItem w = {i, kind, lo, hi, next[i], 0, 0, 0};
+            items[pos] = w;
+        }
+        ++next[i];
+        ++pos;
+    });
     return n;  // > max_items means the items buffer was too small
 }
 

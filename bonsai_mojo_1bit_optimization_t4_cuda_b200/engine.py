@@ -127,9 +127,13 @@ class BatchEngine:
         # ---- planning ----------------------------------------------------------------------
         if tokens_per_item <= 0:
             sms = torch.cuda.get_device_properties(dev).multi_processor_count if dev.type == "cuda" else 148
-            tokens_per_item = int(min(max(int(self.cap.sum()) // (4 * sms), 96), 2048))
+            tokens_per_item = int(min(max(int(self.cap.sum()) // (2 * sms), 96), 2048))
         self.tokens_per_item = (tokens_per_item + 95) // 96 * 96
-        self.max_items = int(sum((int(c) + self.tokens_per_item - 1) // self.tokens_per_item + 2 for c in self.cap))
+        # the planner shrinks the last items of a launch (down to 48 tokens), or cuts one to three pieces per
+        # SM: room for either on top of the full-size items
+        sms_plan = torch.cuda.get_device_properties(dev).multi_processor_count if dev.type == "cuda" else 148
+        tail_items = int(4 * sms_plan * (1.0 + np.log(self.tokens_per_item / 48.0))) + 16
+        self.max_items = int(sum((int(c) + self.tokens_per_item - 1) // self.tokens_per_item + 2 for c in self.cap)) + tail_items
         self.ws_bytes = int(self.lib.khq_b200_decode_workspace_bytes(self.max_items))
         self.workspace = z(self.ws_bytes, torch.uint8)
         self.d_items = z(self.max_items * WORK_ITEM.itemsize, torch.uint8)

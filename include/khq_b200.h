@@ -149,11 +149,16 @@ typedef struct khq_work_item {
     int32_t desc, kind, lo, hi, slot, r0, r1, r2; /* kind 0: compressed tokens [lo,hi); 1: window */
 } khq_work_item;
 
-/* Host-side planner (pure CPU, no CUDA call).  c_len[i]/win_len[i] describe problem i; problems
- * should be ordered by table_id so that consecutive items share tables.  tokens_per_item <= 0
- * picks a size that fills the GPU.  Writes up to max_items items, and per problem the first
- * partial slot and the slot count (copy them into the descriptors).  Returns the item count
- * (== total slot count); a value > max_items means items_out was too small.  -100 on bad args. */
+/* Host-side planner (pure CPU; its only CUDA call asks for the current device's SM count and falls
+ * back to 148).  c_len[i]/win_len[i] describe problem i; problems should be ordered by table_id so
+ * that consecutive items share tables.  The array order is the launch order (the CTAs pull items off
+ * one counter): every raw window first, then the compressed regions in problem order, each cut into
+ * pieces that start on even tokens.  Piece sizes: tokens_per_item tokens (rounded up to a multiple
+ * of 96; <= 0 picks a size that fills the GPU) while more than 2 x SMs such pieces remain in the
+ * launch, then remaining / (2 x SMs) down to 96 or 48 -- or, when that simulates shorter, one to three
+ * equal pieces per SM.  Slots are numbered problem by problem (window first) whatever the array order.  Writes up to max_items items, and per problem the first partial slot
+ * and the slot count (copy them into the descriptors).  Returns the item count (== total slot
+ * count); a value > max_items means items_out was too small.  -100 on bad args. */
 int khq_b200_plan_decode(const int* c_len, const int* win_len, int n_desc, int tokens_per_item,
                          void* items_out, int max_items, int* first_slot, int* n_slots);
 
