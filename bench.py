@@ -72,6 +72,9 @@ def parse():
                          "one NCCL all-gather (collective)")
     ap.add_argument("--partition", default="contiguous", choices=["contiguous", "cyclic"],
                     help="--workload long / long_context: contiguous context ranges, or 128-token chunks dealt cyclically")
+    ap.add_argument("--cp-engine", default="persistent", choices=["persistent", "splits"],
+                    help="--workload long / long_context: each rank's slice and the raw window as one launch of the persistent "
+                         "batched kernel, or the drop-in split launches (--splits) plus the window launch")
     ap.add_argument("--kernel", default="auto", choices=["auto", "cuda-core", "mma", "tc5", "tc5w"],
                     help="generation of the batched decode kernel")
     return ap.parse_args()
@@ -321,18 +324,30 @@ def long_measure(args, rank, world, dev, steps, warm):
     owner = world - 1
     exchange = args.exchange if world > 1 else "collective"
     cp = ContextParallelDecode(ops, dist.group.WORLD, kv, tab, lo, hi, tb.alpha_k, tb.alpha_v, ring_k, ring_v, owner=owner,
-                               splits=args.splits, device=dev, exchange=exchange, partition=args.partition)
-    checked = None
+                               splits=args.splits, device=dev, exchange=exchange, partition=args.partition, engine=args.cp_engine)
+    checked = []
+    qg0 = torch.randn(24 * 512, generator=g, device=dev).half()
     if world > 1 and exchange == "peer":
         # the two exchanges must give the same answer
         ref = ContextParallelDecode(ops, dist.group.WORLD, kv, tab, lo, hi, tb.alpha_k, tb.alpha_v, ring_k, ring_v, owner=owner,
-                                    splits=args.splits, device=dev, exchange="collective", partition=args.partition)
-        qg0 = torch.randn(24 * 512, generator=g, device=dev).half()
+                                    splits=args.splits, device=dev, exchange="collective", partition=args.partition,
+                                    engine=args.cp_engine)
         a = cp.step(qg0.clone(), args.long_ctx % 256, 256).clone()
         b = ref.step(qg0.clone(), args.long_ctx % 256, 256).clone()
         torch.cuda.synchronize()
         assert torch.equal(a.view(torch.int16), b.view(torch.int16)), "peer exchange differs from the all-gather"
-        checked = "peer-store exchange bit-identical to the NCCL all-gather path on one step"
+        checked.append("peer-store exchange bit-identical to the NCCL all-gather path on one step")
+    if args.cp_engine == "persistent":
+        # ... and so must the two ways of computing a rank's share (different cuts, different merge order: to rounding)
+        ref = ContextParallelDecode(ops, dist.group.WORLD, kv, tab, lo, hi, tb.alpha_k, tb.alpha_v, ring_k, ring_v, owner=owner,
+                                    splits=args.splits, device=dev, exchange="collective", partition=args.partition, engine="splits")
+        a = cp.step(qg0.clone(), args.long_ctx % 256, 256).float().clone()
+        b = ref.step(qg0.clone(), args.long_ctx % 256, 256).float().clone()
+        torch.cuda.synchronize()
+        err = float((a - b).abs().max())
+        assert err < 2e-3 and bool(torch.isfinite(a).all()), f"persistent slice differs from the split launches: {err}"
+        checked.append("persistent-kernel share equal to the drop-in split launches on one step (max |diff| %.1e)" % err)
+    checked = "; ".join(checked) if checked else None
     qg = torch.randn(24 * 512, generator=g, device=dev).half()
     win_start, win_len = args.long_ctx % 256, 256
     for _ in range(warm):
@@ -359,7 +374,9 @@ def long_measure(args, rank, world, dev, steps, warm):
             "partition": ("128-token chunks dealt cyclically (chunk c on rank c mod N)" if args.partition == "cyclic"
                           else "contiguous context ranges cut on 128-token chunks"), "tokens": args.long_ctx, "raw_tokens": win_len,
             "splits": args.splits, "steps": steps, "warmup": warm, "checked": checked, "device_status": status,
-            "gpu_launches_per_step": 5}
+            "engine": ("one launch of the persistent batched kernel per rank (slice + raw window), planner-cut"
+                       if args.cp_engine == "persistent" else "drop-in split launches + window launch"),
+            "gpu_launches_per_step": (3 if args.cp_engine == "persistent" else 5) + (1 if world > 1 and exchange == "peer" else 0)}
 
 
 def run_long(args, rank, world, local_rank):
@@ -380,14 +397,15 @@ def run_long(args, rank, world, local_rank):
             "metric": "KHQ long-context decode attention latency", "value": us, "unit": "us/layer-step", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": us / 1e3, "higher_is_better": False,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "BASELINE configs[2]: one sequence, %d compressed + %d raw tokens, 1 layer, splits %d, "
+            "config": {"workload": "BASELINE configs[2]: one sequence, %d compressed + %d raw tokens, 1 layer, %s, "
                                    "context-partitioned over %d GPU(s), partials: %s"
-                                   % (args.long_ctx, r["raw_tokens"], args.splits, world, r["exchange"]),
+                                   % (args.long_ctx, r["raw_tokens"], r["engine"], world, r["exchange"]),
                        "l2": "payload 115 MB per step, larger than L2 only in aggregate at 1 GPU"},
             "roofline": {"bound": "hbm", "achieved": r["achieved_gbs"], "peak": peak * world, "unit": "GB/s",
                          "frac": r["achieved_gbs"] / (peak * world), "traffic": None,
                          "algorithmic_bytes_per_step": r["algorithmic_bytes_per_step"]},
-            "gpu_launches": 5 * args.steps, "device_status": r["device_status"], "checked": r["checked"]}), flush=True)
+            "gpu_launches": r["gpu_launches_per_step"] * args.steps, "device_status": r["device_status"],
+            "checked": r["checked"]}), flush=True)
     dist.destroy_process_group()
 
 

@@ -17,7 +17,7 @@ SEQ_DESC = np.dtype([
     ("k_mask", "<u8"), ("k_norms", "<u8"), ("k_r_norms", "<u8"), ("v_norms", "<u8"), ("v_r_norms", "<u8"),
     ("ring_k", "<u8"), ("ring_v", "<u8"), ("out", "<u8"),
     ("table_id", "<i4"), ("c_len", "<i4"), ("start_pos", "<i4"), ("win_start", "<i4"), ("win_len", "<i4"),
-    ("first_slot", "<i4"), ("n_slots", "<i4"), ("reserved", "<i4"),
+    ("first_slot", "<i4"), ("n_slots", "<i4"), ("pos_pack", "<i4"),
 ])
 TABLES_DESC = np.dtype([
     ("cents_k", "<u8"), ("cents_v", "<u8"), ("vq", "<u8"), ("k_rotor", "<u8"), ("v_rotor", "<u8"),

@@ -162,6 +162,83 @@ class PeerExchange:
             self.base = 0
 
 
+class PersistentSlice:
+    """One rank's compressed slice (and, on the owner, the raw window) as ONE problem of the
+    library's persistent batched decode kernel, ending in one unnormalised ``(24, 258)`` record
+    (``launch_khq_decode_batched_partial_fp16``).  Against the split launches of the drop-in entry
+    this fills every SM whatever the slice length (the host planner cuts one to three pieces per SM,
+    raw-window pieces included), pays the per-CTA table set-up once and needs no second launch for
+    the window.  CUDA only; the descriptor and the work items are re-sent only when the slice length
+    or the window length changed."""
+
+    def __init__(self, lib, kv: dict, tables: dict, alpha_k: float, alpha_v: float, ring_k, ring_v, start_pos: int,
+                 pos_chunk: int = 0, pos_stride_chunks: int = 0, device="cuda", generation: int = -1):
+        from .batched import SEQ_DESC, TABLES_DESC, WORK_ITEM
+        from .lib import check, current_stream
+
+        self.lib, self._check, self._stream = lib, check, current_stream
+        self.generation = generation
+        dev = torch.device(device)
+        self._keep = (kv, tables, ring_k, ring_v)  # the descriptors hold raw addresses
+        self.q = torch.zeros(H_Q * 2 * D, dtype=torch.float16, device=dev)
+        t = np.zeros(1, TABLES_DESC)
+        for name, key in (("cents_k", "cents_k"), ("cents_v", "cents_v"), ("vq", "vq"), ("k_rotor", "rotor_k"),
+                          ("v_rotor", "rotor_v"), ("d_k", "d_k"), ("d_v", "d_v")):
+            t[0][name] = tables[key].data_ptr()
+        t[0]["alpha_k"], t[0]["alpha_v"] = alpha_k, alpha_v
+        self.d_tables = torch.from_numpy(t.view(np.uint8).copy()).to(dev)
+        self.h_desc = torch.zeros(SEQ_DESC.itemsize, dtype=torch.uint8).pin_memory()
+        d = self.h_desc.numpy().view(SEQ_DESC)
+        for k in ("k_payload", "v_payload", "v_shared_meta", "k_mask", "k_norms", "k_r_norms", "v_norms", "v_r_norms"):
+            d[0][k] = kv[k].data_ptr()
+        d[0]["q_gate"] = self.q.data_ptr()
+        d[0]["ring_k"] = ring_k.data_ptr() if ring_k is not None else 0
+        d[0]["ring_v"] = ring_v.data_ptr() if ring_v is not None else 0
+        d[0]["start_pos"] = start_pos
+        assert 0 <= pos_chunk < 65536 and pos_chunk % 2 == 0 and 0 <= pos_stride_chunks < 65536
+        d[0]["pos_pack"] = (pos_chunk << 16) | pos_stride_chunks if pos_chunk else 0
+        self.d_desc = torch.zeros(SEQ_DESC.itemsize, dtype=torch.uint8, device=dev)
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        self.max_items = 16 * sms
+        self.item_bytes = WORK_ITEM.itemsize
+        self.h_items = torch.zeros(self.max_items * self.item_bytes, dtype=torch.uint8).pin_memory()
+        self.d_items = torch.zeros(self.max_items * self.item_bytes, dtype=torch.uint8, device=dev)
+        self.ws_bytes = int(lib.khq_b200_decode_workspace_bytes(self.max_items))
+        self.workspace = torch.zeros(self.ws_bytes, dtype=torch.uint8, device=dev)
+        self._planned = None
+        self._sent = torch.cuda.Event()
+        self.n_items = 0
+
+    def launch(self, q_gate: torch.Tensor, n_tok: int, win_start: int, win_len: int, out_partial: torch.Tensor,
+               scale: float, rope_base: float) -> None:
+        """out_partial: (24, 258) fp32.  n_tok + win_len must be positive."""
+        from .batched import SEQ_DESC
+
+        self.q.copy_(q_gate.reshape(-1), non_blocking=True)
+        if self._planned != (n_tok, win_start, win_len):
+            self._sent.synchronize()  # the pinned buffers may still be the source of the last copies
+            c = np.array([n_tok], np.int32)
+            w = np.array([win_len], np.int32)
+            first, cnt = np.zeros(1, np.int32), np.zeros(1, np.int32)
+            n = self.lib.khq_b200_plan_decode(c.ctypes.data, w.ctypes.data, 1, 0, self.h_items.data_ptr(), self.max_items,
+                                              first.ctypes.data, cnt.ctypes.data)
+            if n <= 0 or n > self.max_items:
+                raise RuntimeError(f"khq_b200_plan_decode returned {n} items (room for {self.max_items})")
+            self.n_items = int(n)
+            d = self.h_desc.numpy().view(SEQ_DESC)
+            d[0]["c_len"], d[0]["win_start"], d[0]["win_len"] = n_tok, win_start, win_len
+            d[0]["first_slot"], d[0]["n_slots"] = int(first[0]), int(cnt[0])
+            nb = self.n_items * self.item_bytes
+            self.d_items[:nb].copy_(self.h_items[:nb], non_blocking=True)
+            self.d_desc.copy_(self.h_desc, non_blocking=True)
+            self._sent.record(torch.cuda.current_stream())
+            self._planned = (n_tok, win_start, win_len)
+        self._check("launch_khq_decode_batched_partial_fp16", self.lib.launch_khq_decode_batched_partial_fp16(
+            self.d_desc.data_ptr(), self.d_tables.data_ptr(), self.d_items.data_ptr(), 1, self.n_items,
+            self.workspace.data_ptr(), self.ws_bytes, self.n_items, float(scale), float(rope_base), 256,
+            int(self.generation), out_partial.data_ptr(), self._stream()))
+
+
 class ContextParallelDecode:
     """One rank's share of a context-parallel decode step.
 
@@ -172,12 +249,14 @@ class ContextParallelDecode:
 
     def __init__(self, ops, group, kv: dict, tables: dict, lo: int, hi: int, alpha_k: float, alpha_v: float,
                  ring_k=None, ring_v=None, owner: int = 0, splits: int = 32, device="cuda", exchange: str = "collective",
-                 partition: str = "contiguous"):
+                 partition: str = "contiguous", engine: str = "splits"):
         """``exchange``: "collective" = one all-gather of the partials (NCCL / gloo), "peer" = every
         rank stores its partials into the peers' buffers over NVLink and the merge kernel waits for
         the flags (``PeerExchange``; CUDA only).  ``partition``: "contiguous" = ``kv`` holds the rows of
         tokens ``[lo, hi)``; "cyclic" = ``kv`` holds this rank's chunks of the chunk-cyclic partition
-        back to back (``hi - lo`` local tokens; ``lo`` is ignored)."""
+        back to back (``hi - lo`` local tokens; ``lo`` is ignored).  ``engine``: "splits" = the drop-in entries
+        (``launch_khq_attn_fp16`` / ``_strided`` with ``splits`` splits, then the window launch); "persistent" =
+        slice and window as one launch of the persistent batched kernel (``PersistentSlice``; CUDA only)."""
         self.ops, self.group = ops, group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
@@ -202,6 +281,15 @@ class ContextParallelDecode:
         # device status word; it is read back every `status_every` steps and at close().
         self.status_every = 64
         self._steps = 0
+        assert engine in ("splits", "persistent")
+        self.persistent = None
+        if engine == "persistent":
+            mine_ring = self.rank == self.owner
+            cyc = partition == "cyclic"
+            self.persistent = PersistentSlice(ops.lib, kv, tables, alpha_k, alpha_v, ring_k if mine_ring else None,
+                                              ring_v if mine_ring else None,
+                                              start_pos=(self.rank * CHUNK if cyc else lo), pos_chunk=(CHUNK if cyc else 0),
+                                              pos_stride_chunks=(self.world if cyc else 0), device=device)
 
     def check_status(self) -> None:
         """Read and clear the library's device status word (a blocking 4-byte copy) and raise if a
@@ -243,6 +331,14 @@ class ContextParallelDecode:
         elif broadcast_q and self.world > 1:
             dist.broadcast(q_gate, src=dist.get_global_rank(self.group, self.owner), group=self.group)
         n = self.hi - self.lo
+        if self.persistent is not None:
+            wl = win_len if self.rank == self.owner else 0
+            if n + wl > 0:
+                self.persistent.launch(q_gate, n, win_start, wl, self.mine[0], scale, rope_base)
+            else:
+                self.mine[0].copy_(self._neutral)
+            self.mine[1].copy_(self._neutral)
+            return self._exchange_and_merge(q_gate)
         if n > 0 and self.partition == "cyclic":
             ops.attn_strided(q_gate, kv["k_payload"], kv["v_payload"], kv["v_shared_meta"], kv["k_mask"], kv["k_norms"],
                              kv["k_r_norms"], kv["v_norms"], kv["v_r_norms"], tb["cents_k"], tb["cents_v"], tb["vq"],
@@ -261,6 +357,10 @@ class ContextParallelDecode:
                             scale)
         else:
             self.mine[1].copy_(self._neutral)
+        return self._exchange_and_merge(q_gate)
+
+    def _exchange_and_merge(self, q_gate: torch.Tensor) -> torch.Tensor:
+        ops = self.ops
         if self.peer is not None:
             self.peer.publish(self.mine)
             self.peer.merge(q_gate, self.out)

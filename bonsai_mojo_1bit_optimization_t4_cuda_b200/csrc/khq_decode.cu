@@ -318,6 +318,7 @@ __device__ __forceinline__ void compressed_range(unsigned char* smem, const __ha
 
 // Inverse V rotor + FWHT + /16/(d_v+1e-8) of the merged state of head h, stored as one
 // (acc[256], max, sum_exp) record.  Called by one warp per kv-head.
+template <int H0 = 0, int H1 = NREP>  // heads [H0, H1) of the kv-head: two warps may share the six
 __device__ __forceinline__ void v_epilogue_store(const WarpState& st, const CompressedKV& P, int lane,
                                                  float* const (&ob)[NREP]) {
     float dvi[8];
@@ -328,12 +329,21 @@ __device__ __forceinline__ void v_epilogue_store(const WarpState& st, const Comp
         for (int j = 0; j < 8; ++j) dvi[j] = (1.0f / 16.0f) / (__half2float(hd[j]) + 1e-8f);
     }
     float rv[2][16];
+    {
+        const uint4* rp = reinterpret_cast<const uint4*>(P.v_rotor + lane * 32);
+        const uint4 r0 = rp[0], r1 = rp[1], r2 = rp[2], r3 = rp[3];
+        __half hr[32];
+        *reinterpret_cast<uint4*>(&hr[0]) = r0;
+        *reinterpret_cast<uint4*>(&hr[8]) = r1;
+        *reinterpret_cast<uint4*>(&hr[16]) = r2;
+        *reinterpret_cast<uint4*>(&hr[24]) = r3;
 #pragma unroll
-    for (int p = 0; p < 2; ++p)
+        for (int p = 0; p < 2; ++p)
 #pragma unroll
-        for (int i = 0; i < 16; ++i) rv[p][i] = __half2float(P.v_rotor[(lane * 2 + p) * 16 + i]);
+            for (int i = 0; i < 16; ++i) rv[p][i] = __half2float(hr[p * 16 + i]);
+    }
 #pragma unroll
-    for (int h = 0; h < NREP; ++h) {
+    for (int h = H0; h < H1; ++h) {
         float z[8];
 #pragma unroll
         for (int p = 0; p < 2; ++p)
@@ -409,20 +419,71 @@ khq_attn_compressed_kernel(const __half* __restrict__ q, CompressedKV P, float* 
     }
 }
 
-// LSE merge over splits: partial (nq, splits, 258) -> out (nq, 258), unnormalised.
-__global__ void __launch_bounds__(D) khq_attn_reduce_kernel(const float* __restrict__ partial,
-                                                            float* __restrict__ out, int num_splits) {
-    const int qid = blockIdx.x, d = threadIdx.x;
-    const float* base = partial + (size_t)qid * num_splits * PART;
+// LSE merge of `n` partial records `stride` floats apart (acc[D], max, sum) by one block of
+// G * D threads: M = max m_i, num = sum acc_i[dd] e^{m_i - M}, den = sum s_i e^{m_i - M}.
+// Thread (group g, dim dd) adds records g, g + G, ... in order; the groups' sums are then
+// added in group order.  A problem cut over all SMs owns hundreds of records and only H_q blocks merge
+// them, so what counts is how many loads a block keeps in flight: the maximum and the weights are
+// computed a record per thread, and four groups walk the records side by side.  Valid in threads
+// of group 0 on return.
+constexpr int MERGE_GROUPS = 4;  // launches with many records per problem; the others use one group
+template <int G>
+__device__ __forceinline__ float lse_merge_records(const float* __restrict__ base, size_t stride, int n, float& num,
+                                                   float& den) {
+    constexpr int NT = G * D;
+    __shared__ float s_red[NT / 32];
+    __shared__ float s_w[NT];
+    __shared__ float s_num[G > 1 ? G - 1 : 1][D], s_den[G > 1 ? G - 1 : 1];
+    const int tid = threadIdx.x, dd = tid & (D - 1), grp = tid / D;
     float M = NEG_BIG;
-    for (int sp = 0; sp < num_splits; ++sp) M = fmaxf(M, base[(size_t)sp * PART + D]);
-    float num = 0.0f, den = 0.0f;
-    for (int sp = 0; sp < num_splits; ++sp) {
-        const float* p = base + (size_t)sp * PART;
-        const float w = __expf(p[D] - M);
-        num = fmaf(p[d], w, num);
-        den = fmaf(p[D + 1], w, den);
+    for (int s = tid; s < n; s += NT) M = fmaxf(M, base[s * stride + D]);
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, m));
+    if ((tid & 31) == 0) s_red[tid >> 5] = M;
+    __syncthreads();
+    M = s_red[0];
+#pragma unroll
+    for (int w = 1; w < NT / 32; ++w) M = fmaxf(M, s_red[w]);
+    num = 0.0f;
+    den = 0.0f;
+    for (int s0 = 0; s0 < n; s0 += NT) {
+        const int cnt = min(NT, n - s0);
+        __syncthreads();
+        if (tid < cnt) s_w[tid] = __expf(base[(s0 + tid) * stride + D] - M);
+        __syncthreads();
+#pragma unroll 4
+        for (int j = grp; j < cnt; j += G) {
+            const float* p = base + (s0 + j) * stride;
+            const float w = s_w[j];
+            num = fmaf(p[dd], w, num);
+            den = fmaf(p[D + 1], w, den);
+        }
     }
+    if (G > 1) {
+        if (grp > 0) {
+            s_num[grp - 1][dd] = num;
+            if (dd == 0) s_den[grp - 1] = den;
+        }
+        __syncthreads();
+        if (grp == 0) {
+#pragma unroll
+            for (int g = 0; g < G - 1; ++g) {
+                num += s_num[g][dd];
+                den += s_den[g];
+            }
+        }
+    }
+    return M;
+}
+
+// LSE merge over splits: partial (nq, splits, 258) -> out (nq, 258), unnormalised.
+template <int G>
+__global__ void __launch_bounds__(G * D) khq_attn_reduce_kernel(const float* __restrict__ partial, float* __restrict__ out,
+                                                                int num_splits) {
+    const int qid = blockIdx.x, d = threadIdx.x;
+    float num, den;
+    const float M = lse_merge_records<G>(partial + (size_t)qid * num_splits * PART, (size_t)PART, num_splits, num, den);
+    if (d >= D) return;
     float* o = out + (size_t)qid * PART;
     o[d] = num;
     if (d == 0) {
@@ -562,7 +623,8 @@ khq_decode_batched_kernel(const KhqSeqDesc* __restrict__ descs, const KhqTablesD
             P.cents_k = t.cents_k; P.cents_v = t.cents_v; P.vq = t.vq; P.k_rotor = t.k_rotor;
             P.v_rotor = t.v_rotor; P.d_k = t.d_k; P.d_v = t.d_v;
             P.alpha_k = t.alpha_k; P.alpha_v = t.alpha_v; P.rope_base = rope_base;
-            P.start_pos = d.start_pos; P.c_len = d.c_len; P.bulk_ok = 1; P.pos_chunk = 0; P.pos_stride = 0;
+            P.start_pos = d.start_pos; P.c_len = d.c_len; P.bulk_ok = 1;
+            unpack_pos(d.pos_pack, P);
             if (d.table_id != cur_table) {
                 setup_tables(smem, P, tid);
                 if (VQS) load_codebook(reinterpret_cast<unsigned short*>(smem + SM_VQ), P.vq, tid);
@@ -587,24 +649,37 @@ khq_decode_batched_kernel(const KhqSeqDesc* __restrict__ descs, const KhqTablesD
 namespace khq {
 
 // Per problem and query head: LSE merge of the problem's partial slots, /(den+1e-8), sigmoid
-// gate, fp16 store.  grid = n_desc*HQ blocks of D threads.
-__global__ void __launch_bounds__(D)
+// gate, fp16 store.  grid = n_desc*HQ blocks of G * D threads.
+template <int G>
+__global__ void __launch_bounds__(G * D)
 khq_batched_merge_gate_kernel(const KhqSeqDesc* __restrict__ descs, const float* __restrict__ partials) {
     const int di = blockIdx.x / HQ, h = blockIdx.x % HQ, dd = threadIdx.x;
     const KhqSeqDesc d = descs[di];
-    float M = NEG_BIG;
-    for (int s = 0; s < d.n_slots; ++s)
-        M = fmaxf(M, partials[((size_t)(d.first_slot + s) * HQ + h) * PART + D]);
-    float num = 0.0f, den = 0.0f;
-    for (int s = 0; s < d.n_slots; ++s) {
-        const float* p = partials + ((size_t)(d.first_slot + s) * HQ + h) * PART;
-        const float w = __expf(p[D] - M);
-        num = fmaf(p[dd], w, num);
-        den = fmaf(p[D + 1], w, den);
-    }
+    float num, den;
+    lse_merge_records<G>(partials + ((size_t)d.first_slot * HQ + h) * PART, (size_t)HQ * PART, d.n_slots, num, den);
+    if (dd >= D) return;
     const float val = num / (den + 1e-8f);
     const float g = __half2float(d.q_gate[(size_t)h * 2 * D + D + dd]);
     d.out[(size_t)h * D + dd] = __float2half(val * (1.0f / (1.0f + __expf(-g))));
+}
+
+// The same merge without the division and the gate: one unnormalised record (num[256], max, den) per
+// (problem, head) into out_partials (n_desc, H_q, 258) -- what a context-parallel rank hands to the exchange.
+template <int G>
+__global__ void __launch_bounds__(G * D)
+khq_batched_merge_partial_kernel(const KhqSeqDesc* __restrict__ descs, const float* __restrict__ partials,
+                                 float* __restrict__ out_partials) {
+    const int di = blockIdx.x / HQ, h = blockIdx.x % HQ, dd = threadIdx.x;
+    const KhqSeqDesc d = descs[di];
+    float num, den;
+    const float M = lse_merge_records<G>(partials + ((size_t)d.first_slot * HQ + h) * PART, (size_t)HQ * PART, d.n_slots, num, den);
+    if (dd >= D) return;
+    float* o = out_partials + ((size_t)di * HQ + h) * PART;
+    o[dd] = num;
+    if (dd == 0) {
+        o[D] = (d.n_slots > 0) ? M : -1e20f;  // a problem without items: the neutral record
+        o[D + 1] = den;
+    }
 }
 
 // Fused tail of a decode step for one sequence: appends the step's token to the three rings (K
@@ -995,8 +1070,12 @@ static int attn_launch_impl(const void* q, const void* k_payload, const void* v_
         if (err != cudaSuccess) return static_cast<int>(err);
     }
     if (num_splits > 1) {
-        khq_attn_reduce_kernel<<<(unsigned)num_queries, D, 0, stream>>>(
-            static_cast<const float*>(out_partial), static_cast<float*>(out_attn), num_splits);
+        if (num_splits > 32)
+            khq_attn_reduce_kernel<MERGE_GROUPS><<<(unsigned)num_queries, MERGE_GROUPS * D, 0, stream>>>(
+                static_cast<const float*>(out_partial), static_cast<float*>(out_attn), num_splits);
+        else
+            khq_attn_reduce_kernel<1><<<(unsigned)num_queries, D, 0, stream>>>(
+                static_cast<const float*>(out_partial), static_cast<float*>(out_attn), num_splits);
         err = cudaGetLastError();
         if (err != cudaSuccess) return static_cast<int>(err);
     }
@@ -1148,12 +1227,13 @@ static int plan_sm_count() {
 #include <vector>
 
 namespace {
-constexpr int PLAN_WINDOW_COST = 3, PLAN_ITEM_COST = 16;
+constexpr int PLAN_WINDOW_COST = 3, PLAN_ITEM_COST = 56;  // measured: 0.25 us per compressed token, 0.75 us per window token, 14 us per item
 
 struct PlanRule {
-    int kind;   // 0: guided self-scheduling (cap, floor); 1: one piece count per problem (pieces)
+    int kind;   // 0: guided self-scheduling (cap, floor), windows whole; 1: piece counts per problem (pieces, win_pieces)
     int cap, floor_;
     const std::vector<int>* pieces;
+    const std::vector<int>* win_pieces;
 };
 
 // Walks the items of a plan in launch order: fn(problem, kind, lo, hi).
@@ -1162,8 +1242,13 @@ void plan_walk(const PlanRule& rule, const int* c_len, const int* win_len, int n
     long long remaining = 0;
     for (int i = 0; i < n_desc; ++i) remaining += c_len[i] > 0 ? c_len[i] : 0;
     // every raw window first (they need no tables): the last items of a launch are then small pieces
-    for (int i = 0; i < n_desc; ++i)
-        if (win_len[i] > 0) fn(i, 1, 0, win_len[i]);
+    for (int i = 0; i < n_desc; ++i) {
+        const int wl = win_len[i];
+        if (wl <= 0) continue;
+        const int wp = rule.kind == 1 ? (*rule.win_pieces)[i] : 1;
+        const int per = (wl + wp - 1) / wp;
+        for (int lo = 0; lo < wl; lo += per) fn(i, 1, lo, lo + per < wl ? lo + per : wl);
+    }
     for (int i = 0; i < n_desc; ++i) {
         const int cl = c_len[i] > 0 ? c_len[i] : 0;
         if (rule.kind == 0) {
@@ -1243,8 +1328,8 @@ extern "C" int khq_b200_plan_decode(const int* c_len, const int* win_len, int n_
     }
     tokens_per_item = ((tokens_per_item + 95) / 96) * 96;  // a multiple of every generation's staging tile (24, 32 tokens)
 
-    std::vector<int> pieces[3];
-    PlanRule best = {0, tokens_per_item, 96, nullptr};
+    std::vector<int> pieces[3], win_pieces[3];
+    PlanRule best = {0, tokens_per_item, 96, nullptr, nullptr};
     // A launch of many waves is planned by the guided rule as it stands (its tail is a fraction of a percent);
     // smaller ones compare the candidates.
     if (total <= 8LL * sms * tokens_per_item) {
@@ -1256,11 +1341,27 @@ extern "C" int khq_b200_plan_decode(const int* c_len, const int* win_len, int n_
                 best = r;
             }
         };
-        consider(PlanRule{0, tokens_per_item, 48, nullptr});
+        consider(PlanRule{0, tokens_per_item, 48, nullptr, nullptr});
         // an explicit tokens_per_item stays an upper bound on every piece
         const int max_piece = auto_size ? 2112 : tokens_per_item;
-        for (int k = 1; k <= 3; ++k)
-            if (plan_even_pieces(c_len, n_desc, k * sms, max_piece, pieces[k - 1])) consider(PlanRule{1, 0, 0, &pieces[k - 1]});
+        long long work = total;
+        for (int i = 0; i < n_desc; ++i) work += (long long)PLAN_WINDOW_COST * (win_len[i] > 0 ? win_len[i] : 0);
+        for (int k = 1; k <= 3; ++k) {
+            // k items per SM of about work / (k x SMs) each: a raw window that costs more than that is cut too
+            const long long target = std::max<long long>(work / ((long long)k * sms), 48);
+            std::vector<int>& wp = win_pieces[k - 1];
+            wp.assign(n_desc, 0);
+            int n_win = 0;
+            for (int i = 0; i < n_desc; ++i)
+                if (win_len[i] > 0) {
+                    long long c = ((long long)PLAN_WINDOW_COST * win_len[i] + target / 2) / target;
+                    c = std::min<long long>(std::max<long long>(c, 1), std::max(win_len[i] / 16, 1));
+                    wp[i] = (int)c;
+                    n_win += (int)c;
+                }
+            if (plan_even_pieces(c_len, n_desc, k * sms - n_win, max_piece, pieces[k - 1]))
+                consider(PlanRule{1, 0, 0, &pieces[k - 1], &wp});
+        }
     }
 
     // slots are numbered problem by problem (a problem's partial records are contiguous, its window first);
@@ -1290,11 +1391,9 @@ extern "C" int khq_b200_plan_decode(const int* c_len, const int* win_len, int n_
     return n;  // > max_items means the items buffer was too small
 }
 
-extern "C" int launch_khq_decode_batched_fp16(const void* descs, const void* tables, const void* items,
-                                              int n_desc, int n_items, void* workspace,
-                                              size_t workspace_bytes, int n_slots_total, float scale,
-                                              float rope_base, int ring_cap, int codebook_in_smem,
-                                              cudaStream_t stream) {
+static int decode_batched_impl(const void* descs, const void* tables, const void* items, int n_desc, int n_items,
+                               void* workspace, size_t workspace_bytes, int n_slots_total, float scale, float rope_base,
+                               int ring_cap, int codebook_in_smem, float* out_partials, cudaStream_t stream) {
     if (n_desc <= 0 || n_items <= 0 || !descs || !tables || !items || !workspace) return -100;
     if (workspace_bytes < khq_b200_decode_workspace_bytes(n_slots_total) || ring_cap <= 0) return -105;
     if (!aligned(workspace, 256)) return -104;
@@ -1328,9 +1427,38 @@ extern "C" int launch_khq_decode_batched_fp16(const void* descs, const void* tab
             static_cast<const KhqWorkItem*>(items), n_items, counter, partials, scale, rope_base, ring_cap);
     err = cudaGetLastError();
     if (err != cudaSuccess) return static_cast<int>(err);
-    khq_batched_merge_gate_kernel<<<n_desc * HQ, D, 0, stream>>>(static_cast<const KhqSeqDesc*>(descs), partials);
+    const KhqSeqDesc* dd = static_cast<const KhqSeqDesc*>(descs);
+    const bool many = n_items > 32 * n_desc;  // many records per problem
+    if (out_partials) {
+        if (many) khq_batched_merge_partial_kernel<MERGE_GROUPS><<<n_desc * HQ, MERGE_GROUPS * D, 0, stream>>>(dd, partials, out_partials);
+        else khq_batched_merge_partial_kernel<1><<<n_desc * HQ, D, 0, stream>>>(dd, partials, out_partials);
+    } else {
+        if (many) khq_batched_merge_gate_kernel<MERGE_GROUPS><<<n_desc * HQ, MERGE_GROUPS * D, 0, stream>>>(dd, partials);
+        else khq_batched_merge_gate_kernel<1><<<n_desc * HQ, D, 0, stream>>>(dd, partials);
+    }
     err = cudaGetLastError();
     return (err == cudaSuccess) ? 0 : static_cast<int>(err);
+}
+
+extern "C" int launch_khq_decode_batched_fp16(const void* descs, const void* tables, const void* items,
+                                              int n_desc, int n_items, void* workspace,
+                                              size_t workspace_bytes, int n_slots_total, float scale,
+                                              float rope_base, int ring_cap, int codebook_in_smem,
+                                              cudaStream_t stream) {
+    return decode_batched_impl(descs, tables, items, n_desc, n_items, workspace, workspace_bytes, n_slots_total, scale,
+                               rope_base, ring_cap, codebook_in_smem, nullptr, stream);
+}
+
+// The same launch, ending in one unnormalised record (acc[256], max, sum) per (problem, head) in
+// out_partials (n_desc, H_q, 258) fp32 instead of the gated fp16 outputs: the share of a context-parallel
+// rank.  Descriptors may carry chunk-cyclic positions (pos_pack; generations 1 and 2).
+extern "C" int launch_khq_decode_batched_partial_fp16(const void* descs, const void* tables, const void* items,
+                                                      int n_desc, int n_items, void* workspace, size_t workspace_bytes,
+                                                      int n_slots_total, float scale, float rope_base, int ring_cap,
+                                                      int codebook_in_smem, void* out_partials, cudaStream_t stream) {
+    if (!out_partials || !aligned(out_partials, 8)) return out_partials ? -104 : -100;
+    return decode_batched_impl(descs, tables, items, n_desc, n_items, workspace, workspace_bytes, n_slots_total, scale,
+                               rope_base, ring_cap, codebook_in_smem, static_cast<float*>(out_partials), stream);
 }
 
 // Per-sequence state of a batch engine that changes every step and is the same for all layers

@@ -66,7 +66,8 @@ struct KhqSeqDesc {  // one (sequence, layer) decode problem
     const __half* ring_k;
     const __half* ring_v;
     __half* out;
-    int table_id, c_len, start_pos, win_start, win_len, first_slot, n_slots, reserved;
+    int table_id, c_len, start_pos, win_start, win_len, first_slot, n_slots;
+    int pos_pack;  // 0: token s of the arrays sits at position start_pos + s; else (pos_chunk << 16) | (pos_stride / pos_chunk)
 };
 struct KhqTablesDesc {  // one layer's calibration tables
     const __half* cents_k;
@@ -108,6 +109,12 @@ struct CompressedKV {  // device pointers of one sequence-layer's compressed reg
     // pos_chunk == 0: consecutive positions.
     int pos_chunk, pos_stride;
 };
+
+// Chunk-cyclic positions of a descriptor (KhqSeqDesc::pos_pack) into P.
+__host__ __device__ __forceinline__ void unpack_pos(int pos_pack, CompressedKV& P) {
+    P.pos_chunk = (int)((unsigned)pos_pack >> 16);
+    P.pos_stride = P.pos_chunk * (pos_pack & 0xFFFF);
+}
 
 // Absolute position of token `tok` of the arrays.
 __device__ __forceinline__ int token_pos(const CompressedKV& P, int tok) {

@@ -225,21 +225,43 @@ __device__ __forceinline__ void m2_build_query(M2Query& Q, const __half* __restr
                                                uint2* qlo /* this kv-head's [16][32] low-order q1 fragments; the
                                                              q2 ones sit HKV*16*32 entries further */) {
     const int g = lane >> 2, t = lane & 3;
-    // q~ in the lane-owns-8-dims layout: q~ = R^T H256 (q * dinv * [dim >= 64])
+    // q~ in the lane-owns-8-dims layout: q~ = R^T H256 (q * dinv * [dim >= 64]).  This runs once per work
+    // item on the critical path, so every global load is issued before the first one is needed: the
+    // tables as wide loads, each head's query row one head ahead of its transform.
     float dv[8], rr[2][16];
+    uint4 qnext = *reinterpret_cast<const uint4*>(q + (size_t)(kvh * NREP) * q_head_stride + lane * 8);
+    // for the fragments built after the transforms: the centroids of dims 64 t + 4 s + {0..3} and the raw rotary query dims
+    uint2 cck[16];
+    uint32_t qrw[4][2];
+#pragma unroll
+    for (int s = 0; s < 16; ++s) cck[s] = (g < NREP) ? *reinterpret_cast<const uint2*>(P.cents_k + 2 * D + 64 * t + 4 * s) : make_uint2(0u, 0u);
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+        const __half* qh = q + (size_t)(kvh * NREP + (g < NREP ? g : 0)) * q_head_stride + 16 * kk + 2 * t;
+        qrw[kk][0] = (g < NREP) ? *reinterpret_cast<const uint32_t*>(qh) : 0u;
+        qrw[kk][1] = (g < NREP) ? *reinterpret_cast<const uint32_t*>(qh + 8) : 0u;
+    }
     {
         const uint4 dr = *reinterpret_cast<const uint4*>(P.d_k + lane * 8);
+        const uint4* rp = reinterpret_cast<const uint4*>(P.k_rotor + lane * 32);
+        const uint4 r0 = rp[0], r1 = rp[1], r2 = rp[2], r3 = rp[3];
         const __half* hd = reinterpret_cast<const __half*>(&dr);
 #pragma unroll
         for (int j = 0; j < 8; ++j) dv[j] = (lane >= 8) ? (1.0f / 256.0f) / (__half2float(hd[j]) + 1e-8f) : 0.0f;
+        __half hr[32];
+        *reinterpret_cast<uint4*>(&hr[0]) = r0;
+        *reinterpret_cast<uint4*>(&hr[8]) = r1;
+        *reinterpret_cast<uint4*>(&hr[16]) = r2;
+        *reinterpret_cast<uint4*>(&hr[24]) = r3;
 #pragma unroll
         for (int p = 0; p < 2; ++p)
 #pragma unroll
-            for (int i = 0; i < 16; ++i) rr[p][i] = __half2float(P.k_rotor[(lane * 2 + p) * 16 + i]);
+            for (int i = 0; i < 16; ++i) rr[p][i] = __half2float(hr[p * 16 + i]);
     }
 #pragma unroll 1
     for (int h = 0; h < NREP; ++h) {
-        const uint4 qraw = *reinterpret_cast<const uint4*>(q + (size_t)(kvh * NREP + h) * q_head_stride + lane * 8);
+        const uint4 qraw = qnext;
+        if (h + 1 < NREP) qnext = *reinterpret_cast<const uint4*>(q + (size_t)(kvh * NREP + h + 1) * q_head_stride + lane * 8);
         const __half* hq = reinterpret_cast<const __half*>(&qraw);
         float x[8];
 #pragma unroll
@@ -262,8 +284,7 @@ __device__ __forceinline__ void m2_build_query(M2Query& Q, const __half* __restr
         float v[4] = {0.0f, 0.0f, 0.0f, 0.0f}, c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         if (g < NREP) {
             const float4 qq = *reinterpret_cast<const float4*>(scratch + g * D + d0);
-            const uint2 cc = *reinterpret_cast<const uint2*>(P.cents_k + 2 * D + d0);
-            const __half* hc = reinterpret_cast<const __half*>(&cc);
+            const __half* hc = reinterpret_cast<const __half*>(&cck[s]);
             v[0] = qq.x; v[1] = qq.z; v[2] = qq.y; v[3] = qq.w;  // dims d0 + {0, 2, 1, 3}
             c[0] = __half2float(hc[0]); c[1] = __half2float(hc[2]); c[2] = __half2float(hc[1]); c[3] = __half2float(hc[3]);
         }
@@ -278,14 +299,8 @@ __device__ __forceinline__ void m2_build_query(M2Query& Q, const __half* __restr
     }
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
-        uint32_t b0 = 0, b1 = 0;
-        if (g < NREP) {
-            const __half* qh = q + (size_t)(kvh * NREP + g) * q_head_stride + 16 * kk + 2 * t;
-            b0 = *reinterpret_cast<const uint32_t*>(qh);
-            b1 = *reinterpret_cast<const uint32_t*>(qh + 8);
-        }
-        Q.qr[kk][0] = b0;
-        Q.qr[kk][1] = b1;
+        Q.qr[kk][0] = qrw[kk][0];
+        Q.qr[kk][1] = qrw[kk][1];
     }
     __syncwarp();
 }
@@ -583,6 +598,7 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
 // warps 0..3 hold in `ws` the merged state of their kv-head's six heads in the first generation's
 // layout (lane = 8 dims, rotated V domain), ready for merge_from / v_epilogue_store.  Tables must
 // be set up; all 256 threads call it.
+template <bool ALL_WARPS_MERGE = false>  // true: warps 4..7 also return the merged state of kv-head warp - 4
 __device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const __half* __restrict__ q,
                                                     size_t q_head_stride, const CompressedKV& P, int my_lo, int my_hi,
                                                     float scale, unsigned& tiles_done, WarpState& ws) {
@@ -592,15 +608,23 @@ __device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const _
     const float* freq_s = reinterpret_cast<const float*>(smem + M2_SM_FREQ);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + M2_SM_BARS);
 
+    // dim-3 centroids of this thread's 8 patches (32 consecutive halfs of each row): loaded before the query is built
+    float c3[8][2];
+    {
+        uint4 cr[2][4];
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+            for (int v = 0; v < 4; ++v) cr[r][v] = reinterpret_cast<const uint4*>(P.cents_v + r * D + 32 * g)[v];
+#pragma unroll
+        for (int pl = 0; pl < 8; ++pl) {
+            c3[pl][0] = __half2float(reinterpret_cast<const __half*>(&cr[0][0])[4 * pl + 3]) * P.alpha_v;
+            c3[pl][1] = __half2float(reinterpret_cast<const __half*>(&cr[1][0])[4 * pl + 3]) * P.alpha_v;
+        }
+    }
     M2Query Q;
     m2_build_query(Q, q, q_head_stride, P, kvh, lane, reinterpret_cast<float*>(smem + M2_SM_STAGES) + warp * NREP * D,
                    reinterpret_cast<uint2*>(smem + M2_SM_QLO) + kvh * 16 * 32);
-    float c3[8][2];
-#pragma unroll
-    for (int pl = 0; pl < 8; ++pl) {
-        c3[pl][0] = __half2float(P.cents_v[0 * D + (8 * g + pl) * 4 + 3]) * P.alpha_v;
-        c3[pl][1] = __half2float(P.cents_v[1 * D + (8 * g + pl) * 4 + 3]) * P.alpha_v;
-    }
     __syncthreads();  // the query scratch aliases the stages
 
     const int base = my_lo & ~1;
@@ -661,9 +685,9 @@ __device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const _
     }
     __syncthreads();
     ws.init();
-    if (warp < 4) {
-        merge_from(ws, reinterpret_cast<const float*>(smem + M2_SM_STAGES) + warp * MERGE_FLOATS, lane);
-        merge_from(ws, reinterpret_cast<const float*>(smem + M2_SM_STAGES) + (warp + 4) * MERGE_FLOATS, lane);
+    if (ALL_WARPS_MERGE || warp < 4) {
+        merge_from(ws, reinterpret_cast<const float*>(smem + M2_SM_STAGES) + kvh * MERGE_FLOATS, lane);
+        merge_from(ws, reinterpret_cast<const float*>(smem + M2_SM_STAGES) + (kvh + 4) * MERGE_FLOATS, lane);
     }
 }
 
@@ -704,15 +728,18 @@ khq_decode_batched_mma_kernel(const KhqSeqDesc* __restrict__ descs, const KhqTab
             P.cents_k = tb.cents_k; P.cents_v = tb.cents_v; P.vq = tb.vq; P.k_rotor = tb.k_rotor;
             P.v_rotor = tb.v_rotor; P.d_k = tb.d_k; P.d_v = tb.d_v;
             P.alpha_k = tb.alpha_k; P.alpha_v = tb.alpha_v; P.rope_base = rope_base;
-            P.start_pos = d.start_pos; P.c_len = d.c_len; P.bulk_ok = 1; P.pos_chunk = 0; P.pos_stride = 0;
+            P.start_pos = d.start_pos; P.c_len = d.c_len; P.bulk_ok = 1;
+            unpack_pos(d.pos_pack, P);
             if (d.table_id != cur_table) {
                 m2_setup_tables(smem, P, tid);
                 cur_table = d.table_id;
                 __syncthreads();
             }
             WarpState ws;
-            m2_compressed_range(smem, d.q_gate, (size_t)2 * D, P, w.lo, w.hi, scale, tiles_done, ws);
-            if (warp < 4) v_epilogue_store(ws, P, lane, ob);
+            m2_compressed_range<true>(smem, d.q_gate, (size_t)2 * D, P, w.lo, w.hi, scale, tiles_done, ws);
+            // the two warps of a kv-head transform and store three heads each
+            if (sub == 0) v_epilogue_store<0, NREP / 2>(ws, P, lane, ob);
+            else v_epilogue_store<NREP / 2, NREP>(ws, P, lane, ob);
         } else {
             WarpState ws;
             ws.init();

@@ -858,6 +858,8 @@ khq_decode_batched_tc5_kernel(const KhqSeqDesc* __restrict__ descs, const KhqTab
             P.v_rotor = tb.v_rotor; P.d_k = tb.d_k; P.d_v = tb.d_v;
             P.alpha_k = tb.alpha_k; P.alpha_v = tb.alpha_v; P.rope_base = rope_base;
             P.start_pos = d.start_pos; P.c_len = d.c_len; P.bulk_ok = 1; P.pos_chunk = 0; P.pos_stride = 0;
+            // this generation advances RoPE by whole tiles: chunk-cyclic positions are not supported (status 4)
+            if (d.pos_pack != 0 && tid == 0) atomicExch(&g_status, 4);
             if (d.table_id != cur_table) {
                 if (tid == 0) soft->all_alpha = 1;
                 __syncthreads();

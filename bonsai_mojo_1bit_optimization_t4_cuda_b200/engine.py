@@ -125,6 +125,9 @@ class BatchEngine:
                 e["table_id"] = l
         self.d_descs = torch.from_numpy(d.view(np.uint8).reshape(-1).copy()).to(dev)
         # ---- planning ----------------------------------------------------------------------
+        # tokens_per_item <= 0: the library's planner chooses (it is handed 0 every step); the size it would start
+        # from only bounds the buffers here
+        self.tokens_per_item_arg = int(tokens_per_item) if tokens_per_item > 0 else 0
         if tokens_per_item <= 0:
             sms = torch.cuda.get_device_properties(dev).multi_processor_count if dev.type == "cuda" else 148
             tokens_per_item = int(min(max(int(self.cap.sum()) // (2 * sms), 96), 2048))
@@ -194,7 +197,7 @@ class BatchEngine:
         first = np.zeros(self.B, np.int32)
         cnt = np.zeros(self.B, np.int32)
         items = ctl["items"].numpy().view(WORK_ITEM)
-        n = self.lib.khq_b200_plan_decode(c.ctypes.data, w.ctypes.data, self.B, self.tokens_per_item, items.ctypes.data,
+        n = self.lib.khq_b200_plan_decode(c.ctypes.data, w.ctypes.data, self.B, self.tokens_per_item_arg, items.ctypes.data,
                                           self.max_items, first.ctypes.data, cnt.ctypes.data)
         if n < 0 or n > self.max_items:
             raise _lib.KhqLaunchError("khq_b200_plan_decode", n)

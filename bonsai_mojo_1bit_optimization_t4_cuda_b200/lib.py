@@ -35,6 +35,8 @@ SIGNATURES = {
     "khq_b200_decode_workspace_bytes": (c_size_t, [c_int]),
     "launch_khq_decode_batched_fp16": (
         c_int, [_P, _P, _P, c_int, c_int, _P, c_size_t, c_int, c_float, c_float, c_int, c_int, _P]),
+    "launch_khq_decode_batched_partial_fp16": (
+        c_int, [_P, _P, _P, c_int, c_int, _P, c_size_t, c_int, c_float, c_float, c_int, c_int, _P, _P]),
     "launch_khq_attn_static_fp16": (
         c_int, [_P] * 17 + [c_int] * 5 + [c_float, c_float, c_float, c_float, c_int, c_int, _P]),
     "launch_khq_merge_slots_gate_fp16": (c_int, [_P, c_int, _P, _P, c_int, c_int, _P]),

@@ -129,7 +129,11 @@ typedef struct khq_seq_desc {
     int32_t win_len;            /* raw window tokens */
     int32_t first_slot;         /* filled by khq_b200_plan_decode */
     int32_t n_slots;            /* filled by khq_b200_plan_decode */
-    int32_t reserved;
+    int32_t pos_pack;           /* 0: compressed token s sits at position start_pos + s.  Otherwise the arrays
+                                 * hold every G-th chunk of a longer context (chunk-cyclic context partition):
+                                 * (pos_chunk << 16) | G, token s at start_pos + (s / pos_chunk) * G * pos_chunk
+                                 * + s % pos_chunk; pos_chunk even.  Kernel generations 1 and 2 only (3 and 4 set
+                                 * the device status word to 4). */
 } khq_seq_desc;
 
 /* One layer's calibration tables (fp16 device arrays in the khq_calib layout). 64 bytes. */
@@ -180,6 +184,16 @@ int launch_khq_decode_batched_fp16(const void* descs, const void* tables, const 
                                    int n_items, void* workspace, size_t workspace_bytes,
                                    int n_slots_total, float scale, float rope_base, int ring_cap,
                                    int codebook_in_smem, khq_stream_t stream);
+
+/* The same launch ending in one unnormalised record (acc[256], max, sum_exp) per (problem, head),
+ * out_partials (n_desc, 24, 258) fp32, instead of the gated fp16 outputs (khq_seq_desc::out is not
+ * touched): the share of one GPU in a context-parallel step, merged across GPUs by
+ * launch_khq_merge_slots_gate_fp16.  No counterpart in the reference (it serves one GPU).  Extra
+ * returns: -100 (out_partials NULL), -104 (its alignment). */
+int launch_khq_decode_batched_partial_fp16(const void* descs, const void* tables, const void* items, int n_desc,
+                                           int n_items, void* workspace, size_t workspace_bytes,
+                                           int n_slots_total, float scale, float rope_base, int ring_cap,
+                                           int codebook_in_smem, void* out_partials, khq_stream_t stream);
 
 /* ---- Pre-step: everything between the q/k/v projections and khq_step, in one launch --------
  * Replaces five launches of the reference host: head_rmsnorm_sm75_gpu on q and k
@@ -372,7 +386,9 @@ const char* khq_b200_version(void);
  * call it outside the hot loop.  Returns the flag, or -(cudaError_t) on failure. */
 int khq_b200_device_status(void);
 /* The same read, then the word is reset to 0.  Values: 1 = a bounded wait on an asynchronous copy
- * gave up, 3 = launch_khq_merge_slots_wait_gate_fp16 gave up waiting for a peer's flag. */
+ * gave up, 2 = a tensor-core decode kernel found its shared memory misaligned, 3 =
+ * launch_khq_merge_slots_wait_gate_fp16 gave up waiting for a peer's flag, 4 = a descriptor asked a
+ * decode kernel generation for chunk-cyclic positions it does not support. */
 int khq_b200_device_status_clear(void);
 
 /* ---- Context parallelism without a collective library: partials exchanged over peer memory ----

@@ -14,9 +14,9 @@ from bonsai_mojo_1bit_optimization_t4_cuda_b200 import batched
 def _check_cover(items, first, cnt, c_len, win_len):
     # slots: problem by problem, the window's first; array order: all windows, then the pieces in problem order
     assert sorted(items["slot"]) == list(range(len(items)))
-    n_win = int((np.asarray(win_len) > 0).sum())
+    n_win = int((items["kind"] == 1).sum())
     assert np.all(items["kind"][:n_win] == 1) and np.all(items["kind"][n_win:] == 0)
-    assert np.all(np.diff(items["desc"][:n_win]) > 0) and np.all(np.diff(items["desc"][n_win:]) >= 0)
+    assert np.all(np.diff(items["desc"][:n_win]) >= 0) and np.all(np.diff(items["desc"][n_win:]) >= 0)
     pos = 0
     for i, (cl, wl) in enumerate(zip(c_len, win_len)):
         assert first[i] == pos
@@ -29,9 +29,12 @@ def _check_cover(items, first, cnt, c_len, win_len):
             lo = it["hi"]
         assert lo == max(cl, 0)
         win = mine[mine["kind"] == 1]
-        assert len(win) == (1 if wl > 0 else 0)
-        if wl > 0:
-            assert (win[0]["lo"], win[0]["hi"], win[0]["slot"]) == (0, wl, pos)
+        assert (len(win) > 0) == (wl > 0)
+        lo = 0
+        for j, it in enumerate(win):  # window pieces tile [0, wl) and own the problem's first slots
+            assert it["lo"] == lo and it["hi"] > it["lo"] and it["slot"] == pos + j
+            lo = it["hi"]
+        assert lo == max(wl, 0)
         pos += cnt[i]
     assert pos == len(items)
 
@@ -79,3 +82,15 @@ def test_many_sequences_end_with_small_items():
     assert np.median(size[: len(size) // 2]) == 2112 and size[-20:].max() <= 144
     ideal = (float(c_len.sum()) + 3.0 * float(win_len.sum())) / 148.0
     assert _makespan(items) <= 1.01 * ideal
+
+
+def test_small_launch_cuts_the_raw_window_too():
+    # one sequence of 16 384 + 128 tokens: a raw token costs three compressed ones, so the window is cut into
+    # pieces of about a third of a compressed piece and everything fits one wave of 148 items
+    c_len, win_len = np.array([16384], np.int32), np.array([128], np.int32)
+    items, first, cnt = batched.plan(c_len, win_len, 0)
+    _check_cover(items, first, cnt, c_len, win_len)
+    assert len(items) <= 148
+    win = items[items["kind"] == 1]
+    comp = items[items["kind"] == 0]
+    assert len(win) >= 3 and (win["hi"] - win["lo"]).max() * 3 <= (comp["hi"] - comp["lo"]).max() + 24

@@ -349,3 +349,74 @@ def test_attn_strided_positions_vs_oracle(cuda_ops, oracle):
         check_partial(oa.cpu().numpy().reshape(H_Q, 258), want, f"strided c_len={c_len}")
     assert cuda_ops.lib.launch_khq_attn_strided_fp16(*([0] * 18), 24, 24, 1, 64, 6, 0.0625, 1.0, 1.0, 1e7, 0, 1, 127, 256, 0) == -103
     assert cuda_ops.lib.launch_khq_attn_strided_fp16(*([0] * 18), 24, 24, 1, 64, 6, 0.0625, 1.0, 1.0, 1e7, 0, 1, 128, 64, 0) == -103
+
+
+def _merge_records(recs):
+    """LSE merge of (n, 24, 258) unnormalised records into one (24, 258) record."""
+    recs = np.asarray(recs, np.float64)
+    M = recs[:, :, D].max(axis=0)
+    w = np.exp(recs[:, :, D] - M[None])
+    out = np.zeros((H_Q, 258))
+    out[:, :D] = (recs[:, :, :D] * w[:, :, None]).sum(axis=0)
+    out[:, D] = M
+    out[:, D + 1] = (recs[:, :, D + 1] * w).sum(axis=0)
+    return out.astype(np.float32)
+
+
+@pytest.mark.parametrize("c_len,win_len,cyclic", [(1000, 0, True), (128 * 40 + 64, 200, True), (2500, 256, False), (0, 130, False)])
+def test_persistent_slice_vs_oracle(cuda_ops, oracle, c_len, win_len, cyclic):
+    """PersistentSlice (launch_khq_decode_batched_partial_fp16): the share of rank 1 of 3 of a context-parallel
+    step -- its slice of the compressed region (chunk-cyclic or contiguous positions) and the raw window -- as
+    one launch of the persistent kernel ending in one unnormalised record, against the oracle's records of the
+    same slice and window merged on the host."""
+    torch = _torch()
+    from bonsai_mojo_1bit_optimization_t4_cuda_b200.context_parallel import PersistentSlice, partition_context
+
+    world, rank = 3, 1
+    case = cases.make_case(5200 + c_len + win_len, c_len + win_len + 1, "calib")
+    f, tb = case["f16"], case["tables"]
+    tab = {k: dev(v) for k, v in f.items()}
+    recs = []
+    if c_len > 0:
+        kv_full = cases.compress_with(oracle.compress, case, c_len)
+        if cyclic:
+            chunks = list(range(rank, (c_len + 127) // 128, world))
+            idx = np.concatenate([np.arange(c * 128 * H_KV, min(c_len, (c + 1) * 128) * H_KV) for c in chunks])
+            start_pos, chunk, stride = rank * 128, 128, world * 128
+        else:
+            lo, hi = partition_context(c_len, world)[rank]
+            idx = np.arange(lo * H_KV, hi * H_KV)
+            start_pos, chunk, stride = lo, 0, 0
+        kv = {k: np.ascontiguousarray(v[idx]) for k, v in kv_full.items() if k != "near_ties"}
+        n = len(idx) // H_KV
+        want_c = np.zeros((H_Q, 258), np.float32)
+        oracle.OracleOps().attn_strided(case["q_gate"], kv["k_payload"], kv["v_payload"], kv["v_shared_meta"], kv["k_mask"],
+                                        kv["k_norms"], kv["k_r_norms"], kv["v_norms"], kv["v_r_norms"], f["cents_k"], f["cents_v"],
+                                        f["vq"], f["rotor_k"], f["rotor_v"], f["d_k"], f["d_v"], want_c, None, H_Q, H_Q, 1, n, 6,
+                                        SCALE, tb.alpha_k, tb.alpha_v, 1e7, start_pos, 1, chunk if chunk else n + 2 - n % 2,
+                                        stride if stride else n + 2 - n % 2)
+        recs.append(want_c)
+    else:
+        # no compressed token on this rank: one dummy row keeps the arrays addressable
+        kv = {k: np.zeros((H_KV,) + v.shape[1:], v.dtype) for k, v in cases.compress_with(oracle.compress, case, 1).items()
+              if k != "near_ties"}
+        n, start_pos, chunk, stride = 0, 0, 0, 0
+    ring_k = np.zeros((256, H_KV, D), np.float16)
+    ring_v = np.zeros((256, H_KV, D), np.float16)
+    win_start = c_len % 256
+    if win_len > 0:
+        for s in range(win_len):
+            ring_k[(win_start + s) % 256], ring_v[(win_start + s) % 256] = case["k_roped"][c_len + s], case["v"][c_len + s]
+        want_w = np.zeros((H_Q, 258), np.float32)
+        oracle.window_attn(case["q_gate"], ring_k, ring_v, want_w, win_start, win_len, 256, H_Q, H_KV, D, SCALE)
+        recs.append(want_w)
+    arr = {k: dev(v) for k, v in kv.items()}
+    ps = PersistentSlice(cuda_ops.lib, arr, tab, tb.alpha_k, tb.alpha_v, dev(ring_k), dev(ring_v), start_pos=start_pos,
+                         pos_chunk=chunk, pos_stride_chunks=(stride // chunk if chunk else 0))
+    out = torch.full((H_Q, 258), float("nan"), dtype=torch.float32, device="cuda")
+    q = dev(case["q_gate"])
+    for _ in range(2):  # the second call reuses the plan
+        ps.launch(q, n, win_start, win_len, out, SCALE, 1e7)
+    torch.cuda.synchronize()
+    assert cuda_ops.lib.khq_b200_device_status() == 0
+    check_partial(out.cpu().numpy(), _merge_records(recs), f"persistent slice c_len={c_len} win={win_len} cyclic={cyclic}")
