@@ -206,15 +206,22 @@ class PersistentSlice:
         self.ws_bytes = int(lib.khq_b200_decode_workspace_bytes(self.max_items))
         self.workspace = torch.zeros(self.ws_bytes, dtype=torch.uint8, device=dev)
         self._planned = None
+        self._descs = {}
         self._sent = torch.cuda.Event()
         self.n_items = 0
 
-    def launch(self, q_gate: torch.Tensor, n_tok: int, win_start: int, win_len: int, out_partial: torch.Tensor,
+    def launch(self, q_gate, n_tok: int, win_start: int, win_len: int, out_partial: torch.Tensor,
                scale: float, rope_base: float) -> None:
-        """out_partial: (24, 258) fp32.  n_tok + win_len must be positive."""
+        """q_gate: (24*512,) fp16 tensor, or the device address of one (the peer exchange hands out the
+        address of the query inside its own buffer).  out_partial: (24, 258) fp32.  n_tok + win_len must
+        be positive."""
         from .batched import SEQ_DESC
 
-        self.q.copy_(q_gate.reshape(-1), non_blocking=True)
+        if isinstance(q_gate, int):
+            q_ptr = q_gate
+        else:
+            self.q.copy_(q_gate.reshape(-1), non_blocking=True)
+            q_ptr = self.q.data_ptr()
         if self._planned != (n_tok, win_start, win_len):
             self._sent.synchronize()  # the pinned buffers may still be the source of the last copies
             c = np.array([n_tok], np.int32)
@@ -230,11 +237,19 @@ class PersistentSlice:
             d[0]["first_slot"], d[0]["n_slots"] = int(first[0]), int(cnt[0])
             nb = self.n_items * self.item_bytes
             self.d_items[:nb].copy_(self.h_items[:nb], non_blocking=True)
-            self.d_desc.copy_(self.h_desc, non_blocking=True)
             self._sent.record(torch.cuda.current_stream())
+            self._descs = {}
             self._planned = (n_tok, win_start, win_len)
+        d_desc = self._descs.get(q_ptr)
+        if d_desc is None:  # one device descriptor per query address (the exchange alternates between two)
+            self._sent.synchronize()
+            self.h_desc.numpy().view(SEQ_DESC)[0]["q_gate"] = q_ptr
+            d_desc = torch.empty_like(self.d_desc)
+            d_desc.copy_(self.h_desc, non_blocking=True)
+            self._sent.record(torch.cuda.current_stream())
+            self._descs[q_ptr] = d_desc
         self._check("launch_khq_decode_batched_partial_fp16", self.lib.launch_khq_decode_batched_partial_fp16(
-            self.d_desc.data_ptr(), self.d_tables.data_ptr(), self.d_items.data_ptr(), 1, self.n_items,
+            d_desc.data_ptr(), self.d_tables.data_ptr(), self.d_items.data_ptr(), 1, self.n_items,
             self.workspace.data_ptr(), self.ws_bytes, self.n_items, float(scale), float(rope_base), 256,
             int(self.generation), out_partial.data_ptr(), self._stream()))
 
@@ -284,6 +299,7 @@ class ContextParallelDecode:
         assert engine in ("splits", "persistent")
         self.persistent = None
         if engine == "persistent":
+            self.mine[1].copy_(self._neutral)
             mine_ring = self.rank == self.owner
             cyc = partition == "cyclic"
             self.persistent = PersistentSlice(ops.lib, kv, tables, alpha_k, alpha_v, ring_k if mine_ring else None,
@@ -337,8 +353,7 @@ class ContextParallelDecode:
                 self.persistent.launch(q_gate, n, win_start, wl, self.mine[0], scale, rope_base)
             else:
                 self.mine[0].copy_(self._neutral)
-            self.mine[1].copy_(self._neutral)
-            return self._exchange_and_merge(q_gate)
+            return self._exchange_and_merge(q_gate)  # mine[1] stays the neutral record it was initialised to
         if n > 0 and self.partition == "cyclic":
             ops.attn_strided(q_gate, kv["k_payload"], kv["v_payload"], kv["v_shared_meta"], kv["k_mask"], kv["k_norms"],
                              kv["k_r_norms"], kv["v_norms"], kv["v_r_norms"], tb["cents_k"], tb["cents_v"], tb["vq"],
