@@ -72,6 +72,8 @@ def parse():
                          "one NCCL all-gather (collective)")
     ap.add_argument("--partition", default="contiguous", choices=["contiguous", "cyclic"],
                     help="--workload long / long_context: contiguous context ranges, or 128-token chunks dealt cyclically")
+    ap.add_argument("--tokens-per-item", type=int, default=0,
+                    help="largest work item of the batched decode in tokens (0: the library's planner chooses)")
     ap.add_argument("--cp-engine", default="persistent", choices=["persistent", "splits"],
                     help="--workload long / long_context: each rank's slice and the raw window as one launch of the persistent "
                          "batched kernel, or the drop-in split launches (--splits) plus the window launch")
@@ -1022,7 +1024,8 @@ def main():
     # ---- headline: args.seqs sequences on every GPU (weak scaling), no collective -------------------
     c_len, win = workload(args, rank)
     t_setup = time.perf_counter()
-    eng = BatchEngine(tables, c_len, win, device=f"cuda:{local_rank}", codebook_in_smem=gen, grow_tokens=256)
+    eng = BatchEngine(tables, c_len, win, device=f"cuda:{local_rank}", codebook_in_smem=gen, grow_tokens=256,
+                      tokens_per_item=args.tokens_per_item)
     eng.fill_synthetic(20260914 + 1000 * 3 + rank)
     torch.cuda.synchronize()
     setup_s = time.perf_counter() - t_setup
