@@ -110,6 +110,26 @@ struct CompressedKV {  // device pointers of one sequence-layer's compressed reg
     int pos_chunk, pos_stride;
 };
 
+// Stages a layer's V codebook (NP patches x 256 codes x 3 halfs; entry e = patch * 256 + code starts at
+// half 3e) into the two shared-memory tables of the tensor-core generations: the (d0, d1) word at
+// vqa[code * STRIDE_A_WORDS + patch], the d2 half at vqb[code * (STRIDE_B_BYTES / 2) + patch].  Two
+// entries (three words) per thread and iteration, eight iterations' loads in flight: the staging runs
+// once per CTA and layer and is bound by load latency, not by bytes.
+template <int NT, int STRIDE_A_WORDS, int STRIDE_B_BYTES>
+__device__ __forceinline__ void stage_vq_codebook(const __half* __restrict__ vq, unsigned int* __restrict__ vqa,
+                                                  unsigned short* __restrict__ vqb, int tid) {
+    const unsigned int* src = reinterpret_cast<const unsigned int*>(vq);
+#pragma unroll 8
+    for (int u = tid; u < NP * 256 / 2; u += NT) {
+        const unsigned int w0 = __ldg(src + 3 * u), w1 = __ldg(src + 3 * u + 1), w2 = __ldg(src + 3 * u + 2);
+        const int e = 2 * u, patch = e >> 8, code = e & 255;  // the pair never straddles a patch (256 codes)
+        vqa[code * STRIDE_A_WORDS + patch] = w0;
+        vqb[code * (STRIDE_B_BYTES / 2) + patch] = (unsigned short)(w1 & 0xFFFFu);
+        vqa[(code + 1) * STRIDE_A_WORDS + patch] = (w1 >> 16) | (w2 << 16);
+        vqb[(code + 1) * (STRIDE_B_BYTES / 2) + patch] = (unsigned short)(w2 >> 16);
+    }
+}
+
 // Chunk-cyclic positions of a descriptor (KhqSeqDesc::pos_pack) into P.
 __host__ __device__ __forceinline__ void unpack_pos(int pos_pack, CompressedKV& P) {
     P.pos_chunk = (int)((unsigned)pos_pack >> 16);

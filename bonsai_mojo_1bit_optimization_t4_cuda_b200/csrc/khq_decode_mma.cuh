@@ -190,26 +190,7 @@ __device__ __forceinline__ void m2_setup_tables(unsigned char* smem, const Compr
         brot[512 + e] = hi;    // rotor (residual operand), fp16 hi
         brot[1536 + e] = lo;   //   and what fp16 lost
     }
-    // one (patch, code) entry per iteration: its three halfs lie in two consecutive words of the
-    // table (entry e starts at half 3e), and go to one word of the (d0, d1) table and one half of the d2 table
-    {
-        const unsigned int* src = reinterpret_cast<const unsigned int*>(P.vq);
-        for (int e = tid; e < NP * 256; e += M2_THREADS) {
-            const int w = (3 * e) >> 1;
-            const unsigned int a = __ldg(src + w), b = __ldg(src + w + 1);
-            unsigned int d01, d2;
-            if (e & 1) {  // starts at the high half of word w
-                d01 = (a >> 16) | (b << 16);
-                d2 = b >> 16;
-            } else {
-                d01 = a;
-                d2 = b & 0xFFFFu;
-            }
-            const int patch = e >> 8, code = e & 255;
-            reinterpret_cast<unsigned int*>(vqa)[code * M2_VQA_STRIDE + patch] = d01;
-            vqb[code * (M2_VQB_STRIDE / 2) + patch] = (unsigned short)d2;
-        }
-    }
+    stage_vq_codebook<M2_THREADS, M2_VQA_STRIDE, M2_VQB_STRIDE>(P.vq, reinterpret_cast<unsigned int*>(vqa), vqb, tid);
 }
 
 // Query-side operands of one (sequence, layer, kv-head): this warp's B fragments.

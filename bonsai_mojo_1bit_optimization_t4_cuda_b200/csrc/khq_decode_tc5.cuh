@@ -215,26 +215,7 @@ __device__ __forceinline__ void setup_layer(unsigned char* smem, const Compresse
     Soft* soft = reinterpret_cast<Soft*>(smem + SM_SOFT);
     unsigned short* vqa = reinterpret_cast<unsigned short*>(smem + SM_VQA);
     unsigned short* vqb = reinterpret_cast<unsigned short*>(smem + SM_VQB);
-    // one (patch, code) entry per iteration: its three halfs lie in two consecutive words of the
-    // table (entry e starts at half 3e), and go to one word of the (d0, d1) table and one half of the d2 table
-    {
-        const unsigned int* src = reinterpret_cast<const unsigned int*>(P.vq);
-        for (int e = tid; e < NP * 256; e += NT) {
-            const int w = (3 * e) >> 1;
-            const unsigned int a = __ldg(src + w), b = __ldg(src + w + 1);
-            unsigned int d01, d2;
-            if (e & 1) {  // starts at the high half of word w
-                d01 = (a >> 16) | (b << 16);
-                d2 = b >> 16;
-            } else {
-                d01 = a;
-                d2 = b & 0xFFFFu;
-            }
-            const int patch = e >> 8, code = e & 255;
-            reinterpret_cast<unsigned int*>(vqa)[code * VQA_STRIDE + patch] = d01;
-            vqb[code * (VQB_STRIDE / 2) + patch] = (unsigned short)d2;
-        }
-    }
+    stage_vq_codebook<NT, VQA_STRIDE, VQB_STRIDE>(P.vq, reinterpret_cast<unsigned int*>(vqa), vqb, tid);
     // rotary columns: B[kap(i)][32 + m] = ceff_i * dinv_m * sum_c' R[p][c'][k] * (-1)^popc(m & ((4p + c') & 63))
     for (int e = tid; e < 64 * D; e += NT) {
         const int m = e & 63, i = e >> 6;
