@@ -107,8 +107,10 @@ class BatchEngine:
         self.ring_u = [ring() for _ in range(self.L)]
         self.q_gate = [z(self.B * H_Q * 2 * D, torch.float16).view(self.B, H_Q * 2 * D) for _ in range(self.L)]
         self.out = [z(self.B * H_Q * D, torch.float16).view(self.B, H_Q * D) for _ in range(self.L)]
-        self.d_k = z(self.B * KV, torch.float16).view(self.B, KV)
-        self.d_v = z(self.B * KV, torch.float16).view(self.B, KV)
+        # two parities of the K / V input rows: the copy stream fills one while the pre-step reads the other
+        self.d_k = [z(self.B * KV, torch.float16).view(self.B, KV) for _ in range(2)]
+        self.d_v = [z(self.B * KV, torch.float16).view(self.B, KV) for _ in range(2)]
+        self._copy_stream = torch.cuda.Stream(device=dev) if dev.type == "cuda" else None
         # ---- descriptors: layer-major, pointers fixed, the step-dependent ints rewritten per step
         d = np.zeros(self.L * self.B, SEQ_DESC)
         for l in range(self.L):
@@ -319,16 +321,34 @@ class BatchEngine:
         if ctl["done"] is not None:
             ctl["done"].record()
         seg_bytes = self.B * COMPRESS_SEG.itemsize
+        # Host <-> device copies run on their own stream, one layer ahead of (inputs) and behind (outputs) the
+        # kernels: layer l's inputs land while layer l - 1 computes.  Events order the two streams.
+        main, cs = torch.cuda.current_stream(), self._copy_stream
+        cs.wait_stream(main)  # everything queued so far (the previous step's reads of q_gate / d_k / d_v, the control block)
+        in_ready, k_free = [None] * self.L, [None] * self.L
+
+        def stage_inputs(l):
+            with torch.cuda.stream(cs):
+                if l >= 2:
+                    cs.wait_event(k_free[l - 2])  # the pre-step of layer l - 2 has consumed this parity of d_k / d_v
+                self.q_gate[l].copy_(self.h_q[l], non_blocking=True)
+                self.d_k[l & 1].copy_(self.h_k[l], non_blocking=True)
+                self.d_v[l & 1].copy_(self.h_v[l], non_blocking=True)
+                in_ready[l] = cs.record_event()
+
+        stage_inputs(0)
         for l in range(self.L):
-            self.q_gate[l].copy_(self.h_q[l], non_blocking=True)
-            self.d_k.copy_(self.h_k[l], non_blocking=True)
-            self.d_v.copy_(self.h_v[l], non_blocking=True)
+            if l + 1 < self.L:
+                stage_inputs(l + 1)
+            main.wait_event(in_ready[l])
+            d_k, d_v = self.d_k[l & 1], self.d_v[l & 1]
             qw, kw = self.norm_w[l] if self.norm_w is not None else (None, None)
             rc = self.lib.launch_khq_prestep_batched_fp16(
-                self.q_gate[l].data_ptr(), self.d_k.data_ptr(), self.d_v.data_ptr(), _lib.ptr(qw), _lib.ptr(kw),
+                self.q_gate[l].data_ptr(), d_k.data_ptr(), d_v.data_ptr(), _lib.ptr(qw), _lib.ptr(kw),
                 self.ring_k[l].data_ptr(), self.ring_v[l].data_ptr(), self.ring_u[l].data_ptr(), RING * KV, self.d_slots.data_ptr(),
                 self.d_pos.data_ptr(), self.B, H_Q, H_KV, D, ROTARY_DIM, self.rope_theta, self.rms_eps, 1 if qw is not None else 0, st)
             check("launch_khq_prestep_batched_fp16", rc)
+            k_free[l] = main.record_event()
             if n_ev:
                 tb, P = self.tables[l], self.pay[l]
                 seg_ptr = self.d_segs.data_ptr() + l * seg_bytes
@@ -344,5 +364,9 @@ class BatchEngine:
                     self._v_minus_u[l], st)
                 check("launch_khq_compress_batched_fp16", rc)
             self.attention_resident(l, scale)
-            self.h_out[l].copy_(self.out[l], non_blocking=True)
+            done_l = main.record_event()
+            with torch.cuda.stream(cs):
+                cs.wait_event(done_l)
+                self.h_out[l].copy_(self.out[l], non_blocking=True)
+        main.wait_stream(cs)  # the caller synchronises the current stream before it reads h_out
         return self.h_out
