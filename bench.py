@@ -632,7 +632,7 @@ def loop_measure(args, dev, n_layers, with_reference_kernels=True):
            "ours": {"prompt_ms": ms_prompt, "decode_ms": ms_decode,
                     "us_per_layer_step": 1e3 * ms_decode / (decode * n_layers),
                     "tok_s": decode / (ms_decode * 1e-3), "path": "khq_prefill (tcgen05 prefill + appends) then khq_step_fused"},
-           "reference_t4_published": {"khq_overhead_us_per_layer_step": 176.0, "source": "BASELINE.md section 1 (README.md:44-47, Tesla T4)"},
+           "reference_t4_published": {"khq_overhead_us_per_layer_step": 176.0, "source": "the reference's README.md:44-47 (Tesla T4)"},
            "device_status": khqlib.load().khq_b200_device_status()}
     ref_path = ROOT / "oracle" / "_ref" / "libbonsai_ref_sm100a.so"
     if with_reference_kernels and ref_path.exists():
