@@ -56,7 +56,8 @@ constexpr int M2_SM_FREQ = M2_SM_LUT + 448;
 constexpr int M2_SM_DINV = M2_SM_FREQ + 128;                         // 64 floats
 constexpr int M2_SM_BARS = M2_SM_DINV + 256;
 constexpr int M2_SM_QLO = M2_SM_BARS + 64;                           // 2 kinds x 4 kv-heads x 16 steps x 32 lanes x 8 B
-constexpr int M2_SM_TOTAL = M2_SM_QLO + 2 * HKV * 16 * 32 * 8;
+constexpr int M2_SM_C3 = M2_SM_QLO + 2 * HKV * 16 * 32 * 8;              // 64 patches x float2: dim-3 centroids x alpha_v
+constexpr int M2_SM_TOTAL = M2_SM_C3 + NP * 8;
 static_assert(M2_SM_TOTAL <= 227 * 1024 && M2_SM_QLO % 16 == 0 && M2_SM_ROPE % 16 == 0 && M2_SM_VQB % 16 == 0,
               "shared memory budget");
 static_assert(HKV * MERGE_FLOATS * 4 <= 256 * M2_VQA_STRIDE * 4, "cluster export records alias the codebook");
@@ -156,6 +157,9 @@ __device__ __forceinline__ void m2_setup_tables(unsigned char* smem, const Compr
     unsigned short* vqa = reinterpret_cast<unsigned short*>(smem + M2_SM_VQ);
     unsigned short* vqb = reinterpret_cast<unsigned short*>(smem + M2_SM_VQB);
     if (tid < 32) freq_s[tid] = powf(P.rope_base, -2.0f * (float)tid / 64.0f);
+    if (tid >= 128 && tid < 128 + NP)
+        reinterpret_cast<float2*>(smem + M2_SM_C3)[tid - 128] = make_float2(__half2float(P.cents_v[0 * D + 4 * (tid - 128) + 3]) * P.alpha_v,
+                                                                             __half2float(P.cents_v[1 * D + 4 * (tid - 128) + 3]) * P.alpha_v);
     if (tid < 64) dinv_s[tid] = (1.0f / 256.0f) / (__half2float(P.d_k[tid]) + 1e-8f);
     if (tid >= 64 && tid < 64 + KD_LUT_ENTRIES) lut[tid - 64] = kd_make_lut_entry((uint32_t)(tid - 64));
     // Rotor B fragments with the three low index bits of the 64-point Hadamard transform folded
@@ -303,7 +307,7 @@ struct M2State {
 __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, const unsigned char* __restrict__ smem,
                                          const float2* __restrict__ rope, int r0, int kvh, int lane, int valid_lo,
                                          int valid_hi, const M2Query& Q, const CompressedKV& P, float scale,
-                                         const float (&c3)[8][2], M2State& st) {
+                                         M2State& st) {
     const int g = lane >> 2, t = lane & 3;
     const KdLutEntry* lut = reinterpret_cast<const KdLutEntry*>(smem + M2_SM_LUT);
     const uint2* brot = reinterpret_cast<const uint2*>(smem + M2_SM_BROT);
@@ -311,6 +315,7 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
     const float* dinv_s = reinterpret_cast<const float*>(smem + M2_SM_DINV);
     const unsigned char* vqa = smem + M2_SM_VQ;
     const unsigned char* vqb = smem + M2_SM_VQB;
+    const float2* c3s = reinterpret_cast<const float2*>(smem + M2_SM_C3) + 8 * g;
 
     // ================================ K side: scores ==========================================
     const uint32_t* kp[2];
@@ -553,9 +558,10 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
             const int pl = 2 * pp + u;
             float cv[4];
             uint32_t dv[4];
+            const float2 c3p = c3s[pl];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                cv[i] = ((f3[u][i] >> 7) & 1u) ? c3[pl][1] : c3[pl][0];
+                cv[i] = ((f3[u][i] >> 7) & 1u) ? c3p.y : c3p.x;
                 dv[i] = 0x6400u | (f3[u][i] >> 8);  // fp16 bits of 1024 + dump
             }
             ca[u] = m2_pack(cv[0], cv[1]);
@@ -589,20 +595,6 @@ __device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const _
     const float* freq_s = reinterpret_cast<const float*>(smem + M2_SM_FREQ);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + M2_SM_BARS);
 
-    // dim-3 centroids of this thread's 8 patches (32 consecutive halfs of each row): loaded before the query is built
-    float c3[8][2];
-    {
-        uint4 cr[2][4];
-#pragma unroll
-        for (int r = 0; r < 2; ++r)
-#pragma unroll
-            for (int v = 0; v < 4; ++v) cr[r][v] = reinterpret_cast<const uint4*>(P.cents_v + r * D + 32 * g)[v];
-#pragma unroll
-        for (int pl = 0; pl < 8; ++pl) {
-            c3[pl][0] = __half2float(reinterpret_cast<const __half*>(&cr[0][0])[4 * pl + 3]) * P.alpha_v;
-            c3[pl][1] = __half2float(reinterpret_cast<const __half*>(&cr[1][0])[4 * pl + 3]) * P.alpha_v;
-        }
-    }
     M2Query Q;
     m2_build_query(Q, q, q_head_stride, P, kvh, lane, reinterpret_cast<float*>(smem + M2_SM_STAGES) + warp * NREP * D,
                    reinterpret_cast<uint2*>(smem + M2_SM_QLO) + kvh * 16 * 32);
@@ -634,7 +626,7 @@ __device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const _
         const int vlo = max(my_lo - blk0, 0), vhi = min(my_hi - blk0, 16);
         if (vhi > vlo)
             m2_block(smem + M2_SM_STAGES + stg * M2_STAGE_BYTES, smem, rope_tab + (i & 1) * M2_TT * 32, 16 * sub, kvh,
-                     lane, vlo, vhi, Q, P, scale, c3, st);
+                     lane, vlo, vhi, Q, P, scale, st);
         __syncthreads();  // stage and rope buffer free for the tile after next
     }
     tiles_done = t0 + (unsigned)ntiles;
