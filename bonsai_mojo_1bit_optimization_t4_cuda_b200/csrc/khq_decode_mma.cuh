@@ -57,7 +57,8 @@ constexpr int M2_SM_DINV = M2_SM_FREQ + 128;                         // 64 float
 constexpr int M2_SM_BARS = M2_SM_DINV + 256;
 constexpr int M2_SM_QLO = M2_SM_BARS + 64;                           // 2 kinds x 4 kv-heads x 16 steps x 32 lanes x 8 B
 constexpr int M2_SM_C3 = M2_SM_QLO + 2 * HKV * 16 * 32 * 8;              // 64 patches x float2: dim-3 centroids x alpha_v
-constexpr int M2_SM_TOTAL = M2_SM_C3 + NP * 8;
+constexpr int M2_SM_QR = M2_SM_C3 + NP * 8;                             // raw rotary query fragments: 4 kv-heads x 4 k-steps x 32 lanes x 8 B
+constexpr int M2_SM_TOTAL = M2_SM_QR + HKV * 4 * 32 * 8;
 static_assert(M2_SM_TOTAL <= 227 * 1024 && M2_SM_QLO % 16 == 0 && M2_SM_ROPE % 16 == 0 && M2_SM_VQB % 16 == 0,
               "shared memory budget");
 static_assert(HKV * MERGE_FLOATS * 4 <= 256 * M2_VQA_STRIDE * 4, "cluster export records alias the codebook");
@@ -201,14 +202,14 @@ __device__ __forceinline__ void m2_setup_tables(unsigned char* smem, const Compr
 struct M2Query {
     uint32_t q1[16][2];  // q~ * c   (ternary part), per k-step
     uint32_t q2[16][2];  // q~       (residual part)
-    uint32_t qr[4][2];   // raw rotary query dims 0..63
 };
 
 // q: (H_q, ..) with `q_head_stride` halfs between heads.  scratch: this warp's NREP*D floats.
 __device__ __forceinline__ void m2_build_query(M2Query& Q, const __half* __restrict__ q, size_t q_head_stride,
                                                const CompressedKV& P, int kvh, int lane, float* scratch,
                                                uint2* qlo /* this kv-head's [16][32] low-order q1 fragments; the
-                                                             q2 ones sit HKV*16*32 entries further */) {
+                                                             q2 ones sit HKV*16*32 entries further */,
+                                               uint2* qr_s /* this kv-head's [4][32] raw rotary query fragments */) {
     const int g = lane >> 2, t = lane & 3;
     // q~ in the lane-owns-8-dims layout: q~ = R^T H256 (q * dinv * [dim >= 64]).  This runs once per work
     // item on the critical path, so every global load is issued before the first one is needed: the
@@ -283,10 +284,7 @@ __device__ __forceinline__ void m2_build_query(M2Query& Q, const __half* __restr
         qlo[HKV * 16 * 32 + s * 32 + lane] = lo2;
     }
 #pragma unroll
-    for (int kk = 0; kk < 4; ++kk) {
-        Q.qr[kk][0] = qrw[kk][0];
-        Q.qr[kk][1] = qrw[kk][1];
-    }
+    for (int kk = 0; kk < 4; ++kk) qr_s[kk * 32 + lane] = make_uint2(qrw[kk][0], qrw[kk][1]);  // both warps of a kv-head write the same values
     __syncwarp();
 }
 
@@ -316,6 +314,7 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
     const unsigned char* vqa = smem + M2_SM_VQ;
     const unsigned char* vqb = smem + M2_SM_VQB;
     const float2* c3s = reinterpret_cast<const float2*>(smem + M2_SM_C3) + 8 * g;
+    const uint2* qr_s = reinterpret_cast<const uint2*>(smem + M2_SM_QR) + kvh * 4 * 32;
 
     // ================================ K side: scores ==========================================
     const uint32_t* kp[2];
@@ -430,8 +429,9 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
             m2_pack_hilo(cu[2 * kk][2], cu[2 * kk][3], a[1], al[1]);
             m2_pack_hilo(cu[2 * kk + 1][0], cu[2 * kk + 1][1], a[2], al[2]);
             m2_pack_hilo(cu[2 * kk + 1][2], cu[2 * kk + 1][3], a[3], al[3]);
-            m2_mma(cr, a, Q.qr[kk][0], Q.qr[kk][1]);
-            m2_mma_lo(cr, al, Q.qr[kk][0], Q.qr[kk][1]);
+            const uint2 qrk = qr_s[kk * 32 + lane];
+            m2_mma(cr, a, qrk.x, qrk.y);
+            m2_mma_lo(cr, al, qrk.x, qrk.y);
         }
     }
     // ================================ softmax over the block ====================================
@@ -597,7 +597,8 @@ __device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const _
 
     M2Query Q;
     m2_build_query(Q, q, q_head_stride, P, kvh, lane, reinterpret_cast<float*>(smem + M2_SM_STAGES) + warp * NREP * D,
-                   reinterpret_cast<uint2*>(smem + M2_SM_QLO) + kvh * 16 * 32);
+                   reinterpret_cast<uint2*>(smem + M2_SM_QLO) + kvh * 16 * 32,
+                   reinterpret_cast<uint2*>(smem + M2_SM_QR) + kvh * 4 * 32);
     __syncthreads();  // the query scratch aliases the stages
 
     const int base = my_lo & ~1;
