@@ -49,8 +49,8 @@ constexpr int M2_VQA_STRIDE = 65;                                    // words pe
 constexpr int M2_VQB_STRIDE = 130;                                   // bytes per code row
 constexpr int M2_SM_VQ = M2_SM_STAGES + M2_NSTAGE * M2_STAGE_BYTES;  // (d0, d1): 256 x 65 x 4 B
 constexpr int M2_SM_VQB = M2_SM_VQ + 256 * M2_VQA_STRIDE * 4;        // d2: 256 x 130 B
-constexpr int M2_SM_ROPE = M2_SM_VQB + 256 * M2_VQB_STRIDE;          // 2 x 32 tokens x 32 float2
-constexpr int M2_SM_BROT = M2_SM_ROPE + 2 * M2_TT * 32 * 8;          // 4 kinds x 16 steps x 32 lanes x 8 B
+constexpr int M2_SM_ROPE = M2_SM_VQB + 256 * M2_VQB_STRIDE;          // 32 tokens x 32 float2
+constexpr int M2_SM_BROT = M2_SM_ROPE + M2_TT * 32 * 8;          // 4 kinds x 16 steps x 32 lanes x 8 B
 constexpr int M2_SM_LUT = M2_SM_BROT + 4 * 16 * 32 * 8;              // scatter table
 constexpr int M2_SM_FREQ = M2_SM_LUT + 448;
 constexpr int M2_SM_DINV = M2_SM_FREQ + 128;                         // 64 floats
@@ -58,7 +58,9 @@ constexpr int M2_SM_BARS = M2_SM_DINV + 256;
 constexpr int M2_SM_QLO = M2_SM_BARS + 64;                           // 2 kinds x 4 kv-heads x 16 steps x 32 lanes x 8 B
 constexpr int M2_SM_C3 = M2_SM_QLO + 2 * HKV * 16 * 32 * 8;              // 64 patches x float2: dim-3 centroids x alpha_v
 constexpr int M2_SM_QR = M2_SM_C3 + NP * 8;                             // raw rotary query fragments: 4 kv-heads x 4 k-steps x 32 lanes x 8 B
-constexpr int M2_SM_TOTAL = M2_SM_QR + HKV * 4 * 32 * 8;
+constexpr int M2_Q2_SMEM_STEPS = 12;                                     // k-steps whose residual-part query fragments live in shared memory
+constexpr int M2_SM_Q2 = M2_SM_QR + HKV * 4 * 32 * 8;                    // 4 kv-heads x M2_Q2_SMEM_STEPS x 32 lanes x 8 B
+constexpr int M2_SM_TOTAL = M2_SM_Q2 + HKV * M2_Q2_SMEM_STEPS * 32 * 8;
 static_assert(M2_SM_TOTAL <= 227 * 1024 && M2_SM_QLO % 16 == 0 && M2_SM_ROPE % 16 == 0 && M2_SM_VQB % 16 == 0,
               "shared memory budget");
 static_assert(HKV * MERGE_FLOATS * 4 <= 256 * M2_VQA_STRIDE * 4, "cluster export records alias the codebook");
@@ -201,7 +203,7 @@ __device__ __forceinline__ void m2_setup_tables(unsigned char* smem, const Compr
 // Query-side operands of one (sequence, layer, kv-head): this warp's B fragments.
 struct M2Query {
     uint32_t q1[16][2];  // q~ * c   (ternary part), per k-step
-    uint32_t q2[16][2];  // q~       (residual part)
+    uint32_t q2[16 - M2_Q2_SMEM_STEPS][2];  // q~ (residual part), the last k-steps; the first ones sit in shared memory
 };
 
 // q: (H_q, ..) with `q_head_stride` halfs between heads.  scratch: this warp's NREP*D floats.
@@ -209,7 +211,8 @@ __device__ __forceinline__ void m2_build_query(M2Query& Q, const __half* __restr
                                                const CompressedKV& P, int kvh, int lane, float* scratch,
                                                uint2* qlo /* this kv-head's [16][32] low-order q1 fragments; the
                                                              q2 ones sit HKV*16*32 entries further */,
-                                               uint2* qr_s /* this kv-head's [4][32] raw rotary query fragments */) {
+                                               uint2* qr_s /* this kv-head's [4][32] raw rotary query fragments */,
+                                               uint2* q2_s /* this kv-head's [M2_Q2_SMEM_STEPS][32] q2 fragments */) {
     const int g = lane >> 2, t = lane & 3;
     // q~ in the lane-owns-8-dims layout: q~ = R^T H256 (q * dinv * [dim >= 64]).  This runs once per work
     // item on the critical path, so every global load is issued before the first one is needed: the
@@ -278,10 +281,16 @@ __device__ __forceinline__ void m2_build_query(M2Query& Q, const __half* __restr
         m2_pack_hilo(v[0] * c[0], v[1] * c[1], Q.q1[s][0], lo.x);
         m2_pack_hilo(v[2] * c[2], v[3] * c[3], Q.q1[s][1], lo.y);
         qlo[s * 32 + lane] = lo;  // both warps of a kv-head write the same values
-        uint2 lo2;
-        m2_pack_hilo(v[0], v[1], Q.q2[s][0], lo2.x);
-        m2_pack_hilo(v[2], v[3], Q.q2[s][1], lo2.y);
+        uint2 lo2, hi2;
+        m2_pack_hilo(v[0], v[1], hi2.x, lo2.x);
+        m2_pack_hilo(v[2], v[3], hi2.y, lo2.y);
         qlo[HKV * 16 * 32 + s * 32 + lane] = lo2;
+        if (s < M2_Q2_SMEM_STEPS) {
+            q2_s[s * 32 + lane] = hi2;
+        } else {
+            Q.q2[s - M2_Q2_SMEM_STEPS][0] = hi2.x;
+            Q.q2[s - M2_Q2_SMEM_STEPS][1] = hi2.y;
+        }
     }
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) qr_s[kk * 32 + lane] = make_uint2(qrw[kk][0], qrw[kk][1]);  // both warps of a kv-head write the same values
@@ -315,6 +324,7 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
     const unsigned char* vqb = smem + M2_SM_VQB;
     const float2* c3s = reinterpret_cast<const float2*>(smem + M2_SM_C3) + 8 * g;
     const uint2* qr_s = reinterpret_cast<const uint2*>(smem + M2_SM_QR) + kvh * 4 * 32;
+    const uint2* q2_s = reinterpret_cast<const uint2*>(smem + M2_SM_Q2) + kvh * M2_Q2_SMEM_STEPS * 32;
 
     // ================================ K side: scores ==========================================
     const uint32_t* kp[2];
@@ -379,7 +389,10 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
             const uint2 ql = qlo[s * 32 + lane], ql2 = qlo[HKV * 16 * 32 + s * 32 + lane];
             m2_mma(cs, a1, Q.q1[s][0], Q.q1[s][1]);
             m2_mma_lo(cs, a1, ql.x, ql.y);  // low-order halves of the query operands: the code operands are exact
-            m2_mma(cs2, ax, Q.q2[s][0], Q.q2[s][1]);
+            uint2 q2h;
+            if (s < M2_Q2_SMEM_STEPS) q2h = q2_s[s * 32 + lane];
+            else q2h = make_uint2(Q.q2[s < M2_Q2_SMEM_STEPS ? 0 : s - M2_Q2_SMEM_STEPS][0], Q.q2[s < M2_Q2_SMEM_STEPS ? 0 : s - M2_Q2_SMEM_STEPS][1]);
+            m2_mma(cs2, ax, q2h.x, q2h.y);
             m2_mma_lo(cs2, ax, ql2.x, ql2.y);
             m2_mma(cu[s >> 1], a1, b1.x, b1.y);
             m2_mma_lo(cu[s >> 1], a1, b1l.x, b1l.y);
@@ -598,7 +611,8 @@ __device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const _
     M2Query Q;
     m2_build_query(Q, q, q_head_stride, P, kvh, lane, reinterpret_cast<float*>(smem + M2_SM_STAGES) + warp * NREP * D,
                    reinterpret_cast<uint2*>(smem + M2_SM_QLO) + kvh * 16 * 32,
-                   reinterpret_cast<uint2*>(smem + M2_SM_QR) + kvh * 4 * 32);
+                   reinterpret_cast<uint2*>(smem + M2_SM_QR) + kvh * 4 * 32,
+                   reinterpret_cast<uint2*>(smem + M2_SM_Q2) + kvh * M2_Q2_SMEM_STEPS * 32);
     __syncthreads();  // the query scratch aliases the stages
 
     const int base = my_lo & ~1;
@@ -620,13 +634,16 @@ __device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const _
             const int tok0 = base + (i + 1) * M2_TT;
             m2_stage_tile(P, smem + M2_SM_STAGES + ((gi + 1) % M2_NSTAGE) * M2_STAGE_BYTES, &bars[(gi + 1) % M2_NSTAGE],
                           tok0, min(M2_TT, P.c_len - tok0), tid);
-            m2_fill_rope(rope_tab + ((i + 1) & 1) * M2_TT * 32, freq_s, P, tok0, tid);
+        }
+        if (i > 0) {  // one RoPE table: tile i - 1 was finished with it at the barrier that ended its iteration
+            m2_fill_rope(rope_tab, freq_s, P, base + i * M2_TT, tid);
+            __syncthreads();
         }
         mbar_wait_bounded(&bars[stg], (uint32_t)((gi / M2_NSTAGE) & 1), &g_status);
         const int blk0 = base + i * M2_TT + 16 * sub;
         const int vlo = max(my_lo - blk0, 0), vhi = min(my_hi - blk0, 16);
         if (vhi > vlo)
-            m2_block(smem + M2_SM_STAGES + stg * M2_STAGE_BYTES, smem, rope_tab + (i & 1) * M2_TT * 32, 16 * sub, kvh,
+            m2_block(smem + M2_SM_STAGES + stg * M2_STAGE_BYTES, smem, rope_tab, 16 * sub, kvh,
                      lane, vlo, vhi, Q, P, scale, st);
         __syncthreads();  // stage and rope buffer free for the tile after next
     }
