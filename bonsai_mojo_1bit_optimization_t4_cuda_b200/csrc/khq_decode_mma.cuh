@@ -49,8 +49,8 @@ constexpr int M2_VQA_STRIDE = 65;                                    // words pe
 constexpr int M2_VQB_STRIDE = 130;                                   // bytes per code row
 constexpr int M2_SM_VQ = M2_SM_STAGES + M2_NSTAGE * M2_STAGE_BYTES;  // (d0, d1): 256 x 65 x 4 B
 constexpr int M2_SM_VQB = M2_SM_VQ + 256 * M2_VQA_STRIDE * 4;        // d2: 256 x 130 B
-constexpr int M2_SM_ROPE = M2_SM_VQB + 256 * M2_VQB_STRIDE;          // 32 tokens x 32 float2
-constexpr int M2_SM_BROT = M2_SM_ROPE + M2_TT * 32 * 8;          // 4 kinds x 16 steps x 32 lanes x 8 B
+constexpr int M2_SM_ROPE = M2_SM_VQB + 256 * M2_VQB_STRIDE;          // 2 x 32 tokens x 32 float2
+constexpr int M2_SM_BROT = M2_SM_ROPE + 2 * M2_TT * 32 * 8;          // 4 kinds x 16 steps x 32 lanes x 8 B
 constexpr int M2_SM_LUT = M2_SM_BROT + 4 * 16 * 32 * 8;              // scatter table
 constexpr int M2_SM_FREQ = M2_SM_LUT + 448;
 constexpr int M2_SM_DINV = M2_SM_FREQ + 128;                         // 64 floats
@@ -58,9 +58,13 @@ constexpr int M2_SM_BARS = M2_SM_DINV + 256;
 constexpr int M2_SM_QLO = M2_SM_BARS + 64;                           // 2 kinds x 4 kv-heads x 16 steps x 32 lanes x 8 B
 constexpr int M2_SM_C3 = M2_SM_QLO + 2 * HKV * 16 * 32 * 8;              // 64 patches x float2: dim-3 centroids x alpha_v
 constexpr int M2_SM_QR = M2_SM_C3 + NP * 8;                             // raw rotary query fragments: 4 kv-heads x 4 k-steps x 32 lanes x 8 B
-constexpr int M2_Q2_SMEM_STEPS = 12;                                     // k-steps whose residual-part query fragments live in shared memory
-constexpr int M2_SM_Q2 = M2_SM_QR + HKV * 4 * 32 * 8;                    // 4 kv-heads x M2_Q2_SMEM_STEPS x 32 lanes x 8 B
-constexpr int M2_SM_TOTAL = M2_SM_Q2 + HKV * M2_Q2_SMEM_STEPS * 32 * 8;
+constexpr int M2_SM_TOTAL = M2_SM_QR + HKV * 4 * 32 * 8;
+// Tensor memory as a second register file: the 64 query-side B fragments of a warp (ternary part q1 and residual
+// part q2, two registers each per k-step) are the same for a whole work item.  Held in registers they took 64 of
+// the 255 across the tile loop; they are written to tensor memory once per item (tcgen05.st) and fetched one
+// k-step ahead of use (tcgen05.ld).  Warp w owns lanes 32 (w & 3) .. +31, columns 64 (w >> 2) .. +63
+// (four per k-step: q1[0], q1[1], q2[0], q2[1]).
+constexpr uint32_t M2_TM_COLS = 128;
 static_assert(M2_SM_TOTAL <= 227 * 1024 && M2_SM_QLO % 16 == 0 && M2_SM_ROPE % 16 == 0 && M2_SM_VQB % 16 == 0,
               "shared memory budget");
 static_assert(HKV * MERGE_FLOATS * 4 <= 256 * M2_VQA_STRIDE * 4, "cluster export records alias the codebook");
@@ -202,17 +206,43 @@ __device__ __forceinline__ void m2_setup_tables(unsigned char* smem, const Compr
 
 // Query-side operands of one (sequence, layer, kv-head): this warp's B fragments.
 struct M2Query {
-    uint32_t q1[16][2];  // q~ * c   (ternary part), per k-step
-    uint32_t q2[16 - M2_Q2_SMEM_STEPS][2];  // q~ (residual part), the last k-steps; the first ones sit in shared memory
+    uint32_t tm;  // tensor-memory address of this warp's 64 columns
 };
+
+__device__ __forceinline__ void m2_tm_st4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%4], {%0,%1,%2,%3};" ::"r"(a), "r"(b), "r"(c), "r"(d), "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void m2_tm_ld4(uint32_t taddr, uint32_t (&r)[4]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void m2_tm_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void m2_tm_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// Allocation by warp 0 of a CTA (one CTA per SM by shared memory, so the columns are always free); the address goes
+// through `slot` in shared memory.  Followed by a CTA barrier by the caller.
+__device__ __forceinline__ void m2_tm_alloc(uint32_t* slot, int warp) {
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "n"(M2_TM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+// After a CTA barrier behind the last use.
+__device__ __forceinline__ void m2_tm_free(uint32_t tmem, int warp) {
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(M2_TM_COLS) : "memory");
+    }
+}
 
 // q: (H_q, ..) with `q_head_stride` halfs between heads.  scratch: this warp's NREP*D floats.
 __device__ __forceinline__ void m2_build_query(M2Query& Q, const __half* __restrict__ q, size_t q_head_stride,
                                                const CompressedKV& P, int kvh, int lane, float* scratch,
                                                uint2* qlo /* this kv-head's [16][32] low-order q1 fragments; the
                                                              q2 ones sit HKV*16*32 entries further */,
-                                               uint2* qr_s /* this kv-head's [4][32] raw rotary query fragments */,
-                                               uint2* q2_s /* this kv-head's [M2_Q2_SMEM_STEPS][32] q2 fragments */) {
+                                               uint2* qr_s /* this kv-head's [4][32] raw rotary query fragments */) {
     const int g = lane >> 2, t = lane & 3;
     // q~ in the lane-owns-8-dims layout: q~ = R^T H256 (q * dinv * [dim >= 64]).  This runs once per work
     // item on the critical path, so every global load is issued before the first one is needed: the
@@ -277,21 +307,17 @@ __device__ __forceinline__ void m2_build_query(M2Query& Q, const __half* __restr
             v[0] = qq.x; v[1] = qq.z; v[2] = qq.y; v[3] = qq.w;  // dims d0 + {0, 2, 1, 3}
             c[0] = __half2float(hc[0]); c[1] = __half2float(hc[2]); c[2] = __half2float(hc[1]); c[3] = __half2float(hc[3]);
         }
-        uint2 lo;
-        m2_pack_hilo(v[0] * c[0], v[1] * c[1], Q.q1[s][0], lo.x);
-        m2_pack_hilo(v[2] * c[2], v[3] * c[3], Q.q1[s][1], lo.y);
+        uint2 lo, hi;
+        m2_pack_hilo(v[0] * c[0], v[1] * c[1], hi.x, lo.x);
+        m2_pack_hilo(v[2] * c[2], v[3] * c[3], hi.y, lo.y);
         qlo[s * 32 + lane] = lo;  // both warps of a kv-head write the same values
         uint2 lo2, hi2;
         m2_pack_hilo(v[0], v[1], hi2.x, lo2.x);
         m2_pack_hilo(v[2], v[3], hi2.y, lo2.y);
         qlo[HKV * 16 * 32 + s * 32 + lane] = lo2;
-        if (s < M2_Q2_SMEM_STEPS) {
-            q2_s[s * 32 + lane] = hi2;
-        } else {
-            Q.q2[s - M2_Q2_SMEM_STEPS][0] = hi2.x;
-            Q.q2[s - M2_Q2_SMEM_STEPS][1] = hi2.y;
-        }
+        m2_tm_st4(Q.tm + 4 * s, hi.x, hi.y, hi2.x, hi2.y);
     }
+    m2_tm_st_wait();
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) qr_s[kk * 32 + lane] = make_uint2(qrw[kk][0], qrw[kk][1]);  // both warps of a kv-head write the same values
     __syncwarp();
@@ -324,7 +350,6 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
     const unsigned char* vqb = smem + M2_SM_VQB;
     const float2* c3s = reinterpret_cast<const float2*>(smem + M2_SM_C3) + 8 * g;
     const uint2* qr_s = reinterpret_cast<const uint2*>(smem + M2_SM_QR) + kvh * 4 * 32;
-    const uint2* q2_s = reinterpret_cast<const uint2*>(smem + M2_SM_Q2) + kvh * M2_Q2_SMEM_STEPS * 32;
 
     // ================================ K side: scores ==========================================
     const uint32_t* kp[2];
@@ -366,6 +391,8 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
     float cu[8][4];                          // rotor block sums u[token, 8j + n]
 #pragma unroll
     for (int j = 0; j < 8; ++j) cu[j][0] = cu[j][1] = cu[j][2] = cu[j][3] = 0.0f;
+    uint32_t qf[2][4];  // this and the next k-step's query fragments: q1[0], q1[1], q2[0], q2[1]
+    m2_tm_ld4(Q.tm, qf[0]);
 #pragma unroll
     for (int wi = 0; wi < 4; ++wi) {
         const uint32_t wa = wi == 0 ? mw[0].x : wi == 1 ? mw[0].y : wi == 2 ? mw[0].z : mw[0].w;
@@ -387,12 +414,11 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
             const uint2 b1 = brot[s * 32 + lane], b2 = brot[512 + s * 32 + lane], b1l = brot[1024 + s * 32 + lane],
                         b2l = brot[1536 + s * 32 + lane];
             const uint2 ql = qlo[s * 32 + lane], ql2 = qlo[HKV * 16 * 32 + s * 32 + lane];
-            m2_mma(cs, a1, Q.q1[s][0], Q.q1[s][1]);
+            m2_tm_ld_wait();
+            if (s + 1 < 16) m2_tm_ld4(Q.tm + 4 * (s + 1), qf[(s + 1) & 1]);
+            m2_mma(cs, a1, qf[s & 1][0], qf[s & 1][1]);
             m2_mma_lo(cs, a1, ql.x, ql.y);  // low-order halves of the query operands: the code operands are exact
-            uint2 q2h;
-            if (s < M2_Q2_SMEM_STEPS) q2h = q2_s[s * 32 + lane];
-            else q2h = make_uint2(Q.q2[s < M2_Q2_SMEM_STEPS ? 0 : s - M2_Q2_SMEM_STEPS][0], Q.q2[s < M2_Q2_SMEM_STEPS ? 0 : s - M2_Q2_SMEM_STEPS][1]);
-            m2_mma(cs2, ax, q2h.x, q2h.y);
+            m2_mma(cs2, ax, qf[s & 1][2], qf[s & 1][3]);
             m2_mma_lo(cs2, ax, ql2.x, ql2.y);
             m2_mma(cu[s >> 1], a1, b1.x, b1.y);
             m2_mma_lo(cu[s >> 1], a1, b1l.x, b1l.y);
@@ -601,7 +627,7 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
 template <bool ALL_WARPS_MERGE = false>  // true: warps 4..7 also return the merged state of kv-head warp - 4
 __device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const __half* __restrict__ q,
                                                     size_t q_head_stride, const CompressedKV& P, int my_lo, int my_hi,
-                                                    float scale, unsigned& tiles_done, WarpState& ws) {
+                                                    float scale, unsigned& tiles_done, WarpState& ws, uint32_t tmem) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kvh = warp & 3, sub = warp >> 2, g = lane >> 2, t = lane & 3;
     float2* rope_tab = reinterpret_cast<float2*>(smem + M2_SM_ROPE);
@@ -609,10 +635,10 @@ __device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const _
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + M2_SM_BARS);
 
     M2Query Q;
+    Q.tm = tmem + ((uint32_t)(32 * kvh) << 16) + 64u * (uint32_t)sub;
     m2_build_query(Q, q, q_head_stride, P, kvh, lane, reinterpret_cast<float*>(smem + M2_SM_STAGES) + warp * NREP * D,
                    reinterpret_cast<uint2*>(smem + M2_SM_QLO) + kvh * 16 * 32,
-                   reinterpret_cast<uint2*>(smem + M2_SM_QR) + kvh * 4 * 32,
-                   reinterpret_cast<uint2*>(smem + M2_SM_Q2) + kvh * M2_Q2_SMEM_STEPS * 32);
+                   reinterpret_cast<uint2*>(smem + M2_SM_QR) + kvh * 4 * 32);
     __syncthreads();  // the query scratch aliases the stages
 
     const int base = my_lo & ~1;
@@ -634,16 +660,13 @@ __device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const _
             const int tok0 = base + (i + 1) * M2_TT;
             m2_stage_tile(P, smem + M2_SM_STAGES + ((gi + 1) % M2_NSTAGE) * M2_STAGE_BYTES, &bars[(gi + 1) % M2_NSTAGE],
                           tok0, min(M2_TT, P.c_len - tok0), tid);
-        }
-        if (i > 0) {  // one RoPE table: tile i - 1 was finished with it at the barrier that ended its iteration
-            m2_fill_rope(rope_tab, freq_s, P, base + i * M2_TT, tid);
-            __syncthreads();
+            m2_fill_rope(rope_tab + ((i + 1) & 1) * M2_TT * 32, freq_s, P, tok0, tid);
         }
         mbar_wait_bounded(&bars[stg], (uint32_t)((gi / M2_NSTAGE) & 1), &g_status);
         const int blk0 = base + i * M2_TT + 16 * sub;
         const int vlo = max(my_lo - blk0, 0), vhi = min(my_hi - blk0, 16);
         if (vhi > vlo)
-            m2_block(smem + M2_SM_STAGES + stg * M2_STAGE_BYTES, smem, rope_tab, 16 * sub, kvh,
+            m2_block(smem + M2_SM_STAGES + stg * M2_STAGE_BYTES, smem, rope_tab + (i & 1) * M2_TT * 32, 16 * sub, kvh,
                      lane, vlo, vhi, Q, P, scale, st);
         __syncthreads();  // stage and rope buffer free for the tile after next
     }
@@ -692,10 +715,15 @@ khq_decode_batched_mma_kernel(const KhqSeqDesc* __restrict__ descs, const KhqTab
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kvh = warp & 3, sub = warp >> 2;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + M2_SM_BARS);
+    uint32_t* tm_slot = reinterpret_cast<uint32_t*>(smem + M2_SM_BARS + 32);
     if (tid == 0) {
         for (int s = 0; s < M2_NSTAGE; ++s) mbar_init(&bars[s], 1);
         fence_barrier_init();
     }
+    m2_tm_alloc(tm_slot, warp);
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tm_slot;
     int cur_table = -1;
     unsigned tiles_done = 0;
 #pragma unroll 1
@@ -727,7 +755,7 @@ khq_decode_batched_mma_kernel(const KhqSeqDesc* __restrict__ descs, const KhqTab
                 __syncthreads();
             }
             WarpState ws;
-            m2_compressed_range<true>(smem, d.q_gate, (size_t)2 * D, P, w.lo, w.hi, scale, tiles_done, ws);
+            m2_compressed_range<true>(smem, d.q_gate, (size_t)2 * D, P, w.lo, w.hi, scale, tiles_done, ws, tmem);
             // the two warps of a kv-head transform and store three heads each
             if (sub == 0) v_epilogue_store<0, NREP / 2>(ws, P, lane, ob);
             else v_epilogue_store<NREP / 2, NREP>(ws, P, lane, ob);
@@ -744,6 +772,9 @@ khq_decode_batched_mma_kernel(const KhqSeqDesc* __restrict__ descs, const KhqTab
             }
         }
     }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    m2_tm_free(tmem, warp);
 }
 
 // Drop-in (single sequence-layer) variant: grid = num_splits * cluster_size CTAs; the CTAs of a
@@ -768,15 +799,23 @@ khq_attn_compressed_mma_kernel(const __half* __restrict__ q, CompressedKV P, flo
     const int chunk = (((len + csize - 1) / csize) + 1) & ~1;
     const int my_lo = min(s_lo + crank * chunk, s_hi);
     const int my_hi = min(my_lo + chunk, s_hi);
+    uint32_t* tm_slot = reinterpret_cast<uint32_t*>(smem + M2_SM_BARS + 32);
     if (tid == 0) {
         for (int s = 0; s < M2_NSTAGE; ++s) mbar_init(&bars[s], 1);
         fence_barrier_init();
     }
+    m2_tm_alloc(tm_slot, warp);
     m2_setup_tables(smem, P, tid);
     __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tm_slot;
     unsigned tiles_done = 0;
     WarpState ws;
-    m2_compressed_range(smem, q + (size_t)l_idx * 2 * D, (size_t)L_q * 2 * D, P, my_lo, my_hi, scale, tiles_done, ws);
+    m2_compressed_range(smem, q + (size_t)l_idx * 2 * D, (size_t)L_q * 2 * D, P, my_lo, my_hi, scale, tiles_done, ws, tmem);
+    // the query fragments are not needed any more; everything below is ordinary memory
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    m2_tm_free(tmem, warp);
     // cluster merge: records exported over the (no longer needed) codebook area
     float* exp_rec = reinterpret_cast<float*>(smem + M2_SM_VQ) + (warp & 3) * MERGE_FLOATS;
     if (csize > 1) {
