@@ -55,17 +55,20 @@ constexpr int M2_SM_LUT = M2_SM_BROT + 4 * 16 * 32 * 8;              // scatter 
 constexpr int M2_SM_FREQ = M2_SM_LUT + 448;
 constexpr int M2_SM_DINV = M2_SM_FREQ + 128;                         // 64 floats
 constexpr int M2_SM_BARS = M2_SM_DINV + 256;
-constexpr int M2_SM_QLO = M2_SM_BARS + 64;                           // 2 kinds x 4 kv-heads x 16 steps x 32 lanes x 8 B
-constexpr int M2_SM_C3 = M2_SM_QLO + 2 * HKV * 16 * 32 * 8;              // 64 patches x float2: dim-3 centroids x alpha_v
+constexpr int M2_SM_C3 = M2_SM_BARS + 64;              // 64 patches x float2: dim-3 centroids x alpha_v
 constexpr int M2_SM_QR = M2_SM_C3 + NP * 8;                             // raw rotary query fragments: 4 kv-heads x 4 k-steps x 32 lanes x 8 B
 constexpr int M2_SM_TOTAL = M2_SM_QR + HKV * 4 * 32 * 8;
-// Tensor memory as a second register file: the 64 query-side B fragments of a warp (ternary part q1 and residual
-// part q2, two registers each per k-step) are the same for a whole work item.  Held in registers they took 64 of
-// the 255 across the tile loop; they are written to tensor memory once per item (tcgen05.st) and fetched one
-// k-step ahead of use (tcgen05.ld).  Warp w owns lanes 32 (w & 3) .. +31, columns 64 (w >> 2) .. +63
-// (four per k-step: q1[0], q1[1], q2[0], q2[1]).
-constexpr uint32_t M2_TM_COLS = 128;
-static_assert(M2_SM_TOTAL <= 227 * 1024 && M2_SM_QLO % 16 == 0 && M2_SM_ROPE % 16 == 0 && M2_SM_VQB % 16 == 0,
+// Tensor memory as a second register file.  The B fragments of the K side are per-lane constants: the query
+// side (ternary part q1 and residual part q2, fp16 hi and lo, eight registers per k-step) for a whole work
+// item, the rotor side (rotor x centroid and rotor, hi and lo, eight registers per k-step) for a whole layer.
+// Held in registers the hi query fragments alone took 64 of the 255 across the tile loop, and the rest came
+// from shared memory with six loads per k-step.  They are written to tensor memory (tcgen05.st: the query side
+// once per item, the rotor side once per layer) and fetched one k-step ahead of use with two tcgen05.ld.
+// Warp w owns lanes 32 (w & 3) .. +31.  Columns: 128 (w >> 2) .. +127 = the warp's query fragments (eight per
+// k-step: q1.x, q1.y, q2.x, q2.y and their low-order halves), 256 .. 383 = the rotor fragments of the lane quadrant
+// (eight per k-step: b1.x, b1.y, b2.x, b2.y and their low-order halves; the same values in all four quadrants).
+constexpr uint32_t M2_TM_COLS = 512, M2_TM_ROT = 256;
+static_assert(M2_SM_TOTAL <= 227 * 1024 && M2_SM_C3 % 16 == 0 && M2_SM_ROPE % 16 == 0 && M2_SM_VQB % 16 == 0,
               "shared memory budget");
 static_assert(HKV * MERGE_FLOATS * 4 <= 256 * M2_VQA_STRIDE * 4, "cluster export records alias the codebook");
 static_assert(8 * MERGE_FLOATS * 4 <= M2_NSTAGE * M2_STAGE_BYTES, "records alias the stages");
@@ -206,7 +209,8 @@ __device__ __forceinline__ void m2_setup_tables(unsigned char* smem, const Compr
 
 // Query-side operands of one (sequence, layer, kv-head): this warp's B fragments.
 struct M2Query {
-    uint32_t tm;  // tensor-memory address of this warp's 64 columns
+    uint32_t tm;   // tensor-memory address of this warp's query fragments
+    uint32_t rot;  // ... and of its lane quadrant's rotor fragments
 };
 
 __device__ __forceinline__ void m2_tm_st4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
@@ -215,6 +219,18 @@ __device__ __forceinline__ void m2_tm_st4(uint32_t taddr, uint32_t a, uint32_t b
 __device__ __forceinline__ void m2_tm_ld4(uint32_t taddr, uint32_t (&r)[4]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void m2_tm_st8(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t e, uint32_t f,
+                                          uint32_t g, uint32_t h) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%8], {%0,%1,%2,%3,%4,%5,%6,%7};" ::"r"(a), "r"(b), "r"(c), "r"(d), "r"(e),
+                 "r"(f), "r"(g), "r"(h), "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void m2_tm_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                  : "r"(taddr)
                  : "memory");
 }
@@ -237,11 +253,27 @@ __device__ __forceinline__ void m2_tm_free(uint32_t tmem, int warp) {
     }
 }
 
+// The layer's rotor fragments from their shared-memory staging table into the tensor memory of every lane
+// quadrant (warps 0..3, one quadrant each).  After the CTA barrier that follows m2_setup_tables; the readers
+// pass another CTA barrier and a tcgen05 fence before their first load.
+__device__ __forceinline__ void m2_rotor_to_tmem(const unsigned char* smem, uint32_t tmem, int warp, int lane) {
+    if (warp < 4) {
+        const uint2* brot = reinterpret_cast<const uint2*>(smem + M2_SM_BROT);
+        const uint32_t dst = tmem + ((uint32_t)(32 * warp) << 16) + M2_TM_ROT;
+#pragma unroll 4
+        for (int s = 0; s < 16; ++s) {
+            const uint2 b1 = brot[s * 32 + lane], b2 = brot[512 + s * 32 + lane], b1l = brot[1024 + s * 32 + lane],
+                        b2l = brot[1536 + s * 32 + lane];
+            m2_tm_st8(dst + 8 * s, b1.x, b1.y, b2.x, b2.y, b1l.x, b1l.y, b2l.x, b2l.y);
+        }
+        m2_tm_st_wait();
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+
 // q: (H_q, ..) with `q_head_stride` halfs between heads.  scratch: this warp's NREP*D floats.
 __device__ __forceinline__ void m2_build_query(M2Query& Q, const __half* __restrict__ q, size_t q_head_stride,
                                                const CompressedKV& P, int kvh, int lane, float* scratch,
-                                               uint2* qlo /* this kv-head's [16][32] low-order q1 fragments; the
-                                                             q2 ones sit HKV*16*32 entries further */,
                                                uint2* qr_s /* this kv-head's [4][32] raw rotary query fragments */) {
     const int g = lane >> 2, t = lane & 3;
     // q~ in the lane-owns-8-dims layout: q~ = R^T H256 (q * dinv * [dim >= 64]).  This runs once per work
@@ -310,12 +342,10 @@ __device__ __forceinline__ void m2_build_query(M2Query& Q, const __half* __restr
         uint2 lo, hi;
         m2_pack_hilo(v[0] * c[0], v[1] * c[1], hi.x, lo.x);
         m2_pack_hilo(v[2] * c[2], v[3] * c[3], hi.y, lo.y);
-        qlo[s * 32 + lane] = lo;  // both warps of a kv-head write the same values
         uint2 lo2, hi2;
         m2_pack_hilo(v[0], v[1], hi2.x, lo2.x);
         m2_pack_hilo(v[2], v[3], hi2.y, lo2.y);
-        qlo[HKV * 16 * 32 + s * 32 + lane] = lo2;
-        m2_tm_st4(Q.tm + 4 * s, hi.x, hi.y, hi2.x, hi2.y);
+        m2_tm_st8(Q.tm + 8 * s, hi.x, hi.y, hi2.x, hi2.y, lo.x, lo.y, lo2.x, lo2.y);
     }
     m2_tm_st_wait();
 #pragma unroll
@@ -343,8 +373,6 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
                                          M2State& st) {
     const int g = lane >> 2, t = lane & 3;
     const KdLutEntry* lut = reinterpret_cast<const KdLutEntry*>(smem + M2_SM_LUT);
-    const uint2* brot = reinterpret_cast<const uint2*>(smem + M2_SM_BROT);
-    const uint2* qlo = reinterpret_cast<const uint2*>(smem + M2_SM_QLO) + kvh * 16 * 32;
     const float* dinv_s = reinterpret_cast<const float*>(smem + M2_SM_DINV);
     const unsigned char* vqa = smem + M2_SM_VQ;
     const unsigned char* vqb = smem + M2_SM_VQB;
@@ -391,8 +419,9 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
     float cu[8][4];                          // rotor block sums u[token, 8j + n]
 #pragma unroll
     for (int j = 0; j < 8; ++j) cu[j][0] = cu[j][1] = cu[j][2] = cu[j][3] = 0.0f;
-    uint32_t qf[2][4];  // this and the next k-step's query fragments: q1[0], q1[1], q2[0], q2[1]
-    m2_tm_ld4(Q.tm, qf[0]);
+    uint32_t qf[2][8], rf[2][8];  // this and the next k-step's query and rotor fragments
+    m2_tm_ld8(Q.tm, qf[0]);
+    m2_tm_ld8(Q.rot, rf[0]);
 #pragma unroll
     for (int wi = 0; wi < 4; ++wi) {
         const uint32_t wa = wi == 0 ? mw[0].x : wi == 1 ? mw[0].y : wi == 2 ? mw[0].z : mw[0].w;
@@ -411,20 +440,22 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
                                     m2_hmul2(ax[2], ratio_hi[0]), m2_hmul2(ax[3], ratio_hi[1])};
             const uint32_t a3[4] = {m2_hmul2(ax[0], ratio_lo[0]), m2_hmul2(ax[1], ratio_lo[1]),
                                     m2_hmul2(ax[2], ratio_lo[0]), m2_hmul2(ax[3], ratio_lo[1])};
-            const uint2 b1 = brot[s * 32 + lane], b2 = brot[512 + s * 32 + lane], b1l = brot[1024 + s * 32 + lane],
-                        b2l = brot[1536 + s * 32 + lane];
-            const uint2 ql = qlo[s * 32 + lane], ql2 = qlo[HKV * 16 * 32 + s * 32 + lane];
             m2_tm_ld_wait();
-            if (s + 1 < 16) m2_tm_ld4(Q.tm + 4 * (s + 1), qf[(s + 1) & 1]);
-            m2_mma(cs, a1, qf[s & 1][0], qf[s & 1][1]);
-            m2_mma_lo(cs, a1, ql.x, ql.y);  // low-order halves of the query operands: the code operands are exact
-            m2_mma(cs2, ax, qf[s & 1][2], qf[s & 1][3]);
-            m2_mma_lo(cs2, ax, ql2.x, ql2.y);
-            m2_mma(cu[s >> 1], a1, b1.x, b1.y);
-            m2_mma_lo(cu[s >> 1], a1, b1l.x, b1l.y);
-            m2_mma(cu[s >> 1], a2, b2.x, b2.y);
-            m2_mma_lo(cu[s >> 1], a2, b2l.x, b2l.y);
-            m2_mma_lo(cu[s >> 1], a3, b2.x, b2.y);
+            if (s + 1 < 16) {
+                m2_tm_ld8(Q.tm + 8 * (s + 1), qf[(s + 1) & 1]);
+                m2_tm_ld8(Q.rot + 8 * (s + 1), rf[(s + 1) & 1]);
+            }
+            const uint32_t(&qq)[8] = qf[s & 1];  // q1.x, q1.y, q2.x, q2.y, then their low-order halves
+            const uint32_t(&rr)[8] = rf[s & 1];  // b1.x, b1.y, b2.x, b2.y, then their low-order halves
+            m2_mma(cs, a1, qq[0], qq[1]);
+            m2_mma_lo(cs, a1, qq[4], qq[5]);  // low-order halves of the query operands: the code operands are exact
+            m2_mma(cs2, ax, qq[2], qq[3]);
+            m2_mma_lo(cs2, ax, qq[6], qq[7]);
+            m2_mma(cu[s >> 1], a1, rr[0], rr[1]);
+            m2_mma_lo(cu[s >> 1], a1, rr[4], rr[5]);
+            m2_mma(cu[s >> 1], a2, rr[2], rr[3]);
+            m2_mma_lo(cu[s >> 1], a2, rr[6], rr[7]);
+            m2_mma_lo(cu[s >> 1], a3, rr[2], rr[3]);
         }
         wbase[0] += kd_count(kwa);
         wbase[1] += kd_count(kwb);
@@ -635,11 +666,12 @@ __device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const _
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + M2_SM_BARS);
 
     M2Query Q;
-    Q.tm = tmem + ((uint32_t)(32 * kvh) << 16) + 64u * (uint32_t)sub;
+    Q.tm = tmem + ((uint32_t)(32 * kvh) << 16) + 128u * (uint32_t)sub;
+    Q.rot = tmem + ((uint32_t)(32 * kvh) << 16) + M2_TM_ROT;
     m2_build_query(Q, q, q_head_stride, P, kvh, lane, reinterpret_cast<float*>(smem + M2_SM_STAGES) + warp * NREP * D,
-                   reinterpret_cast<uint2*>(smem + M2_SM_QLO) + kvh * 16 * 32,
                    reinterpret_cast<uint2*>(smem + M2_SM_QR) + kvh * 4 * 32);
     __syncthreads();  // the query scratch aliases the stages
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");  // the rotor fragments other warps stored
 
     const int base = my_lo & ~1;
     const int ntiles = (my_hi > my_lo) ? (my_hi - base + M2_TT - 1) / M2_TT : 0;
@@ -753,6 +785,7 @@ khq_decode_batched_mma_kernel(const KhqSeqDesc* __restrict__ descs, const KhqTab
                 m2_setup_tables(smem, P, tid);
                 cur_table = d.table_id;
                 __syncthreads();
+                m2_rotor_to_tmem(smem, tmem, warp, lane);
             }
             WarpState ws;
             m2_compressed_range<true>(smem, d.q_gate, (size_t)2 * D, P, w.lo, w.hi, scale, tiles_done, ws, tmem);
@@ -809,6 +842,7 @@ khq_attn_compressed_mma_kernel(const __half* __restrict__ q, CompressedKV P, flo
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tm_slot;
+    m2_rotor_to_tmem(smem, tmem, warp, lane);
     unsigned tiles_done = 0;
     WarpState ws;
     m2_compressed_range(smem, q + (size_t)l_idx * 2 * D, (size_t)L_q * 2 * D, P, my_lo, my_hi, scale, tiles_done, ws, tmem);
