@@ -385,7 +385,7 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
     KdSigns sg[2];
     uint32_t wbase[2];
     float sp[2], sp2[2];
-    uint32_t ratio_hi[2], ratio_lo[2];  // rs/mult as two 7-bit pieces: code (4 bits) * piece is exact in fp16
+    float ratio[2];  // rs / mult of rows g, g + 8: scales the residual part of the rotor sums after their GEMM
 #pragma unroll
     for (int x = 0; x < 2; ++x) {
         const int row = (r0 + g + 8 * x) * HKV + kvh;
@@ -407,16 +407,13 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
         const float kn = hbits2f(reinterpret_cast<const uint16_t*>(S + M2_OFF_KN)[row]);
         sp[x] = P.alpha_k * kn * mult * scale;
         sp2[x] = P.alpha_k * kn * rs * scale;
-        const float ratio = rs / mult;
-        const uint32_t rh = m2_pack(ratio, ratio) & 0xFFF0FFF0u;
-        const float rhf = __half2float(__ushort_as_half((unsigned short)(rh & 0xFFFFu)));
-        ratio_hi[x] = rh;
-        ratio_lo[x] = m2_pack(ratio - rhf, ratio - rhf) & 0xFFF0FFF0u;
+        ratio[x] = rs / mult;
     }
     const uint32_t neg1024 = 0xE400E400u;  // fp16x2 (-1024, -1024)
     float cs[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // pass-part scores, ternary part: rows g (0,1), g+8 (2,3); heads 2t, 2t+1
     float cs2[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // pass-part scores, residual part (exact integer operand)
     float cu[8][4];                          // rotor block sums u[token, 8j + n]
+    float cur[4];                            // their residual part, before the row scale
 #pragma unroll
     for (int j = 0; j < 8; ++j) cu[j][0] = cu[j][1] = cu[j][2] = cu[j][3] = 0.0f;
     uint32_t qf[2][8], rf[2][8];  // this and the next k-step's query and rotor fragments
@@ -435,11 +432,6 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
             const uint32_t a1[4] = {a.t0, b.t0, a.t1, b.t1};
             const uint32_t ax[4] = {m2_hfma2(a.t0, neg1024, a.h0), m2_hfma2(b.t0, neg1024, b.h0),
                                     m2_hfma2(a.t1, neg1024, a.h1), m2_hfma2(b.t1, neg1024, b.h1)};  // sign*code, exact
-            // * rs/mult in two exact pieces: only the rotary GEMM uses them
-            const uint32_t a2[4] = {m2_hmul2(ax[0], ratio_hi[0]), m2_hmul2(ax[1], ratio_hi[1]),
-                                    m2_hmul2(ax[2], ratio_hi[0]), m2_hmul2(ax[3], ratio_hi[1])};
-            const uint32_t a3[4] = {m2_hmul2(ax[0], ratio_lo[0]), m2_hmul2(ax[1], ratio_lo[1]),
-                                    m2_hmul2(ax[2], ratio_lo[0]), m2_hmul2(ax[3], ratio_lo[1])};
             m2_tm_ld_wait();
             if (s + 1 < 16) {
                 m2_tm_ld8(Q.tm + 8 * (s + 1), qf[(s + 1) & 1]);
@@ -453,9 +445,17 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
             m2_mma_lo(cs2, ax, qq[6], qq[7]);
             m2_mma(cu[s >> 1], a1, rr[0], rr[1]);
             m2_mma_lo(cu[s >> 1], a1, rr[4], rr[5]);
-            m2_mma(cu[s >> 1], a2, rr[2], rr[3]);
-            m2_mma_lo(cu[s >> 1], a2, rr[6], rr[7]);
-            m2_mma_lo(cu[s >> 1], a3, rr[2], rr[3]);
+            // residual part of the same rotor sums: exact integer operand first, the row's rs / mult in fp32 after the
+            // two k-steps that feed this tile
+            if ((s & 1) == 0) cur[0] = cur[1] = cur[2] = cur[3] = 0.0f;
+            m2_mma(cur, ax, rr[2], rr[3]);
+            m2_mma_lo(cur, ax, rr[6], rr[7]);
+            if (s & 1) {
+                cu[s >> 1][0] = fmaf(ratio[0], cur[0], cu[s >> 1][0]);
+                cu[s >> 1][1] = fmaf(ratio[0], cur[1], cu[s >> 1][1]);
+                cu[s >> 1][2] = fmaf(ratio[1], cur[2], cu[s >> 1][2]);
+                cu[s >> 1][3] = fmaf(ratio[1], cur[3], cu[s >> 1][3]);
+            }
         }
         wbase[0] += kd_count(kwa);
         wbase[1] += kd_count(kwb);
