@@ -22,7 +22,7 @@
 // adds up.  V side: thread (g, t) owns patch group g (patches 8g..8g+7) of tokens 2t, 2t+1,
 // 2t+8, 2t+9.
 #pragma once
-#include "khq_kdecode.cuh"
+#include "khq_kdecode3.cuh"
 
 namespace khq {
 
@@ -162,7 +162,6 @@ __device__ __forceinline__ void m2_fill_rope(float2* tab, const float* freq, con
 __device__ __forceinline__ void m2_setup_tables(unsigned char* smem, const CompressedKV& P, int tid) {
     float* freq_s = reinterpret_cast<float*>(smem + M2_SM_FREQ);
     float* dinv_s = reinterpret_cast<float*>(smem + M2_SM_DINV);
-    KdLutEntry* lut = reinterpret_cast<KdLutEntry*>(smem + M2_SM_LUT);
     uint2* brot = reinterpret_cast<uint2*>(smem + M2_SM_BROT);
     unsigned short* vqa = reinterpret_cast<unsigned short*>(smem + M2_SM_VQ);
     unsigned short* vqb = reinterpret_cast<unsigned short*>(smem + M2_SM_VQB);
@@ -171,7 +170,6 @@ __device__ __forceinline__ void m2_setup_tables(unsigned char* smem, const Compr
         reinterpret_cast<float2*>(smem + M2_SM_C3)[tid - 128] = make_float2(__half2float(P.cents_v[0 * D + 4 * (tid - 128) + 3]) * P.alpha_v,
                                                                              __half2float(P.cents_v[1 * D + 4 * (tid - 128) + 3]) * P.alpha_v);
     if (tid < 64) dinv_s[tid] = (1.0f / 256.0f) / (__half2float(P.d_k[tid]) + 1e-8f);
-    if (tid >= 64 && tid < 64 + KD_LUT_ENTRIES) lut[tid - 64] = kd_make_lut_entry((uint32_t)(tid - 64));
     // Rotor B fragments with the three low index bits of the 64-point Hadamard transform folded
     // in: u[8j + n] is produced by step s = 2j + (n >> 2) as rotor output c = n & 3, and
     // H64 = H8 (bits 0..2, inside a tile) x H8 (bits 3..5, across tiles), so column n' of the
@@ -372,7 +370,6 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
                                          int valid_hi, const M2Query& Q, const CompressedKV& P, float scale,
                                          M2State& st) {
     const int g = lane >> 2, t = lane & 3;
-    const KdLutEntry* lut = reinterpret_cast<const KdLutEntry*>(smem + M2_SM_LUT);
     const float* dinv_s = reinterpret_cast<const float*>(smem + M2_SM_DINV);
     const unsigned char* vqa = smem + M2_SM_VQ;
     const unsigned char* vqb = smem + M2_SM_VQB;
@@ -382,7 +379,6 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
     // ================================ K side: scores ==========================================
     const uint32_t* kp[2];
     uint4 mw[2];
-    KdSigns sg[2];
     uint32_t wbase[2];
     float sp[2], sp2[2];
     float ratio[2];  // rs / mult of rows g, g + 8: scales the residual part of the rotor sums after their GEMM
@@ -392,15 +388,13 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
         kp[x] = reinterpret_cast<const uint32_t*>(S + M2_OFF_KPAY + row * K_PAY);
         mw[x] = *reinterpret_cast<const uint4*>(S + M2_OFF_MASK + row * 64 + 16 * t);
         // outliers of this thread's quarter, then the ordinal of its first one (scan over the quad)
-        int cnt = (int)(kd_count(kd_word(mw[x].x)) + kd_count(kd_word(mw[x].y)) + kd_count(kd_word(mw[x].z)) +
-                        kd_count(kd_word(mw[x].w)));
+        int cnt = (int)(khq3::k3_count(mw[x].x) + khq3::k3_count(mw[x].y) + khq3::k3_count(mw[x].z) + khq3::k3_count(mw[x].w));
         int incl = cnt;
         int up = __shfl_up_sync(0xFFFFFFFFu, incl, 1);
         if (t >= 1) incl += up;
         up = __shfl_up_sync(0xFFFFFFFFu, incl, 2);
         if (t >= 2) incl += up;
         wbase[x] = (uint32_t)(incl - cnt);
-        sg[x] = kd_signs(kp[x]);
         float mult = (float)kp[x][0] / 1000.0f;
         if (mult < 0.1f || mult > 10.0f || isnan(mult)) mult = 1.0f;
         const float rs = hbits2f(reinterpret_cast<const uint16_t*>(S + M2_OFF_KRN)[row]);
@@ -423,15 +417,16 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
     for (int wi = 0; wi < 4; ++wi) {
         const uint32_t wa = wi == 0 ? mw[0].x : wi == 1 ? mw[0].y : wi == 2 ? mw[0].z : mw[0].w;
         const uint32_t wb = wi == 0 ? mw[1].x : wi == 1 ? mw[1].y : wi == 2 ? mw[1].z : mw[1].w;
-        const KdWord kwa = kd_word(wa), kwb = kd_word(wb);
+        // a whole mask word (16 dims = this thread's share of four k-steps) of each of the two rows at once
+        uint32_t ta[8], ha[8], tb[8], hb[8];
+        wbase[0] += khq3::k3_word(wa, wbase[0], kp[0], ta, ha);
+        wbase[1] += khq3::k3_word(wb, wbase[1], kp[1], tb, hb);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const int s = wi * 4 + q;
-            const KdStep a = kd_step(kwa, q, wbase[0] + kd_prefix(kwa, q), kp[0], sg[0], lut);
-            const KdStep b = kd_step(kwb, q, wbase[1] + kd_prefix(kwb, q), kp[1], sg[1], lut);
-            const uint32_t a1[4] = {a.t0, b.t0, a.t1, b.t1};
-            const uint32_t ax[4] = {m2_hfma2(a.t0, neg1024, a.h0), m2_hfma2(b.t0, neg1024, b.h0),
-                                    m2_hfma2(a.t1, neg1024, a.h1), m2_hfma2(b.t1, neg1024, b.h1)};  // sign*code, exact
+            const uint32_t a1[4] = {ta[q], tb[q], ta[4 + q], tb[4 + q]};  // dims (4q, 4q + 2) and (4q + 1, 4q + 3) of rows g, g + 8
+            const uint32_t ax[4] = {m2_hfma2(ta[q], neg1024, ha[q]), m2_hfma2(tb[q], neg1024, hb[q]),
+                                    m2_hfma2(ta[4 + q], neg1024, ha[4 + q]), m2_hfma2(tb[4 + q], neg1024, hb[4 + q])};  // sign*code, exact
             m2_tm_ld_wait();
             if (s + 1 < 16) {
                 m2_tm_ld8(Q.tm + 8 * (s + 1), qf[(s + 1) & 1]);
@@ -457,8 +452,6 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
                 cu[s >> 1][3] = fmaf(ratio[1], cur[3], cu[s >> 1][3]);
             }
         }
-        wbase[0] += kd_count(kwa);
-        wbase[1] += kd_count(kwb);
     }
     // ---- rotary part: rest of H64 over idx = 8j + 2t + e, /d, rotation, dot with the raw query ----
     float cr[4] = {0.0f, 0.0f, 0.0f, 0.0f};
