@@ -51,8 +51,7 @@ constexpr int M2_SM_VQ = M2_SM_STAGES + M2_NSTAGE * M2_STAGE_BYTES;  // (d0, d1)
 constexpr int M2_SM_VQB = M2_SM_VQ + 256 * M2_VQA_STRIDE * 4;        // d2: 256 x 130 B
 constexpr int M2_SM_ROPE = M2_SM_VQB + 256 * M2_VQB_STRIDE;          // 2 x 32 tokens x 32 float2
 constexpr int M2_SM_BROT = M2_SM_ROPE + 2 * M2_TT * 32 * 8;          // 4 kinds x 16 steps x 32 lanes x 8 B
-constexpr int M2_SM_LUT = M2_SM_BROT + 4 * 16 * 32 * 8;              // scatter table
-constexpr int M2_SM_FREQ = M2_SM_LUT + 448;
+constexpr int M2_SM_FREQ = M2_SM_BROT + 4 * 16 * 32 * 8;
 constexpr int M2_SM_DINV = M2_SM_FREQ + 128;                         // 64 floats
 constexpr int M2_SM_BARS = M2_SM_DINV + 256;
 constexpr int M2_SM_C3 = M2_SM_BARS + 64;              // 64 patches x float2: dim-3 centroids x alpha_v
@@ -156,8 +155,7 @@ __device__ __forceinline__ void m2_fill_rope(float2* tab, const float* freq, con
     }
 }
 
-// Per-layer constants in shared memory: RoPE frequencies, dinv of the 64 rotary dims, the scatter
-// table of the K decode, the rotor B fragments (with and without the centroid factor) and the V
+// Per-layer constants in shared memory: RoPE frequencies, dinv of the 64 rotary dims, the rotor B fragments (with and without the centroid factor) and the V
 // codebook.  Must be followed by __syncthreads().
 __device__ __forceinline__ void m2_setup_tables(unsigned char* smem, const CompressedKV& P, int tid) {
     float* freq_s = reinterpret_cast<float*>(smem + M2_SM_FREQ);
