@@ -566,7 +566,7 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
         vw[i][0] = vp[3 * g];
         vw[i][1] = vp[3 * g + 1];
         vw[i][2] = vp[3 * g + 2];
-        hb[i] = (vp[24 + (g >> 2)] >> (8 * (g & 3))) & 0xFFu;
+        hb[i] = ((vp[24 + (g >> 2)] >> (8 * (g & 3))) & 0xFFu) << 7;  // bit 7 + pl = high code bit of patch pl
     }
 #pragma unroll
     for (int pp = 0; pp < 4; ++pp) {  // patch pairs (2pp, 2pp+1) -> tiles 3pp .. 3pp+2
@@ -590,7 +590,7 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
                 }
                 f &= 0xFFFu;
                 f3[u][i] = f;
-                const uint32_t code = (f & 0x7Fu) | (((hb[i] >> pl) & 1u) << 7);
+                const uint32_t code = (f & 0x7Fu) | ((hb[i] >> pl) & 0x80u);
                 ex[u][i] = *reinterpret_cast<const uint32_t*>(vqa + (code * M2_VQA_STRIDE + 8 * g + pl) * 4);
                 ey[u][i] = *reinterpret_cast<const unsigned short*>(vqb + code * M2_VQB_STRIDE + (8 * g + pl) * 2);
             }
