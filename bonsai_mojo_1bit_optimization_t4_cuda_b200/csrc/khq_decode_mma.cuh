@@ -55,7 +55,8 @@ constexpr int M2_SM_FREQ = M2_SM_BROT + 4 * 16 * 32 * 8;
 constexpr int M2_SM_DINV = M2_SM_FREQ + 128;                         // 64 floats
 constexpr int M2_SM_BARS = M2_SM_DINV + 256;
 constexpr int M2_SM_C3 = M2_SM_BARS + 64;              // 64 patches x float2: dim-3 centroids x alpha_v
-constexpr int M2_SM_QR = M2_SM_C3 + NP * 8;                             // raw rotary query fragments: 4 kv-heads x 4 k-steps x 32 lanes x 8 B
+constexpr int M2_SM_RSTEP = M2_SM_C3 + NP * 8;                          // 32 x float2: cos / sin of one tile's worth (32 positions) of each rotary pair
+constexpr int M2_SM_QR = M2_SM_RSTEP + 32 * 8;                             // raw rotary query fragments: 4 kv-heads x 4 k-steps x 32 lanes x 8 B
 constexpr int M2_SM_TOTAL = M2_SM_QR + HKV * 4 * 32 * 8;
 // Tensor memory as a second register file.  The B fragments of the K side are per-lane constants: the query
 // side (ternary part q1 and residual part q2, fp16 hi and lo, eight registers per k-step) for a whole work
@@ -155,6 +156,19 @@ __device__ __forceinline__ void m2_fill_rope(float2* tab, const float* freq, con
     }
 }
 
+// The next tile's RoPE table from this tile's: every entry turns by 32 positions of its pair (four FMAs
+// instead of a range reduction and a sincos).  The caller re-seeds with m2_fill_rope every M2_ROPE_RESEED
+// tiles, so that rounding never accumulates over more than that many turns (< 4e-6), and whenever the
+// positions are not contiguous.
+constexpr int M2_ROPE_RESEED = 64;
+__device__ __forceinline__ void m2_step_rope(float2* dst, const float2* src, const float2* step, int tid) {
+#pragma unroll
+    for (int e = tid; e < M2_TT * 32; e += M2_THREADS) {
+        const float2 a = src[e], d = step[e & 31];
+        dst[e] = make_float2(a.x * d.x - a.y * d.y, a.y * d.x + a.x * d.y);
+    }
+}
+
 // Per-layer constants in shared memory: RoPE frequencies, dinv of the 64 rotary dims, the rotor B fragments (with and without the centroid factor) and the V
 // codebook.  Must be followed by __syncthreads().
 __device__ __forceinline__ void m2_setup_tables(unsigned char* smem, const CompressedKV& P, int tid) {
@@ -168,6 +182,12 @@ __device__ __forceinline__ void m2_setup_tables(unsigned char* smem, const Compr
         reinterpret_cast<float2*>(smem + M2_SM_C3)[tid - 128] = make_float2(__half2float(P.cents_v[0 * D + 4 * (tid - 128) + 3]) * P.alpha_v,
                                                                              __half2float(P.cents_v[1 * D + 4 * (tid - 128) + 3]) * P.alpha_v);
     if (tid < 64) dinv_s[tid] = (1.0f / 256.0f) / (__half2float(P.d_k[tid]) + 1e-8f);
+    if (tid >= 192 && tid < 224) {
+        const int m = tid - 192;
+        double th = (double)M2_TT * (double)powf(P.rope_base, -2.0f * (float)m / 64.0f);
+        th -= rint(th * 0.15915494309189535) * 6.283185307179586;
+        reinterpret_cast<float2*>(smem + M2_SM_RSTEP)[m] = make_float2((float)cos(th), (float)sin(th));
+    }
     // Rotor B fragments with the three low index bits of the 64-point Hadamard transform folded
     // in: u[8j + n] is produced by step s = 2j + (n >> 2) as rotor output c = n & 3, and
     // H64 = H8 (bits 0..2, inside a tile) x H8 (bits 3..5, across tiles), so column n' of the
@@ -683,7 +703,11 @@ __device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const _
             const int tok0 = base + (i + 1) * M2_TT;
             m2_stage_tile(P, smem + M2_SM_STAGES + ((gi + 1) % M2_NSTAGE) * M2_STAGE_BYTES, &bars[(gi + 1) % M2_NSTAGE],
                           tok0, min(M2_TT, P.c_len - tok0), tid);
-            m2_fill_rope(rope_tab + ((i + 1) & 1) * M2_TT * 32, freq_s, P, tok0, tid);
+            if (P.pos_chunk == 0 && ((i + 1) % M2_ROPE_RESEED) != 0)
+                m2_step_rope(rope_tab + ((i + 1) & 1) * M2_TT * 32, rope_tab + (i & 1) * M2_TT * 32,
+                             reinterpret_cast<const float2*>(smem + M2_SM_RSTEP), tid);
+            else
+                m2_fill_rope(rope_tab + ((i + 1) & 1) * M2_TT * 32, freq_s, P, tok0, tid);
         }
         mbar_wait_bounded(&bars[stg], (uint32_t)((gi / M2_NSTAGE) & 1), &g_status);
         const int blk0 = base + i * M2_TT + 16 * sub;
