@@ -318,7 +318,7 @@ __device__ __forceinline__ void compressed_range(unsigned char* smem, const __ha
 
 // Inverse V rotor + FWHT + /16/(d_v+1e-8) of the merged state of head h, stored as one
 // (acc[256], max, sum_exp) record.  Called by one warp per kv-head.
-template <int H0 = 0, int H1 = NREP>  // heads [H0, H1) of the kv-head: two warps may share the six
+template <int H0 = 0, int H1 = NREP>  // heads [H0, H1) of the kv-head: several warps may share the six
 __device__ __forceinline__ void v_epilogue_store(const WarpState& st, const CompressedKV& P, int lane,
                                                  float* const (&ob)[NREP]) {
     float dvi[8];

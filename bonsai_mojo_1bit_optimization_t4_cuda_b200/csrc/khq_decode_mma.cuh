@@ -21,13 +21,18 @@
 // covers dims 64t'+4s..+3 of all four quarters, i.e. the four patches that the rotor block sum
 // adds up.  V side: thread (g, t) owns patch group g (patches 8g..8g+7) of tokens 2t, 2t+1,
 // 2t+8, 2t+9.
+//
+// Registers and warps.  Twelve warps (three per scheduler) of at most 168 registers: what a warp keeps for a
+// whole work item or layer -- the query-side and rotor-side B fragments and the 64 O^T accumulators -- lives in
+// tensor memory, used here as a per-lane scratch file (tcgen05.st / tcgen05.ld; no tcgen05.mma), see M2_TM_COLS.
 #pragma once
 #include "khq_kdecode3.cuh"
 
 namespace khq {
 
-constexpr int M2_THREADS = 256;
-constexpr int M2_TT = 32;      // tokens per tile: 2 warps per kv-head x 16 tokens
+constexpr int M2_WPK = 3;           // warps per kv-head (12 warps: three per scheduler, at most 168 registers each)
+constexpr int M2_TT = 16 * M2_WPK;  // tokens per tile: every warp of a kv-head takes 16
+constexpr int M2_THREADS = 32 * HKV * M2_WPK;
 constexpr int M2_NSTAGE = 2;
 constexpr int M2_ROWS = M2_TT * HKV;
 constexpr int M2_OFF_MASK = 0;
@@ -49,7 +54,7 @@ constexpr int M2_VQA_STRIDE = 65;                                    // words pe
 constexpr int M2_VQB_STRIDE = 130;                                   // bytes per code row
 constexpr int M2_SM_VQ = M2_SM_STAGES + M2_NSTAGE * M2_STAGE_BYTES;  // (d0, d1): 256 x 65 x 4 B
 constexpr int M2_SM_VQB = M2_SM_VQ + 256 * M2_VQA_STRIDE * 4;        // d2: 256 x 130 B
-constexpr int M2_SM_ROPE = M2_SM_VQB + 256 * M2_VQB_STRIDE;          // 2 x 32 tokens x 32 float2
+constexpr int M2_SM_ROPE = M2_SM_VQB + 256 * M2_VQB_STRIDE;          // 2 x M2_TT tokens x 32 float2
 constexpr int M2_SM_BROT = M2_SM_ROPE + 2 * M2_TT * 32 * 8;          // 4 kinds x 16 steps x 32 lanes x 8 B
 constexpr int M2_SM_FREQ = M2_SM_BROT + 4 * 16 * 32 * 8;
 constexpr int M2_SM_DINV = M2_SM_FREQ + 128;                         // 64 floats
@@ -64,15 +69,18 @@ constexpr int M2_SM_TOTAL = M2_SM_QR + HKV * 4 * 32 * 8;
 // Held in registers the hi query fragments alone took 64 of the 255 across the tile loop, and the rest came
 // from shared memory with six loads per k-step.  They are written to tensor memory (tcgen05.st: the query side
 // once per item, the rotor side once per layer) and fetched one k-step ahead of use with two tcgen05.ld.
-// Warp w owns lanes 32 (w & 3) .. +31.  Columns: 128 (w >> 2) .. +127 = the warp's query fragments (eight per
-// k-step: q1.x, q1.y, q2.x, q2.y and their low-order halves), 256 .. 383 = the rotor fragments of the lane quadrant
-// (eight per k-step: b1.x, b1.y, b2.x, b2.y and their low-order halves; the same values in all four quadrants).
-constexpr uint32_t M2_TM_COLS = 512, M2_TM_ROT = 256;
+// Warp w owns lanes 32 (w & 3) .. +31, which it shares with the other warps of its kv-head.  Columns: 0 .. 127 =
+// the kv-head's query fragments (eight per k-step: q1.x, q1.y, q2.x, q2.y and their low-order halves; written by
+// the kv-head's first warp), 128 .. 255 = the rotor fragments of the lane quadrant (eight per k-step: b1.x, b1.y,
+// b2.x, b2.y and their low-order halves; the same values in all four quadrants), 256 + 64 (w >> 2) .. +63 = the
+// warp's O^T accumulators, which are in registers only while the V side of a block runs.
+constexpr uint32_t M2_TM_COLS = 512, M2_TM_ROT = 128, M2_TM_ACC = 256;
+static_assert(M2_TM_ACC + 64 * M2_WPK <= M2_TM_COLS, "tensor-memory columns");
 static_assert(M2_SM_TOTAL <= 227 * 1024 && M2_SM_C3 % 16 == 0 && M2_SM_ROPE % 16 == 0 && M2_SM_VQB % 16 == 0,
               "shared memory budget");
 static_assert(HKV * MERGE_FLOATS * 4 <= 256 * M2_VQA_STRIDE * 4, "cluster export records alias the codebook");
-static_assert(8 * MERGE_FLOATS * 4 <= M2_NSTAGE * M2_STAGE_BYTES, "records alias the stages");
-static_assert(8 * NREP * D * 4 <= M2_NSTAGE * M2_STAGE_BYTES, "prologue scratch aliases the stages");
+static_assert(HKV * M2_WPK * MERGE_FLOATS * 4 <= M2_NSTAGE * M2_STAGE_BYTES, "records alias the stages");
+static_assert(HKV * NREP * D * 4 <= M2_NSTAGE * M2_STAGE_BYTES, "prologue scratch aliases the stages");
 static_assert(M2_STAGE_BYTES % 16 == 0 && M2_OFF_KPAY % 16 == 0 && M2_OFF_VPAY % 16 == 0 && M2_OFF_KN % 16 == 0 &&
                   M2_OFF_VSM % 16 == 0, "bulk copy alignment");
 
@@ -250,6 +258,21 @@ __device__ __forceinline__ void m2_tm_ld8(uint32_t taddr, uint32_t (&r)[8]) {
                  : "r"(taddr)
                  : "memory");
 }
+__device__ __forceinline__ void m2_tm_st16f(uint32_t taddr, const float* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15};" ::"f"(r[0]),
+        "f"(r[1]), "f"(r[2]), "f"(r[3]), "f"(r[4]), "f"(r[5]), "f"(r[6]), "f"(r[7]), "f"(r[8]), "f"(r[9]), "f"(r[10]), "f"(r[11]),
+        "f"(r[12]), "f"(r[13]), "f"(r[14]), "f"(r[15]), "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void m2_tm_ld16f(uint32_t taddr, float* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=f"(r[0]), "=f"(r[1]), "=f"(r[2]), "=f"(r[3]), "=f"(r[4]), "=f"(r[5]), "=f"(r[6]), "=f"(r[7]), "=f"(r[8]), "=f"(r[9]),
+          "=f"(r[10]), "=f"(r[11]), "=f"(r[12]), "=f"(r[13]), "=f"(r[14]), "=f"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ void m2_tm_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void m2_tm_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // Allocation by warp 0 of a CTA (one CTA per SM by shared memory, so the columns are always free); the address goes
@@ -365,17 +388,22 @@ __device__ __forceinline__ void m2_build_query(M2Query& Q, const __half* __restr
     }
     m2_tm_st_wait();
 #pragma unroll
-    for (int kk = 0; kk < 4; ++kk) qr_s[kk * 32 + lane] = make_uint2(qrw[kk][0], qrw[kk][1]);  // both warps of a kv-head write the same values
+    for (int kk = 0; kk < 4; ++kk) qr_s[kk * 32 + lane] = make_uint2(qrw[kk][0], qrw[kk][1]);
     __syncwarp();
 }
 
 // Running attention state of a warp in fragment layout: thread (g, t) holds heads 2t, 2t+1.
 struct M2State {
-    float o[16][4];  // O^T tiles: [0..11] dims 0..2 of the patches, [12..15] dim 3 of the patches
+    uint32_t tm_o;  // tensor-memory address of the warp's 64 accumulator columns: O^T tiles [0..11] dims 0..2 of the
+                    // patches, [12..15] dim 3 of the patches, four registers each; in registers only during the V side
     float m[2], l[2];
-    __device__ __forceinline__ void init() {
+    __device__ __forceinline__ void init() {  // whole warp
+        float z[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+        for (int i = 0; i < 16; ++i) z[i] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) m2_tm_st16f(tm_o + 16 * c, z);
+        m2_tm_st_wait();
         m[0] = m[1] = NEG_BIG;
         l[0] = l[1] = 0.0f;
     }
@@ -539,15 +567,7 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
         pw[1][e] = valid[1] ? __expf(sc[1][e] - mn) : 0.0f;
         st.l[e] = st.l[e] * corr[e] + pw[0][e] + pw[1][e];
     }
-    if (__any_sync(0xFFFFFFFFu, corr[0] != 1.0f || corr[1] != 1.0f)) {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            st.o[i][0] *= corr[0];
-            st.o[i][1] *= corr[1];
-            st.o[i][2] *= corr[0];
-            st.o[i][3] *= corr[1];
-        }
-    }
+    const bool rescale = __any_sync(0xFFFFFFFFu, corr[0] != 1.0f || corr[1] != 1.0f);
     // three scaled variants of P, transposed into B fragments (tokens = k, heads = n)
     uint32_t pb[3][2], pl_[3][2];  // fp16 hi and the fp16 of what hi lost
     {
@@ -577,6 +597,20 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
         }
     }
     // ================================ V side: O^T += V^T P^T ====================================
+    // the accumulators come out of tensor memory for this part only
+    float o[16][4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) m2_tm_ld16f(st.tm_o + 16 * c, &o[4 * c][0]);
+    m2_tm_ld_wait();
+    if (rescale) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            o[i][0] *= corr[0];
+            o[i][1] *= corr[1];
+            o[i][2] *= corr[0];
+            o[i][3] *= corr[1];
+        }
+    }
     // thread (g, t): patch group g of tokens 2t, 2t+1, 2t+8, 2t+9
     uint32_t vw[4][3], hb[4];
 #pragma unroll
@@ -629,8 +663,8 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
 #pragma unroll
         for (int jj = 0; jj < 3; ++jj) {
             const uint32_t a[4] = {lo[2 * jj], lo[2 * jj + 1], hi[2 * jj], hi[2 * jj + 1]};
-            m2_mma(st.o[3 * pp + jj], a, pb[0][0], pb[0][1]);
-            m2_mma_lo(st.o[3 * pp + jj], a, pl_[0][0], pl_[0][1]);
+            m2_mma(o[3 * pp + jj], a, pb[0][0], pb[0][1]);
+            m2_mma_lo(o[3 * pp + jj], a, pl_[0][0], pl_[0][1]);
         }
         // dim 3 of the two patches (rows 0, 1 of tile 12 + pp): centroid choice and (dump - 8)
         uint32_t ca[4], da[4];  // a0..a3 of the two extra MMAs
@@ -654,19 +688,22 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
             da[u] = *reinterpret_cast<const uint32_t*>(&d_lo);
             da[2 + u] = *reinterpret_cast<const uint32_t*>(&d_hi);
         }
-        m2_mma(st.o[12 + pp], ca, pb[1][0], pb[1][1]);
-        m2_mma_lo(st.o[12 + pp], ca, pl_[1][0], pl_[1][1]);
-        m2_mma(st.o[12 + pp], da, pb[2][0], pb[2][1]);
-        m2_mma_lo(st.o[12 + pp], da, pl_[2][0], pl_[2][1]);
+        m2_mma(o[12 + pp], ca, pb[1][0], pb[1][1]);
+        m2_mma_lo(o[12 + pp], ca, pl_[1][0], pl_[1][1]);
+        m2_mma(o[12 + pp], da, pb[2][0], pb[2][1]);
+        m2_mma_lo(o[12 + pp], da, pl_[2][0], pl_[2][1]);
     }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) m2_tm_st16f(st.tm_o + 16 * c, &o[4 * c][0]);
+    m2_tm_st_wait();
 }
 
-// Attention of all 24 query heads over compressed tokens [my_lo, my_hi) of P; the CTA's 8 warps
-// are (kv-head = warp & 3) x (16-token half of each 32-token tile = warp >> 2).  On return,
+// Attention of all 24 query heads over compressed tokens [my_lo, my_hi) of P; the CTA's 12 warps
+// are (kv-head = warp & 3) x (16-token third of each 48-token tile = warp >> 2).  On return,
 // warps 0..3 hold in `ws` the merged state of their kv-head's six heads in the first generation's
 // layout (lane = 8 dims, rotated V domain), ready for merge_from / v_epilogue_store.  Tables must
-// be set up; all 256 threads call it.
-template <bool ALL_WARPS_MERGE = false>  // true: warps 4..7 also return the merged state of kv-head warp - 4
+// be set up; all M2_THREADS threads call it.
+template <bool ALL_WARPS_MERGE = false>  // true: every warp of a kv-head returns the kv-head's merged state
 __device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const __half* __restrict__ q,
                                                     size_t q_head_stride, const CompressedKV& P, int my_lo, int my_hi,
                                                     float scale, unsigned& tiles_done, WarpState& ws, uint32_t tmem) {
@@ -677,12 +714,14 @@ __device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const _
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + M2_SM_BARS);
 
     M2Query Q;
-    Q.tm = tmem + ((uint32_t)(32 * kvh) << 16) + 128u * (uint32_t)sub;
+    Q.tm = tmem + ((uint32_t)(32 * kvh) << 16);
     Q.rot = tmem + ((uint32_t)(32 * kvh) << 16) + M2_TM_ROT;
-    m2_build_query(Q, q, q_head_stride, P, kvh, lane, reinterpret_cast<float*>(smem + M2_SM_STAGES) + warp * NREP * D,
-                   reinterpret_cast<uint2*>(smem + M2_SM_QR) + kvh * 4 * 32);
+    if (sub == 0)  // one warp per kv-head builds the query side; the others read it from tensor / shared memory
+        m2_build_query(Q, q, q_head_stride, P, kvh, lane, reinterpret_cast<float*>(smem + M2_SM_STAGES) + kvh * NREP * D,
+                       reinterpret_cast<uint2*>(smem + M2_SM_QR) + kvh * 4 * 32);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();  // the query scratch aliases the stages
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");  // the rotor fragments other warps stored
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");  // the query and rotor fragments other warps stored
 
     const int base = my_lo & ~1;
     const int ntiles = (my_hi > my_lo) ? (my_hi - base + M2_TT - 1) / M2_TT : 0;
@@ -694,6 +733,7 @@ __device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const _
     }
     __syncthreads();
     M2State st;
+    st.tm_o = tmem + ((uint32_t)(32 * kvh) << 16) + M2_TM_ACC + 64u * (uint32_t)sub;
     st.init();
 #pragma unroll 1
     for (int i = 0; i < ntiles; ++i) {
@@ -727,6 +767,10 @@ __device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const _
         st.l[e] += __shfl_xor_sync(0xFFFFFFFFu, st.l[e], 16);
     }
     float* rec = reinterpret_cast<float*>(smem + M2_SM_STAGES) + warp * MERGE_FLOATS;
+    float o[16][4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) m2_tm_ld16f(st.tm_o + 16 * c, &o[4 * c][0]);
+    m2_tm_ld_wait();
     if (t < 3) {
 #pragma unroll
         for (int j = 0; j < 16; ++j)
@@ -734,8 +778,8 @@ __device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const _
             for (int r = 0; r < 2; ++r) {
                 const int idx = 2 * j + r;
                 const int dim = j < 12 ? 4 * (8 * g + idx / 3) + idx % 3 : 4 * (8 * g + 2 * (j - 12) + r) + 3;
-                rec[(2 * t) * D + dim] = st.o[j][2 * r];
-                rec[(2 * t + 1) * D + dim] = st.o[j][2 * r + 1];
+                rec[(2 * t) * D + dim] = o[j][2 * r];
+                rec[(2 * t + 1) * D + dim] = o[j][2 * r + 1];
             }
         if (g == 0) {
             rec[NREP * D + 2 * t] = st.m[0];
@@ -747,8 +791,9 @@ __device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const _
     __syncthreads();
     ws.init();
     if (ALL_WARPS_MERGE || warp < 4) {
-        merge_from(ws, reinterpret_cast<const float*>(smem + M2_SM_STAGES) + kvh * MERGE_FLOATS, lane);
-        merge_from(ws, reinterpret_cast<const float*>(smem + M2_SM_STAGES) + (kvh + 4) * MERGE_FLOATS, lane);
+#pragma unroll
+        for (int r = 0; r < M2_WPK; ++r)
+            merge_from(ws, reinterpret_cast<const float*>(smem + M2_SM_STAGES) + (kvh + 4 * r) * MERGE_FLOATS, lane);
     }
 }
 
@@ -804,18 +849,21 @@ khq_decode_batched_mma_kernel(const KhqSeqDesc* __restrict__ descs, const KhqTab
             }
             WarpState ws;
             m2_compressed_range<true>(smem, d.q_gate, (size_t)2 * D, P, w.lo, w.hi, scale, tiles_done, ws, tmem);
-            // the two warps of a kv-head transform and store three heads each
-            if (sub == 0) v_epilogue_store<0, NREP / 2>(ws, P, lane, ob);
-            else v_epilogue_store<NREP / 2, NREP>(ws, P, lane, ob);
+            // the three warps of a kv-head transform and store two heads each
+            static_assert(M2_WPK == 3 && NREP == 6, "head split of the item epilogue");
+            if (sub == 0) v_epilogue_store<0, 2>(ws, P, lane, ob);
+            else if (sub == 1) v_epilogue_store<2, 4>(ws, P, lane, ob);
+            else v_epilogue_store<4, 6>(ws, P, lane, ob);
         } else {
             WarpState ws;
             ws.init();
-            window_range(d.q_gate, d.ring_k, d.ring_v, d.win_start, w.lo + sub, 2, w.hi, ring_cap, scale, kvh, lane, ws);
-            float* rec = reinterpret_cast<float*>(smem + M2_SM_STAGES) + kvh * MERGE_FLOATS;
-            if (sub == 1) store_record(ws, rec, lane);
+            window_range(d.q_gate, d.ring_k, d.ring_v, d.win_start, w.lo + sub, M2_WPK, w.hi, ring_cap, scale, kvh, lane, ws);
+            float* rec = reinterpret_cast<float*>(smem + M2_SM_STAGES);
+            if (sub > 0) store_record(ws, rec + (kvh + 4 * (sub - 1)) * MERGE_FLOATS, lane);
             __syncthreads();
             if (sub == 0) {
-                merge_from(ws, rec, lane);
+#pragma unroll
+                for (int r = 0; r < M2_WPK - 1; ++r) merge_from(ws, rec + (kvh + 4 * r) * MERGE_FLOATS, lane);
                 raw_store(ws, lane, ob);
             }
         }
