@@ -1032,31 +1032,33 @@ static int attn_launch_impl(const void* q, const void* k_payload, const void* v_
         const int s_limit = (L_q > 1) ? (c_len < l + 1 ? c_len : l + 1) : c_len;
         const int per = (s_limit + num_splits - 1) / num_splits;
         // CTAs per split (a portable cluster of at most 8) and the kernel generation, by estimated
-        // time in units of one token of tensor-core decode (0.23 us measured): waves x (per-CTA
-        // set-up + tokens per CTA x cost per token), waves = splits / clusters of that size that
-        // fit on the GPU at once (clusters are placed inside a GPC, so fewer than SMs / size fit).
-        // Tensor-core generation: set-up ~160 (codebook staging, query folding), pays from ~192
-        // tokens per CTA on.  CUDA-core generation: set-up ~116, 3.06 per token, ~TT tokens per CTA.
+        // time in units of 0.23 us: waves x (per-CTA set-up + tokens per CTA x cost per token), waves =
+        // splits / clusters of that size that fit on the GPU at once (clusters are placed inside a GPC, so
+        // fewer than SMs / size fit).  Measured: tensor-core generation set-up ~104 (tables, tensor-memory
+        // allocation, query build, record), 0.63 per token in whole 48-token tiles; CUDA-core generation set-up
+        // ~116, 3.06 per token, ~TT tokens per CTA.
         int cluster = (per + TT - 1) / TT;
         if (cluster < 1) cluster = 1;
         if (cluster > 8) cluster = 8;
+        bool use_mma = false;
         {
             const int tpc1 = (per + cluster - 1) / cluster;
             const long long w1 = (num_splits + max_clusters(false, cluster) - 1) / max_clusters(false, cluster);
             long long best = w1 * (116 + (tpc1 * 306LL) / 100);
             for (int c = 1; c <= 8; ++c) {
                 const int tpc = (per + c - 1) / c;
-                if (tpc < 192) break;
+                const int tiles = (tpc + M2_TT - 1) / M2_TT;
                 const long long waves = (num_splits + max_clusters(true, c) - 1) / max_clusters(true, c);
-                const long long cost = waves * (160 + tpc);
+                const long long cost = waves * (104 + (tiles * M2_TT * 63LL) / 100);
                 if (cost < best) {
                     best = cost;
                     cluster = c;
+                    use_mma = true;
                 }
+                if (tpc <= M2_TT) break;  // more CTAs would only add set-ups
             }
         }
-        const int tok_per_cta = (per + cluster - 1) / cluster;
-        if (tok_per_cta >= 192)  // tensor-core generation: its per-CTA table set-up pays from here on
+        if (use_mma)
             err = launch_cluster(khq_attn_compressed_mma_kernel, (unsigned)(num_splits * cluster), (unsigned)cluster,
                                  (size_t)M2_SM_TOTAL, stream, (unsigned)M2_THREADS, static_cast<const __half*>(q), P,
                                  static_cast<float*>(out_attn), static_cast<float*>(out_partial), num_splits, L_q,
