@@ -650,6 +650,25 @@ namespace khq {
 
 // Per problem and query head: LSE merge of the problem's partial slots, /(den+1e-8), sigmoid
 // gate, fp16 store.  grid = n_desc*HQ blocks of G * D threads.
+// A problem with few records (the batched serving case: about a dozen): one plain walk per pass, no barrier.
+__global__ void __launch_bounds__(D)
+khq_batched_merge_gate_few_kernel(const KhqSeqDesc* __restrict__ descs, const float* __restrict__ partials) {
+    const int di = blockIdx.x / HQ, h = blockIdx.x % HQ, dd = threadIdx.x;
+    const KhqSeqDesc d = descs[di];
+    float M = NEG_BIG;
+    for (int s = 0; s < d.n_slots; ++s) M = fmaxf(M, partials[((size_t)(d.first_slot + s) * HQ + h) * PART + D]);
+    float num = 0.0f, den = 0.0f;
+    for (int s = 0; s < d.n_slots; ++s) {
+        const float* p = partials + ((size_t)(d.first_slot + s) * HQ + h) * PART;
+        const float w = __expf(p[D] - M);
+        num = fmaf(p[dd], w, num);
+        den = fmaf(p[D + 1], w, den);
+    }
+    const float val = num / (den + 1e-8f);
+    const float g = __half2float(d.q_gate[(size_t)h * 2 * D + D + dd]);
+    d.out[(size_t)h * D + dd] = __float2half(val * (1.0f / (1.0f + __expf(-g))));
+}
+
 template <int G>
 __global__ void __launch_bounds__(G * D)
 khq_batched_merge_gate_kernel(const KhqSeqDesc* __restrict__ descs, const float* __restrict__ partials) {
@@ -1436,7 +1455,7 @@ static int decode_batched_impl(const void* descs, const void* tables, const void
         else khq_batched_merge_partial_kernel<1><<<n_desc * HQ, D, 0, stream>>>(dd, partials, out_partials);
     } else {
         if (many) khq_batched_merge_gate_kernel<MERGE_GROUPS><<<n_desc * HQ, MERGE_GROUPS * D, 0, stream>>>(dd, partials);
-        else khq_batched_merge_gate_kernel<1><<<n_desc * HQ, D, 0, stream>>>(dd, partials);
+        else khq_batched_merge_gate_few_kernel<<<n_desc * HQ, D, 0, stream>>>(dd, partials);
     }
     err = cudaGetLastError();
     return (err == cudaSuccess) ? 0 : static_cast<int>(err);
