@@ -650,23 +650,43 @@ namespace khq {
 
 // Per problem and query head: LSE merge of the problem's partial slots, /(den+1e-8), sigmoid
 // gate, fp16 store.  grid = n_desc*HQ blocks of G * D threads.
-// A problem with few records (the batched serving case: about a dozen): one plain walk per pass, no barrier.
+// A problem with few records (the batched serving case: about a dozen).  The block is bound by the latency of
+// its loads, so the records are taken eight at a time with all 24 loads of a chunk issued together, and the chunks
+// are folded into the running (max, num, den) the way the attention itself folds blocks of tokens.
 __global__ void __launch_bounds__(D)
 khq_batched_merge_gate_few_kernel(const KhqSeqDesc* __restrict__ descs, const float* __restrict__ partials) {
+    constexpr int CH = 8;
     const int di = blockIdx.x / HQ, h = blockIdx.x % HQ, dd = threadIdx.x;
     const KhqSeqDesc d = descs[di];
-    float M = NEG_BIG;
-    for (int s = 0; s < d.n_slots; ++s) M = fmaxf(M, partials[((size_t)(d.first_slot + s) * HQ + h) * PART + D]);
-    float num = 0.0f, den = 0.0f;
-    for (int s = 0; s < d.n_slots; ++s) {
-        const float* p = partials + ((size_t)(d.first_slot + s) * HQ + h) * PART;
-        const float w = __expf(p[D] - M);
-        num = fmaf(p[dd], w, num);
-        den = fmaf(p[D + 1], w, den);
+    const float* base = partials + ((size_t)d.first_slot * HQ + h) * PART;
+    const float gate = __half2float(d.q_gate[(size_t)h * 2 * D + D + dd]);
+    float M = NEG_BIG, num = 0.0f, den = 0.0f;
+    for (int s0 = 0; s0 < d.n_slots; s0 += CH) {
+        float m[CH], l[CH], a[CH];
+#pragma unroll
+        for (int i = 0; i < CH; ++i) {
+            const bool in = s0 + i < d.n_slots;
+            const float* p = base + (size_t)(in ? s0 + i : s0) * HQ * PART;
+            m[i] = in ? p[D] : NEG_BIG;
+            l[i] = in ? p[D + 1] : 0.0f;
+            a[i] = in ? p[dd] : 0.0f;
+        }
+        float cm = M;
+#pragma unroll
+        for (int i = 0; i < CH; ++i) cm = fmaxf(cm, m[i]);
+        const float keep = __expf(M - cm);
+        num *= keep;
+        den *= keep;
+#pragma unroll
+        for (int i = 0; i < CH; ++i) {
+            const float w = __expf(m[i] - cm);
+            num = fmaf(a[i], w, num);
+            den = fmaf(l[i], w, den);
+        }
+        M = cm;
     }
     const float val = num / (den + 1e-8f);
-    const float g = __half2float(d.q_gate[(size_t)h * 2 * D + D + dd]);
-    d.out[(size_t)h * D + dd] = __float2half(val * (1.0f / (1.0f + __expf(-g))));
+    d.out[(size_t)h * D + dd] = __float2half(val * (1.0f / (1.0f + __expf(-gate))));
 }
 
 template <int G>
