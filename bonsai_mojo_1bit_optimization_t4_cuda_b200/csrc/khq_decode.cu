@@ -1364,7 +1364,7 @@ extern "C" int khq_b200_plan_decode(const int* c_len, const int* win_len, int n_
     if (auto_size) {
         long long t = total / (2LL * sms);  // the guided rule's own first size
         if (t < 48) t = 48;
-        if (t > 4096) t = 4096;  // ~1 ms of work: an item costs ~14 us whatever its size
+        if (t > 8192) t = 8192;  // ~1.2 ms of work: an item costs ~12 us whatever its size
         tokens_per_item = (int)t;
     }
     tokens_per_item = ((tokens_per_item + 95) / 96) * 96;  // a multiple of every generation's staging tile (24, 32 tokens)
@@ -1384,7 +1384,7 @@ extern "C" int khq_b200_plan_decode(const int* c_len, const int* win_len, int n_
         };
         consider(PlanRule{0, tokens_per_item, 48, nullptr, nullptr});
         // an explicit tokens_per_item stays an upper bound on every piece
-        const int max_piece = auto_size ? 4128 : tokens_per_item;
+        const int max_piece = auto_size ? 8256 : tokens_per_item;
         long long work = total;
         for (int i = 0; i < n_desc; ++i) work += (long long)PLAN_WINDOW_COST * (win_len[i] > 0 ? win_len[i] : 0);
         for (int k = 1; k <= 3; ++k) {

@@ -312,24 +312,36 @@ __device__ __forceinline__ void m2_rotor_to_tmem(const unsigned char* smem, uint
 
 // q: (H_q, ..) with `q_head_stride` halfs between heads.  scratch: this warp's NREP*D floats.
 __device__ __forceinline__ void m2_build_query(M2Query& Q, const __half* __restrict__ q, size_t q_head_stride,
-                                               const CompressedKV& P, int kvh, int lane, float* scratch,
+                                               const CompressedKV& P, int kvh, int sub, int lane, float* scratch,
                                                uint2* qr_s /* this kv-head's [4][32] raw rotary query fragments */) {
+    // The M2_WPK warps of a kv-head share the work (it runs once per work item, on the critical path): warp `sub`
+    // transforms query heads sub, sub + M2_WPK, ... into the kv-head's scratch, the warps meet at a named barrier,
+    // then warp `sub` builds the B fragments of k-steps sub, sub + M2_WPK, ... .  Every global load is issued before
+    // the first one is needed.
     const int g = lane >> 2, t = lane & 3;
-    // q~ in the lane-owns-8-dims layout: q~ = R^T H256 (q * dinv * [dim >= 64]).  This runs once per work
-    // item on the critical path, so every global load is issued before the first one is needed: the
-    // tables as wide loads, each head's query row one head ahead of its transform.
+    constexpr int HPW = NREP / M2_WPK;  // heads per warp
+    static_assert(NREP % M2_WPK == 0, "query heads split evenly over the warps of a kv-head");
     float dv[8], rr[2][16];
-    uint4 qnext = *reinterpret_cast<const uint4*>(q + (size_t)(kvh * NREP) * q_head_stride + lane * 8);
+    uint4 qraw[HPW];
+#pragma unroll
+    for (int i = 0; i < HPW; ++i)
+        qraw[i] = *reinterpret_cast<const uint4*>(q + (size_t)(kvh * NREP + sub + M2_WPK * i) * q_head_stride + lane * 8);
     // for the fragments built after the transforms: the centroids of dims 64 t + 4 s + {0..3} and the raw rotary query dims
-    uint2 cck[16];
+    constexpr int SPW = (16 + M2_WPK - 1) / M2_WPK;  // k-steps per warp (the last warps may have one less)
+    uint2 cck[SPW];
     uint32_t qrw[4][2];
 #pragma unroll
-    for (int s = 0; s < 16; ++s) cck[s] = (g < NREP) ? *reinterpret_cast<const uint2*>(P.cents_k + 2 * D + 64 * t + 4 * s) : make_uint2(0u, 0u);
+    for (int i = 0; i < SPW; ++i) {
+        const int s = sub + M2_WPK * i;
+        cck[i] = (g < NREP && s < 16) ? *reinterpret_cast<const uint2*>(P.cents_k + 2 * D + 64 * t + 4 * s) : make_uint2(0u, 0u);
+    }
+    if (sub == 0) {
 #pragma unroll
-    for (int kk = 0; kk < 4; ++kk) {
-        const __half* qh = q + (size_t)(kvh * NREP + (g < NREP ? g : 0)) * q_head_stride + 16 * kk + 2 * t;
-        qrw[kk][0] = (g < NREP) ? *reinterpret_cast<const uint32_t*>(qh) : 0u;
-        qrw[kk][1] = (g < NREP) ? *reinterpret_cast<const uint32_t*>(qh + 8) : 0u;
+        for (int kk = 0; kk < 4; ++kk) {
+            const __half* qh = q + (size_t)(kvh * NREP + (g < NREP ? g : 0)) * q_head_stride + 16 * kk + 2 * t;
+            qrw[kk][0] = (g < NREP) ? *reinterpret_cast<const uint32_t*>(qh) : 0u;
+            qrw[kk][1] = (g < NREP) ? *reinterpret_cast<const uint32_t*>(qh + 8) : 0u;
+        }
     }
     {
         const uint4 dr = *reinterpret_cast<const uint4*>(P.d_k + lane * 8);
@@ -348,11 +360,11 @@ __device__ __forceinline__ void m2_build_query(M2Query& Q, const __half* __restr
 #pragma unroll
             for (int i = 0; i < 16; ++i) rr[p][i] = __half2float(hr[p * 16 + i]);
     }
-#pragma unroll 1
-    for (int h = 0; h < NREP; ++h) {
-        const uint4 qraw = qnext;
-        if (h + 1 < NREP) qnext = *reinterpret_cast<const uint4*>(q + (size_t)(kvh * NREP + h + 1) * q_head_stride + lane * 8);
-        const __half* hq = reinterpret_cast<const __half*>(&qraw);
+    // q~ in the lane-owns-8-dims layout: q~ = R^T H256 (q * dinv * [dim >= 64])
+#pragma unroll
+    for (int i = 0; i < HPW; ++i) {
+        const int h = sub + M2_WPK * i;
+        const __half* hq = reinterpret_cast<const __half*>(&qraw[i]);
         float x[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) x[j] = __half2float(hq[j]) * dv[j];
@@ -367,28 +379,33 @@ __device__ __forceinline__ void m2_build_query(M2Query& Q, const __half* __restr
                 scratch[h * D + lane * 8 + p * 4 + k] = a;
             }
     }
-    __syncwarp();
+    asm volatile("bar.sync %0, %1;" ::"r"(2 + kvh), "n"(32 * M2_WPK) : "memory");  // the kv-head's warps: all six heads are in the scratch
 #pragma unroll
-    for (int s = 0; s < 16; ++s) {
-        const int d0 = 64 * t + 4 * s;
-        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f}, c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        if (g < NREP) {
-            const float4 qq = *reinterpret_cast<const float4*>(scratch + g * D + d0);
-            const __half* hc = reinterpret_cast<const __half*>(&cck[s]);
-            v[0] = qq.x; v[1] = qq.z; v[2] = qq.y; v[3] = qq.w;  // dims d0 + {0, 2, 1, 3}
-            c[0] = __half2float(hc[0]); c[1] = __half2float(hc[2]); c[2] = __half2float(hc[1]); c[3] = __half2float(hc[3]);
+    for (int i = 0; i < SPW; ++i) {
+        const int s = sub + M2_WPK * i;
+        if (s < 16) {
+            const int d0 = 64 * t + 4 * s;
+            float v[4] = {0.0f, 0.0f, 0.0f, 0.0f}, c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (g < NREP) {
+                const float4 qq = *reinterpret_cast<const float4*>(scratch + g * D + d0);
+                const __half* hc = reinterpret_cast<const __half*>(&cck[i]);
+                v[0] = qq.x; v[1] = qq.z; v[2] = qq.y; v[3] = qq.w;  // dims d0 + {0, 2, 1, 3}
+                c[0] = __half2float(hc[0]); c[1] = __half2float(hc[2]); c[2] = __half2float(hc[1]); c[3] = __half2float(hc[3]);
+            }
+            uint2 lo, hi;
+            m2_pack_hilo(v[0] * c[0], v[1] * c[1], hi.x, lo.x);
+            m2_pack_hilo(v[2] * c[2], v[3] * c[3], hi.y, lo.y);
+            uint2 lo2, hi2;
+            m2_pack_hilo(v[0], v[1], hi2.x, lo2.x);
+            m2_pack_hilo(v[2], v[3], hi2.y, lo2.y);
+            m2_tm_st8(Q.tm + 8 * s, hi.x, hi.y, hi2.x, hi2.y, lo.x, lo.y, lo2.x, lo2.y);
         }
-        uint2 lo, hi;
-        m2_pack_hilo(v[0] * c[0], v[1] * c[1], hi.x, lo.x);
-        m2_pack_hilo(v[2] * c[2], v[3] * c[3], hi.y, lo.y);
-        uint2 lo2, hi2;
-        m2_pack_hilo(v[0], v[1], hi2.x, lo2.x);
-        m2_pack_hilo(v[2], v[3], hi2.y, lo2.y);
-        m2_tm_st8(Q.tm + 8 * s, hi.x, hi.y, hi2.x, hi2.y, lo.x, lo.y, lo2.x, lo2.y);
     }
     m2_tm_st_wait();
+    if (sub == 0) {
 #pragma unroll
-    for (int kk = 0; kk < 4; ++kk) qr_s[kk * 32 + lane] = make_uint2(qrw[kk][0], qrw[kk][1]);
+        for (int kk = 0; kk < 4; ++kk) qr_s[kk * 32 + lane] = make_uint2(qrw[kk][0], qrw[kk][1]);
+    }
     __syncwarp();
 }
 
@@ -716,9 +733,8 @@ __device__ __forceinline__ void m2_compressed_range(unsigned char* smem, const _
     M2Query Q;
     Q.tm = tmem + ((uint32_t)(32 * kvh) << 16);
     Q.rot = tmem + ((uint32_t)(32 * kvh) << 16) + M2_TM_ROT;
-    if (sub == 0)  // one warp per kv-head builds the query side; the others read it from tensor / shared memory
-        m2_build_query(Q, q, q_head_stride, P, kvh, lane, reinterpret_cast<float*>(smem + M2_SM_STAGES) + kvh * NREP * D,
-                       reinterpret_cast<uint2*>(smem + M2_SM_QR) + kvh * 4 * 32);
+    m2_build_query(Q, q, q_head_stride, P, kvh, sub, lane, reinterpret_cast<float*>(smem + M2_SM_STAGES) + kvh * NREP * D,
+                   reinterpret_cast<uint2*>(smem + M2_SM_QR) + kvh * 4 * 32);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();  // the query scratch aliases the stages
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");  // the query and rotor fragments other warps stored

@@ -132,7 +132,7 @@ class BatchEngine:
         self.tokens_per_item_arg = int(tokens_per_item) if tokens_per_item > 0 else 0
         if tokens_per_item <= 0:
             sms = torch.cuda.get_device_properties(dev).multi_processor_count if dev.type == "cuda" else 148
-            tokens_per_item = int(min(max(int(self.cap.sum()) // (2 * sms), 96), 4096))
+            tokens_per_item = int(min(max(int(self.cap.sum()) // (2 * sms), 96), 8192))
         self.tokens_per_item = (tokens_per_item + 95) // 96 * 96
         # the planner shrinks the last items of a launch (down to 48 tokens), or cuts one to three pieces per
         # SM: room for either on top of the full-size items

@@ -79,7 +79,7 @@ def test_many_sequences_end_with_small_items():
     _check_cover(items, first, cnt, c_len, win_len)
     comp = items[items["kind"] == 0]
     size = (comp["hi"] - comp["lo"]).astype(np.int64)
-    assert np.median(size[: len(size) // 4]) == 4128 and size[-20:].max() <= 144
+    assert size[: len(size) // 4].max() == 8256 and size[-20:].max() <= 144
     ideal = (float(c_len.sum()) + 3.0 * float(win_len.sum())) / 148.0
     assert _makespan(items) <= 1.01 * ideal
 
