@@ -817,6 +817,23 @@ def run_single(args, rank, world, local_rank):
     with torch.cuda.graph(graph2, stream=side):
         fused_step()
     us_fused_graph = timed(graph2.replay, n_it)
+    # the same state as ONE problem of the batched entry (planner-cut persistent launch + merge and gate): what a serving
+    # host calls; output checked against the three launches
+    from bonsai_mojo_1bit_optimization_t4_cuda_b200.batched import BatchedDecode
+
+    prob = dict(kv)
+    out_b = torch.zeros(24 * 256, dtype=torch.float16, device=dev)
+    prob.update(q_gate=qg, ring_k=ring_k, ring_v=ring_v, out=out_b, table_id=0, c_len=c_len, start_pos=0, win_start=win_start,
+                win_len=win_len)
+    tabs_b = [dict(cents_k=tab["cents_k"], cents_v=tab["cents_v"], vq=tab["vq"], k_rotor=tab["rotor_k"], v_rotor=tab["rotor_v"],
+                   d_k=tab["d_k"], d_v=tab["d_v"], alpha_k=tb.alpha_k, alpha_v=tb.alpha_v)]
+    bd = BatchedDecode([prob], tabs_b)
+    step_with(ours, 0)
+    bd.launch(1.0 / 16.0, 1e7)
+    torch.cuda.synchronize()
+    batched_diff = float((out_b.float() - out.float()).abs().max())
+    assert batched_diff < 2e-3, f"batched entry differs from the three launches: {batched_diff}"
+    us_batched = timed(lambda: bd.launch(1.0 / 16.0, 1e7), n_it)
     ref_us = None
     ref_path = ROOT / "oracle" / "_ref" / "libbonsai_ref_sm100a.so"
     if ref_path.exists():
@@ -839,6 +856,7 @@ def run_single(args, rank, world, local_rank):
                                    "three drop-in launches per step", "l2": "862 KB working set: L2-resident by nature (a "
                        "latency case, not a bandwidth one)"},
             "graph_replay_us": us_graph, "fused_entry_us": us_fused, "fused_entry_graph_replay_us": us_fused_graph,
+            "batched_entry_us": us_batched, "batched_entry_items": int(bd.n_items), "batched_entry_max_abs_diff": batched_diff,
             "reference_kernels_sm100a_us": ref_us,
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
                          "algorithmic_bytes_per_step": b_alg, "note": "launch-latency bound at this size"},
