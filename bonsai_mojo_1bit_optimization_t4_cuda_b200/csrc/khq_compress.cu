@@ -32,7 +32,7 @@ struct CompressScratch {
     unsigned char os[64];   // outlier sign flags, by outlier ordinal
 };
 
-__global__ void __launch_bounds__(CMP_WARPS * 32)
+__global__ void __launch_bounds__(CMP_WARPS * 32, 8)
 khq_compress_kernel(const __half* __restrict__ x, const __half* __restrict__ d_vec,
                     const __half* __restrict__ rotor, const __half* __restrict__ cents,
                     const __half* __restrict__ vq, unsigned int* __restrict__ out_mask,
