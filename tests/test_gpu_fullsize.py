@@ -270,6 +270,63 @@ def test_compress_rows_are_independent_at_prompt_size(cuda_ops):
     assert torch.isfinite(full["k_norms"].float()).all() and torch.isfinite(full["v_norms"].float()).all()
 
 
+def test_compress_grouped_rows_ragged_tail_and_run_table(cuda_ops):
+    """Large V launches carry four rows per warp through the code search.  A row count that is not
+    a multiple of four (32 768 + 3 rows) and a table-driven launch of 65 runs of 512 rows (33 280
+    rows, sources scattered) must write, row for row, what small launches (one row per warp) write."""
+    import torch
+
+    tb, tab = _tables(torch)
+    rows = 32768 + 3
+    g = torch.Generator(device="cuda").manual_seed(17)
+    k = torch.randn(rows, D, generator=g, device="cuda").half()
+    v = torch.randn(rows, D, generator=g, device="cuda").half()
+    full = _compress_all(cuda_ops, torch, tb, tab, k, v, rows)
+    per_row = dict(k_mask=64, k_payload=40, v_payload=104, v_shared_meta=4, k_norms=2, k_r_norms=2, v_norms=2, v_r_norms=2)
+    for a, n in ((rows - 515, 515), (0, 509), (16384, 1024)):
+        part = _compress_all(cuda_ops, torch, tb, tab, k[a:a + n].contiguous(), v[a:a + n].contiguous(), n)
+        for key, rb in per_row.items():
+            assert torch.equal(full[key].view(torch.uint8)[a * rb:(a + n) * rb], part[key].view(torch.uint8)), (key, a)
+
+    # table-driven launch: run i reads 512 rows from a shuffled place in the source and writes rows
+    # 512*perm2[i] ..; V sources sit at a fixed byte distance from the K sources
+    lib = cuda_ops.lib
+    n_seg, rps = 65, 512
+    src = torch.randn(2, n_seg * rps, D, generator=g, device="cuda").half()  # [0] = K rows, [1] = V rows
+    rng = np.random.default_rng(3)
+    perm_src, perm_dst = rng.permutation(n_seg), rng.permutation(n_seg)
+    segs = np.zeros((n_seg, 2), dtype=np.int64)
+    for i in range(n_seg):
+        segs[i, 0] = src[0].data_ptr() + int(perm_src[i]) * rps * D * 2
+        segs[i, 1] = int(perm_dst[i]) * rps
+    d_segs = torch.from_numpy(segs).cuda()
+    total = n_seg * rps
+    out = dict(k_mask=torch.zeros(total * 16, dtype=torch.int32, device="cuda"),
+               k_payload=torch.zeros(total * 40, dtype=torch.uint8, device="cuda"),
+               v_payload=torch.zeros(total * 104, dtype=torch.uint8, device="cuda"),
+               v_shared_meta=torch.zeros(total * 4, dtype=torch.uint8, device="cuda"),
+               k_norms=torch.zeros(total, dtype=torch.float16, device="cuda"), k_r_norms=torch.zeros(total, dtype=torch.float16, device="cuda"),
+               v_norms=torch.zeros(total, dtype=torch.float16, device="cuda"), v_r_norms=torch.zeros(total, dtype=torch.float16, device="cuda"))
+    st = torch.cuda.current_stream().cuda_stream
+    rc = lib.launch_khq_compress_batched_fp16(
+        d_segs.data_ptr(), n_seg, rps, tab["d_k"].data_ptr(), tab["rotor_k"].data_ptr(), tab["cents_k"].data_ptr(),
+        tab["cents_k"].data_ptr(), out["k_mask"].data_ptr(), out["k_norms"].data_ptr(), out["k_r_norms"].data_ptr(),
+        out["k_payload"].data_ptr(), out["v_shared_meta"].data_ptr(), D, float(tb.ts_k), float(tb.alpha_k), 0, 0, st)
+    assert rc == 0
+    rc = lib.launch_khq_compress_batched_fp16(
+        d_segs.data_ptr(), n_seg, rps, tab["d_v"].data_ptr(), tab["rotor_v"].data_ptr(), tab["cents_v"].data_ptr(),
+        tab["vq"].data_ptr(), out["k_mask"].data_ptr(), out["v_norms"].data_ptr(), out["v_r_norms"].data_ptr(),
+        out["v_payload"].data_ptr(), out["v_shared_meta"].data_ptr(), D, float(tb.ts_v), float(tb.alpha_v), 1,
+        src[1].data_ptr() - src[0].data_ptr(), st)
+    assert rc == 0
+    torch.cuda.synchronize()
+    for i in (0, 7, 64):
+        a, b = int(perm_src[i]) * rps, int(perm_dst[i]) * rps
+        part = _compress_all(cuda_ops, torch, tb, tab, src[0, a:a + rps].contiguous(), src[1, a:a + rps].contiguous(), rps)
+        for key, rb in per_row.items():
+            assert torch.equal(out[key].view(torch.uint8)[b * rb:(b + rps) * rb], part[key].view(torch.uint8)), (key, i)
+
+
 def test_long_context_split_invariance(cuda_ops):
     """131 072 compressed tokens (configs[2]): the merged attention must not depend on how the
     context is cut -- 1, 8 or 32 splits in one launch, or four launches over context quarters
