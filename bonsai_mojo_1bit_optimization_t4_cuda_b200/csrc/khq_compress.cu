@@ -17,7 +17,9 @@ namespace khq {
 
 constexpr int CMP_WARPS = 4;  // warps per block, each on its own row (K) or group of rows (V)
 constexpr int CMP_VROWS = 4;  // rows a warp carries through the V code search together (large launches)
-constexpr long long CMP_VROWS_MIN_N = 32768;  // below this a V launch keeps one row per warp (latency)
+// Below this a V launch keeps one row per warp: groups of four would leave SMs without work
+// (148 SMs x 8 blocks x 4 warps x 4 rows = 18 944 rows fill the GPU once).
+constexpr long long CMP_VROWS_MIN_N = 24576;
 
 // One run of rows of a batched launch: source rows (fp16, D per row, contiguous) and the first
 // output row in the launch's output arrays (mirrored in include/khq_b200.h).
