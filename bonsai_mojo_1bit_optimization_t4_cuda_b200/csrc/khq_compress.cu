@@ -38,9 +38,12 @@ struct CompressScratch {
 
 template <int R>
 struct CompressScratchV {
-    float p[R][D];               // x as float, then the rotated projection, per row of the group
-    float a[NP];                 // per-patch true energies of the row in the epilogue
-    float b[NP];                 // per-patch codebook energies
+    // Row strides of D + 4 and NP + 4 floats: the in-order sums read four rows at once (lane l
+    // follows row l % R), and the odd multiple of 16 bytes keeps those four 16-byte reads on
+    // different banks.
+    float p[R][D + 4];           // x as float, then the rotated projection, per row of the group
+    float a[R][NP + 4];          // per-patch true energies
+    float b[R][NP + 4];          // per-patch codebook energies
     unsigned short code[R][NP];  // chosen code per (row, patch)
 };
 
@@ -55,6 +58,40 @@ __device__ __forceinline__ const __half* compress_map_row(const __half* x, const
     const long long rr = lrow % rows_per_seg;
     row = sg.row0 + rr;
     return reinterpret_cast<const __half*>(reinterpret_cast<const char*>(sg.x) + x_byte_offset) + rr * D;
+}
+
+// Normalisation, FWHT-256 and the 4x4 rotor of one row whose norm is known; lane owns dims
+// 8*lane .. 8*lane+7 (xv).
+__device__ __forceinline__ void compress_rotate(const float (&xv)[8], float norm,
+                                                const __half* __restrict__ d_vec,
+                                                const __half* __restrict__ rotor, float f_s, int lane,
+                                                float (&proj)[8]) {
+    const float den = norm + 1e-8f;
+
+    const uint4 draw = *reinterpret_cast<const uint4*>(d_vec + lane * 8);
+    const __half* hd = reinterpret_cast<const __half*>(&draw);
+    float r[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = __fdiv_rn(xv[j] * __half2float(hd[j]), den);
+    fwht256_lane8(r, lane);
+
+    // 4x4 rotor of the lane's two patches: rot[c] = sum_k r[k] * R[k][c], k ascending
+#pragma unroll
+    for (int p = 0; p < 2; ++p) {
+        const uint4* rp = reinterpret_cast<const uint4*>(rotor + (lane * 2 + p) * 16);
+        const uint4 r0 = rp[0], r1 = rp[1];
+        __half hr[16];
+        *reinterpret_cast<uint4*>(&hr[0]) = r0;
+        *reinterpret_cast<uint4*>(&hr[8]) = r1;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            float acc = 0.0f;
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                acc = __fmaf_rn(r[p * 4 + k], __half2float(hr[k * 4 + c]), acc);
+            proj[p * 4 + c] = acc * f_s;
+        }
+    }
 }
 
 // Norm, normalisation, FWHT-256 and the 4x4 rotor of one row; lane owns dims 8*lane .. 8*lane+7.
@@ -84,34 +121,8 @@ __device__ __forceinline__ void compress_front(const __half* __restrict__ xrow,
     }
     __syncwarp();
     norm = sqrtf(sum_sq + 1e-8f);
-    const float den = norm + 1e-8f;
-
-    const uint4 draw = *reinterpret_cast<const uint4*>(d_vec + lane * 8);
-    const __half* hd = reinterpret_cast<const __half*>(&draw);
-    float r[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) r[j] = __fdiv_rn(xv[j] * __half2float(hd[j]), den);
-    fwht256_lane8(r, lane);
-
-    // 4x4 rotor of the lane's two patches: rot[c] = sum_k r[k] * R[k][c], k ascending
-#pragma unroll
-    for (int p = 0; p < 2; ++p) {
-        const uint4* rp = reinterpret_cast<const uint4*>(rotor + (lane * 2 + p) * 16);
-        const uint4 r0 = rp[0], r1 = rp[1];
-        __half hr[16];
-        *reinterpret_cast<uint4*>(&hr[0]) = r0;
-        *reinterpret_cast<uint4*>(&hr[8]) = r1;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            float acc = 0.0f;
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-                acc = __fmaf_rn(r[p * 4 + k], __half2float(hr[k * 4 + c]), acc);
-            proj[p * 4 + c] = acc * f_s;
-        }
-    }
+    compress_rotate(xv, norm, d_vec, rotor, f_s, lane, proj);
 }
-
 // =================================== K rows: one warp per row ===================================
 __global__ void __launch_bounds__(CMP_WARPS * 32, 8)
 khq_compress_k_kernel(const __half* __restrict__ x, const __half* __restrict__ d_vec,
@@ -316,9 +327,36 @@ khq_compress_v_kernel(const __half* __restrict__ x, const __half* __restrict__ d
         for (int r = 0; r < nr; ++r) {
             long long row;
             const __half* xrow = compress_map_row(x, segs, rows_per_seg, x_byte_offset, l0 + r, row);
-            float proj[8], norm;
-            compress_front(xrow, d_vec, rotor, f_s, lane, S.p[r], proj, norm);
+            const uint4 raw = *reinterpret_cast<const uint4*>(xrow + lane * 8);
+            const __half2* hx = reinterpret_cast<const __half2*>(&raw);
+            const float2 x0 = __half22float2(hx[0]), x1 = __half22float2(hx[1]), x2 = __half22float2(hx[2]),
+                         x3 = __half22float2(hx[3]);
+            *reinterpret_cast<float4*>(&S.p[r][lane * 8]) = make_float4(x0.x, x0.y, x1.x, x1.y);
+            *reinterpret_cast<float4*>(&S.p[r][lane * 8 + 4]) = make_float4(x2.x, x2.y, x3.x, x3.y);
+        }
+        __syncwarp();
+        // sums of squares strictly in dim order, the R rows at once: lane l follows row l % R
+        const int cr = lane & (R - 1);
+        float sum_sq = 0.0f;
+#pragma unroll 8
+        for (int i = 0; i < D; i += 4) {
+            const float4 t = *reinterpret_cast<const float4*>(&S.p[cr][i]);
+            sum_sq = __fmaf_rn(t.x, t.x, sum_sq);
+            sum_sq = __fmaf_rn(t.y, t.y, sum_sq);
+            sum_sq = __fmaf_rn(t.z, t.z, sum_sq);
+            sum_sq = __fmaf_rn(t.w, t.w, sum_sq);
+        }
+        __syncwarp();
+#pragma unroll 1
+        for (int r = 0; r < nr; ++r) {
+            long long row;
+            (void)compress_map_row(x, segs, rows_per_seg, x_byte_offset, l0 + r, row);
+            const float norm = sqrtf(__shfl_sync(0xFFFFFFFFu, sum_sq, r) + 1e-8f);
             if (lane == 0) out_norms[row] = __float2half(norm);
+            float xv[8], proj[8];
+            *reinterpret_cast<float4*>(&xv[0]) = *reinterpret_cast<const float4*>(&S.p[r][lane * 8]);
+            *reinterpret_cast<float4*>(&xv[4]) = *reinterpret_cast<const float4*>(&S.p[r][lane * 8 + 4]);
+            compress_rotate(xv, norm, d_vec, rotor, f_s, lane, proj);
             *reinterpret_cast<float4*>(&S.p[r][lane * 8]) = make_float4(proj[0], proj[1], proj[2], proj[3]);
             *reinterpret_cast<float4*>(&S.p[r][lane * 8 + 4]) = make_float4(proj[4], proj[5], proj[6], proj[7]);
         }
@@ -418,8 +456,8 @@ khq_compress_v_kernel(const __half* __restrict__ x, const __half* __restrict__ d
             const float cbest = s ? c1 : c0;
             pres[p] = __fmaf_rn(-cbest, alpha, v3);
             max_res = fmaxf(max_res, fabsf(pres[p]));
-            S.a[pid] = e_true[p];
-            S.b[pid] = e_vq[p];
+            S.a[r][pid] = e_true[p];
+            S.b[r][pid] = e_vq[p];
         }
 #pragma unroll
         for (int m = 16; m > 0; m >>= 1)
@@ -446,21 +484,25 @@ khq_compress_v_kernel(const __half* __restrict__ x, const __half* __restrict__ d
         const unsigned lo = __reduce_or_sync(0xFFFFFFFFu, lane < 16 ? hv : 0u);
         const unsigned hi = __reduce_or_sync(0xFFFFFFFFu, lane >= 16 ? hv : 0u);
         if (lane == 0) { prow[24] = lo; prow[25] = hi; }
+        }
         __syncwarp();
+        // the two energy sums strictly in patch order, the R rows at once
         float st = 0.0f, sv = 0.0f;
 #pragma unroll 4
         for (int i = 0; i < NP; i += 4) {
-            const float4 ta = *reinterpret_cast<const float4*>(&S.a[i]);
-            const float4 tb = *reinterpret_cast<const float4*>(&S.b[i]);
+            const float4 ta = *reinterpret_cast<const float4*>(&S.a[cr][i]);
+            const float4 tb = *reinterpret_cast<const float4*>(&S.b[cr][i]);
             st += ta.x; sv += tb.x;
             st += ta.y; sv += tb.y;
             st += ta.z; sv += tb.z;
             st += ta.w; sv += tb.w;
         }
-        if (lane == 0)
+        if (lane < nr) {
+            long long row;
+            (void)compress_map_row(x, segs, rows_per_seg, x_byte_offset, l0 + lane, row);
             out_r_norms[row] = __float2half(sqrtf(__fdiv_rn(st, sv + 1e-8f)));
-        __syncwarp();
         }
+        __syncwarp();
     }
 }
 
