@@ -426,6 +426,23 @@ struct M2State {
     }
 };
 
+// Packed pairs of fp32 (one instruction for two neighbouring accumulator registers; each half is
+// rounded like the scalar operation).
+__device__ __forceinline__ void m2_add2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+    asm("{.reg .b64 a, b, d; mov.b64 a, {%2, %3}; mov.b64 b, {%4, %5}; add.rn.f32x2 d, a, b; mov.b64 {%0, %1}, d;}"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+__device__ __forceinline__ void m2_sub2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+    asm("{.reg .b64 a, b, d; mov.b64 a, {%2, %3}; mov.b64 b, {%4, %5}; sub.rn.f32x2 d, a, b; mov.b64 {%0, %1}, d;}"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+__device__ __forceinline__ void m2_fma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0,
+                                        float c1) {
+    asm("{.reg .b64 a, b, c, d; mov.b64 a, {%2, %3}; mov.b64 b, {%4, %5}; mov.b64 c, {%6, %7};"
+        " fma.rn.f32x2 d, a, b, c; mov.b64 {%0, %1}, d;}"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+
 // One block of 16 tokens (rows r0..r0+15 of the staged tile) of kv-head `kvh`.
 // valid_lo/valid_hi: block-relative range of tokens that belong to the caller's range.
 __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, const unsigned char* __restrict__ smem,
@@ -509,10 +526,9 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
             m2_mma(cur, ax, rr[2], rr[3]);
             m2_mma_lo(cur, ax, rr[6], rr[7]);
             if (s & 1) {
-                cu[s >> 1][0] = fmaf(ratio[0], cur[0], cu[s >> 1][0]);
-                cu[s >> 1][1] = fmaf(ratio[0], cur[1], cu[s >> 1][1]);
-                cu[s >> 1][2] = fmaf(ratio[1], cur[2], cu[s >> 1][2]);
-                cu[s >> 1][3] = fmaf(ratio[1], cur[3], cu[s >> 1][3]);
+                float* c = cu[s >> 1];
+                m2_fma2(c[0], c[1], ratio[0], ratio[0], cur[0], cur[1], c[0], c[1]);
+                m2_fma2(c[2], c[3], ratio[1], ratio[1], cur[2], cur[3], c[2], c[3]);
             }
         }
     }
@@ -527,10 +543,10 @@ __device__ __forceinline__ void m2_block(const unsigned char* __restrict__ S, co
             for (int j = 0; j < 8; ++j)
                 if ((j & m) == 0)
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float a = cu[j][e], b = cu[j | m][e];
-                        cu[j][e] = a + b;
-                        cu[j | m][e] = a - b;
+                    for (int e = 0; e < 4; e += 2) {
+                        const float a0 = cu[j][e], a1 = cu[j][e + 1], b0 = cu[j | m][e], b1 = cu[j | m][e + 1];
+                        m2_add2(cu[j][e], cu[j][e + 1], a0, a1, b0, b1);
+                        m2_sub2(cu[j | m][e], cu[j | m][e + 1], a0, a1, b0, b1);
                     }
         // scale by dinv, rotate pairs (idx, idx + 32) = tiles (j, j + 4)
 #pragma unroll
