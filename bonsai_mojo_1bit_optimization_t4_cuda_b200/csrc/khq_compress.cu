@@ -16,8 +16,9 @@
 namespace khq {
 
 constexpr int CMP_WARPS = 4;  // warps per block, each on its own row (K) or group of rows (V)
+constexpr int CMP_KROWS = 2;  // rows of a K group (large launches); four would halve the blocks per SM
 constexpr int CMP_VROWS = 4;  // rows a warp carries through the V code search together (large launches)
-// Below this a V launch keeps one row per warp: groups of four would leave SMs without work
+// Below this a launch keeps one row per warp: groups of rows would leave SMs without work
 // (148 SMs x 8 blocks x 4 warps x 4 rows = 18 944 rows fill the GPU once).
 constexpr long long CMP_VROWS_MIN_N = 24576;
 
@@ -29,18 +30,20 @@ struct KhqCompressSeg {
 };
 static_assert(sizeof(KhqCompressSeg) == 16, "ABI");
 
-struct CompressScratch {
-    float a[D];             // x as float, then per-dim |proj| contributions
-    float b[D];             // per-dim centroid contributions
+// Row strides of D + 4 (and NP + 4) floats: the in-order sums read R rows at once (lane l
+// follows row l % R), and the odd multiple of 16 bytes keeps those 16-byte reads on different banks.
+template <int R>
+struct CompressScratchK {
+    float a[R][D + 4];      // x as float, then per-dim |proj| contributions
+    float b[R][D + 4];      // per-dim centroid contributions
+    float q[R][D];          // the rotated projection
+    int incl[R][32];        // per lane: outlier candidates up to and including the lane's dims
     unsigned char oc[64];   // outlier 4-bit codes, by outlier ordinal
     unsigned char os[64];   // outlier sign flags, by outlier ordinal
 };
 
 template <int R>
 struct CompressScratchV {
-    // Row strides of D + 4 and NP + 4 floats: the in-order sums read four rows at once (lane l
-    // follows row l % R), and the odd multiple of 16 bytes keeps those four 16-byte reads on
-    // different banks.
     float p[R][D + 4];           // x as float, then the rotated projection, per row of the group
     float a[R][NP + 4];          // per-patch true energies
     float b[R][NP + 4];          // per-patch codebook energies
@@ -94,36 +97,12 @@ __device__ __forceinline__ void compress_rotate(const float (&xv)[8], float norm
     }
 }
 
-// Norm, normalisation, FWHT-256 and the 4x4 rotor of one row; lane owns dims 8*lane .. 8*lane+7.
-// `stage` is 256 floats of the warp's shared memory, free again on return.
-__device__ __forceinline__ void compress_front(const __half* __restrict__ xrow,
-                                               const __half* __restrict__ d_vec,
-                                               const __half* __restrict__ rotor, float f_s, int lane,
-                                               float* stage, float (&proj)[8], float& norm) {
-    const uint4 raw = *reinterpret_cast<const uint4*>(xrow + lane * 8);
-    const __half* hx = reinterpret_cast<const __half*>(&raw);
-    float xv[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        xv[j] = __half2float(hx[j]);
-        stage[lane * 8 + j] = xv[j];
-    }
-    __syncwarp();
-    // sum of squares strictly in dim order (every lane computes the same chain)
-    float sum_sq = 0.0f;
-#pragma unroll 8
-    for (int i = 0; i < D; i += 4) {
-        const float4 t = *reinterpret_cast<const float4*>(&stage[i]);
-        sum_sq = __fmaf_rn(t.x, t.x, sum_sq);
-        sum_sq = __fmaf_rn(t.y, t.y, sum_sq);
-        sum_sq = __fmaf_rn(t.z, t.z, sum_sq);
-        sum_sq = __fmaf_rn(t.w, t.w, sum_sq);
-    }
-    __syncwarp();
-    norm = sqrtf(sum_sq + 1e-8f);
-    compress_rotate(xv, norm, d_vec, rotor, f_s, lane, proj);
-}
-// =================================== K rows: one warp per row ===================================
+// ============ K rows: a warp takes a group of R rows; their in-order sums run side by side ============
+// The three order-sensitive sums of a K row (256 squares, then the two conditional 256-term sums
+// behind the base multiplier) are dependent chains that every lane of the warp would compute
+// alike; with R rows per warp lane l follows row l % R, so one pass over shared memory serves R
+// rows.  Between the passes a row's projection and outlier ordinals wait in shared memory.
+template <int R>
 __global__ void __launch_bounds__(CMP_WARPS * 32, 8)
 khq_compress_k_kernel(const __half* __restrict__ x, const __half* __restrict__ d_vec,
                       const __half* __restrict__ rotor, const __half* __restrict__ cents,
@@ -132,150 +111,205 @@ khq_compress_k_kernel(const __half* __restrict__ x, const __half* __restrict__ d
                       unsigned char* __restrict__ out_shared_meta, int d_val, int n, float ts,
                       const KhqCompressSeg* __restrict__ segs, int rows_per_seg,
                       long long x_byte_offset) {
-    __shared__ CompressScratch scratch[CMP_WARPS];
+    __shared__ __align__(16) CompressScratchK<R> scratch[CMP_WARPS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    CompressScratch& S = scratch[warp];
+    CompressScratchK<R>& S = scratch[warp];
     // The reference computes this factor at run time from the dimension argument.
     const float f_s = rsqrtf((float)d_val);
-
-    for (long long lrow = (long long)blockIdx.x * CMP_WARPS + warp; lrow < n;
-         lrow += (long long)gridDim.x * CMP_WARPS) {
-        long long row;
-        const __half* xrow = compress_map_row(x, segs, rows_per_seg, x_byte_offset, lrow, row);
-        float proj[8], norm;
-        compress_front(xrow, d_vec, rotor, f_s, lane, S.a, proj, norm);
-        if (lane == 0) out_norms[row] = __float2half(norm);
-
-        const float th_out = 1.60f * f_s, th_lo = 0.47f * f_s;
+    const float th_out = 1.60f * f_s, th_lo = 0.47f * f_s;
+    const long long n_groups = ((long long)n + R - 1) / R;
+    const int cr = lane & (R - 1);
+    float cb[8];  // the lane's 8 dims of the centroid row the base multiplier is fitted to
+    {
         const uint4 craw = *reinterpret_cast<const uint4*>(cents + 2 * D + lane * 8);
         const __half* hc = reinterpret_cast<const __half*>(&craw);
-        float cb[8];
-        unsigned cand = 0;  // dims whose |proj| is above the outlier threshold
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            cb[j] = __half2float(hc[j]);
-            if (fabsf(proj[j]) > th_out) cand |= 1u << j;
-        }
-        // ordinal of the lane's first candidate among all candidates, in dim order
-        const int cnt = __popc(cand);
-        int incl = cnt;
-#pragma unroll
-        for (int dlt = 1; dlt < 32; dlt <<= 1) {
-            const int t = __shfl_up_sync(0xFFFFFFFFu, incl, dlt);
-            if (lane >= dlt) incl += t;
-        }
-        int ord = incl - cnt;
-        const int total_cand = __shfl_sync(0xFFFFFFFFu, incl, 31);
-        const int n_out = total_cand < MAX_OUT ? total_cand : MAX_OUT;
+        for (int j = 0; j < 8; ++j) cb[j] = __half2float(hc[j]);
+    }
 
-        unsigned sym16 = 0;
-        float o_abs[8];
-        int o_ord[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const float pj = proj[j];
-            const float ap = fabsf(pj);
-            unsigned sym;
-            float cn = 0.0f, cc = 0.0f;
-            o_ord[j] = -1;
-            o_abs[j] = 0.0f;
-            if (cand & (1u << j)) {
-                if (ord < MAX_OUT) {
-                    sym = 3;
-                    o_ord[j] = ord;
-                    o_abs[j] = fabsf(pj * ts);
-                } else {
-                    sym = (pj > 0.0f) ? 2u : 1u;  // overflow outlier: not part of the sums
-                }
-                ++ord;
-            } else {
-                if (pj > th_lo) sym = 2;
-                else if (pj < -th_lo) sym = 1;
-                else sym = 0;
-                if (sym != 0) { cn = ap; cc = cb[j]; }
-            }
-            sym16 |= sym << (2 * j);
-            S.a[lane * 8 + j] = cn;  // adding +0.0f leaves a non-negative fp32 sum unchanged
-            S.b[lane * 8 + j] = cc;
+    for (long long grp = (long long)blockIdx.x * CMP_WARPS + warp; grp < n_groups;
+         grp += (long long)gridDim.x * CMP_WARPS) {
+        const long long l0 = grp * R;
+        const int nr = (n - l0 < R) ? (int)(n - l0) : R;
+        // ---- the rows as fp32 in shared memory, then their sums of squares in dim order ----------
+#pragma unroll 1
+        for (int r = 0; r < nr; ++r) {
+            long long row;
+            const __half* xrow = compress_map_row(x, segs, rows_per_seg, x_byte_offset, l0 + r, row);
+            const uint4 raw = *reinterpret_cast<const uint4*>(xrow + lane * 8);
+            const __half2* hx = reinterpret_cast<const __half2*>(&raw);
+            const float2 x0 = __half22float2(hx[0]), x1 = __half22float2(hx[1]), x2 = __half22float2(hx[2]),
+                         x3 = __half22float2(hx[3]);
+            *reinterpret_cast<float4*>(&S.a[r][lane * 8]) = make_float4(x0.x, x0.y, x1.x, x1.y);
+            *reinterpret_cast<float4*>(&S.a[r][lane * 8 + 4]) = make_float4(x2.x, x2.y, x3.x, x3.y);
         }
-        // mask word w = dims 16w..16w+15 = lanes 2w (low half) and 2w+1 (high half)
-        const unsigned hi16 = __shfl_down_sync(0xFFFFFFFFu, sym16, 1);
-        if ((lane & 1) == 0) out_mask[row * 16 + (lane >> 1)] = sym16 | (hi16 << 16);
         __syncwarp();
+        float sum_sq = 0.0f;
+#pragma unroll 8
+        for (int i = 0; i < D; i += 4) {
+            const float4 t = *reinterpret_cast<const float4*>(&S.a[cr][i]);
+            sum_sq = __fmaf_rn(t.x, t.x, sum_sq);
+            sum_sq = __fmaf_rn(t.y, t.y, sum_sq);
+            sum_sq = __fmaf_rn(t.z, t.z, sum_sq);
+            sum_sq = __fmaf_rn(t.w, t.w, sum_sq);
+        }
+        __syncwarp();
+        // ---- per row: projection, symbols, mask words, the terms of the two conditional sums ------
+#pragma unroll 1
+        for (int r = 0; r < nr; ++r) {
+            long long row;
+            (void)compress_map_row(x, segs, rows_per_seg, x_byte_offset, l0 + r, row);
+            const float norm = sqrtf(__shfl_sync(0xFFFFFFFFu, sum_sq, r) + 1e-8f);
+            if (lane == 0) out_norms[row] = __float2half(norm);
+            float xv[8], proj[8];
+            *reinterpret_cast<float4*>(&xv[0]) = *reinterpret_cast<const float4*>(&S.a[r][lane * 8]);
+            *reinterpret_cast<float4*>(&xv[4]) = *reinterpret_cast<const float4*>(&S.a[r][lane * 8 + 4]);
+            compress_rotate(xv, norm, d_vec, rotor, f_s, lane, proj);
+            *reinterpret_cast<float4*>(&S.q[r][lane * 8]) = make_float4(proj[0], proj[1], proj[2], proj[3]);
+            *reinterpret_cast<float4*>(&S.q[r][lane * 8 + 4]) = make_float4(proj[4], proj[5], proj[6], proj[7]);
+
+            unsigned cand = 0;  // dims whose |proj| is above the outlier threshold
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (fabsf(proj[j]) > th_out) cand |= 1u << j;
+            // ordinal of the lane's first candidate among all candidates, in dim order
+            const int cnt = __popc(cand);
+            int incl = cnt;
+#pragma unroll
+            for (int dlt = 1; dlt < 32; dlt <<= 1) {
+                const int t = __shfl_up_sync(0xFFFFFFFFu, incl, dlt);
+                if (lane >= dlt) incl += t;
+            }
+            S.incl[r][lane] = incl;
+            int ord = incl - cnt;
+
+            unsigned sym16 = 0;
+            float cn[8], cc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float pj = proj[j];
+                unsigned sym;
+                cn[j] = 0.0f;
+                cc[j] = 0.0f;
+                if (cand & (1u << j)) {
+                    // kept outlier, or overflow outlier (not part of the sums)
+                    sym = (ord < MAX_OUT) ? 3u : ((pj > 0.0f) ? 2u : 1u);
+                    ++ord;
+                } else {
+                    if (pj > th_lo) sym = 2;
+                    else if (pj < -th_lo) sym = 1;
+                    else sym = 0;
+                    if (sym != 0) { cn[j] = fabsf(pj); cc[j] = cb[j]; }
+                }
+                sym16 |= sym << (2 * j);
+            }
+            // adding +0.0f leaves a non-negative fp32 sum unchanged
+            *reinterpret_cast<float4*>(&S.a[r][lane * 8]) = make_float4(cn[0], cn[1], cn[2], cn[3]);
+            *reinterpret_cast<float4*>(&S.a[r][lane * 8 + 4]) = make_float4(cn[4], cn[5], cn[6], cn[7]);
+            *reinterpret_cast<float4*>(&S.b[r][lane * 8]) = make_float4(cc[0], cc[1], cc[2], cc[3]);
+            *reinterpret_cast<float4*>(&S.b[r][lane * 8 + 4]) = make_float4(cc[4], cc[5], cc[6], cc[7]);
+            // mask word w = dims 16w..16w+15 = lanes 2w (low half) and 2w+1 (high half)
+            const unsigned hi16 = __shfl_down_sync(0xFFFFFFFFu, sym16, 1);
+            if ((lane & 1) == 0) out_mask[row * 16 + (lane >> 1)] = sym16 | (hi16 << 16);
+        }
+        __syncwarp();
+        // ---- the two conditional sums in dim order, R rows side by side ------------------------
         float sum_n = 0.0f, sum_c = 0.0f;
 #pragma unroll 8
         for (int i = 0; i < D; i += 4) {
-            const float4 ta = *reinterpret_cast<const float4*>(&S.a[i]);
-            const float4 tb = *reinterpret_cast<const float4*>(&S.b[i]);
+            const float4 ta = *reinterpret_cast<const float4*>(&S.a[cr][i]);
+            const float4 tb = *reinterpret_cast<const float4*>(&S.b[cr][i]);
             sum_n += ta.x; sum_c += tb.x;
             sum_n += ta.y; sum_c += tb.y;
             sum_n += ta.z; sum_c += tb.z;
             sum_n += ta.w; sum_c += tb.w;
         }
-        __syncwarp();
-        float mult = (sum_c > 1e-5f) ? __fdiv_rn(sum_n, sum_c) : 1.0f;
-        if (mult < 0.1f || mult > 10.0f || isnan(mult)) mult = 1.0f;
+        float mult_own = (sum_c > 1e-5f) ? __fdiv_rn(sum_n, sum_c) : 1.0f;
+        if (mult_own < 0.1f || mult_own > 10.0f || isnan(mult_own)) mult_own = 1.0f;
+        // ---- per row: residuals of the kept outliers, their scale, the 40 payload bytes ----------
+#pragma unroll 1
+        for (int r = 0; r < nr; ++r) {
+            long long row;
+            (void)compress_map_row(x, segs, rows_per_seg, x_byte_offset, l0 + r, row);
+            const float mult = __shfl_sync(0xFFFFFFFFu, mult_own, r);
+            float proj[8];
+            *reinterpret_cast<float4*>(&proj[0]) = *reinterpret_cast<const float4*>(&S.q[r][lane * 8]);
+            *reinterpret_cast<float4*>(&proj[4]) = *reinterpret_cast<const float4*>(&S.q[r][lane * 8 + 4]);
+            unsigned cand = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (fabsf(proj[j]) > th_out) cand |= 1u << j;
+            int ord = S.incl[r][lane] - __popc(cand);
+            const int total_cand = S.incl[r][31];
+            const int n_out = total_cand < MAX_OUT ? total_cand : MAX_OUT;
 
-        float res[8];
-        float max_res = 0.0f;
+            float res[8];
+            int o_ord[8];
+            float max_res = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            res[j] = 0.0f;
-            if (o_ord[j] >= 0) {
-                res[j] = fmaxf(0.0f, __fmaf_rn(-cb[j], mult, o_abs[j]));
-                max_res = fmaxf(max_res, res[j]);
-            }
-        }
-#pragma unroll
-        for (int m = 16; m > 0; m >>= 1)
-            max_res = fmaxf(max_res, __shfl_xor_sync(0xFFFFFFFFu, max_res, m));
-        const float rscale = (n_out > 0) ? __fdiv_rn(fmaxf(max_res, 1e-4f), 15.0f) : 0.0f;
-        if (lane == 0) {
-            out_r_norms[row] = __float2half(rscale);
-            *reinterpret_cast<unsigned int*>(out_shared_meta + row * 4) = 0u;
-        }
-        // stage codes and signs by ordinal, then assemble the 40 payload bytes
-        if (lane < 16) reinterpret_cast<unsigned int*>(S.oc)[lane] = 0u;
-        else reinterpret_cast<unsigned int*>(S.os)[lane - 16] = 0u;
-        __syncwarp();
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            if (o_ord[j] >= 0) {
-                unsigned char code = 0;
-                if (rscale > 0.0f) {
-                    const float r4 = roundf(__fdiv_rn(res[j], rscale));
-                    code = (unsigned char)fmaxf(0.0f, fminf(15.0f, r4));
+            for (int j = 0; j < 8; ++j) {
+                res[j] = 0.0f;
+                o_ord[j] = -1;
+                if (cand & (1u << j)) {
+                    if (ord < MAX_OUT) {
+                        o_ord[j] = ord;
+                        res[j] = fmaxf(0.0f, __fmaf_rn(-cb[j], mult, fabsf(proj[j] * ts)));
+                        max_res = fmaxf(max_res, res[j]);
+                    }
+                    ++ord;
                 }
-                S.oc[o_ord[j]] = code;
-                S.os[o_ord[j]] = (proj[j] > 0.0f) ? 1 : 0;
             }
-        }
-        __syncwarp();
-        if (lane < 10) {
-            unsigned int word = 0;
 #pragma unroll
-            for (int bb = 0; bb < 4; ++bb) {
-                const int byte = lane * 4 + bb;
-                unsigned int v = 0;
-                if (byte < 4) {
-                    const unsigned int mu = (unsigned int)(mult * 1000.0f);
-                    v = (mu >> (8 * byte)) & 0xFFu;
-                } else if (byte < 29) {
-                    const int j0 = (byte - 4) * 2;
-                    v = (unsigned)S.oc[j0] | ((unsigned)S.oc[j0 + 1] << 4);
-                } else if (byte < 36) {
-                    const int j0 = (byte - 29) * 8;
+            for (int m = 16; m > 0; m >>= 1)
+                max_res = fmaxf(max_res, __shfl_xor_sync(0xFFFFFFFFu, max_res, m));
+            const float rscale = (n_out > 0) ? __fdiv_rn(fmaxf(max_res, 1e-4f), 15.0f) : 0.0f;
+            if (lane == 0) {
+                out_r_norms[row] = __float2half(rscale);
+                *reinterpret_cast<unsigned int*>(out_shared_meta + row * 4) = 0u;
+            }
+            // stage codes and signs by ordinal, then assemble the 40 payload bytes
+            if (lane < 16) reinterpret_cast<unsigned int*>(S.oc)[lane] = 0u;
+            else reinterpret_cast<unsigned int*>(S.os)[lane - 16] = 0u;
+            __syncwarp();
 #pragma unroll
-                    for (int t = 0; t < 8; ++t)
-                        if (j0 + t < MAX_OUT) v |= (unsigned)S.os[j0 + t] << t;
-                } else if (byte == 36) {
-                    v = 0x02u;
+            for (int j = 0; j < 8; ++j) {
+                if (o_ord[j] >= 0) {
+                    unsigned char code = 0;
+                    if (rscale > 0.0f) {
+                        const float r4 = roundf(__fdiv_rn(res[j], rscale));
+                        code = (unsigned char)fmaxf(0.0f, fminf(15.0f, r4));
+                    }
+                    S.oc[o_ord[j]] = code;
+                    S.os[o_ord[j]] = (proj[j] > 0.0f) ? 1 : 0;
                 }
-                word |= v << (8 * bb);
             }
-            reinterpret_cast<unsigned int*>(out_payload + row * K_PAY)[lane] = word;
+            __syncwarp();
+            if (lane < 10) {
+                unsigned int word = 0;
+#pragma unroll
+                for (int bb = 0; bb < 4; ++bb) {
+                    const int byte = lane * 4 + bb;
+                    unsigned int v = 0;
+                    if (byte < 4) {
+                        const unsigned int mu = (unsigned int)(mult * 1000.0f);
+                        v = (mu >> (8 * byte)) & 0xFFu;
+                    } else if (byte < 29) {
+                        const int j0 = (byte - 4) * 2;
+                        v = (unsigned)S.oc[j0] | ((unsigned)S.oc[j0 + 1] << 4);
+                    } else if (byte < 36) {
+                        const int j0 = (byte - 29) * 8;
+#pragma unroll
+                        for (int t = 0; t < 8; ++t)
+                            if (j0 + t < MAX_OUT) v |= (unsigned)S.os[j0 + t] << t;
+                    } else if (byte == 36) {
+                        v = 0x02u;
+                    }
+                    word |= v << (8 * bb);
+                }
+                reinterpret_cast<unsigned int*>(out_payload + row * K_PAY)[lane] = word;
+            }
+            __syncwarp();
         }
-        __syncwarp();
     }
 }
 
@@ -527,8 +561,12 @@ int compress_launch(const __half* x, const void* d_vec, const void* rotor, const
     __half* orn = static_cast<__half*>(out_r_norms);
     unsigned char* op = static_cast<unsigned char*>(out_payload);
     unsigned char* om = static_cast<unsigned char*>(out_shared_meta);
-    if (!is_v) {
-        khq_compress_k_kernel<<<grid(n), CMP_WARPS * 32, 0, stream>>>(
+    if (!is_v && n >= CMP_VROWS_MIN_N) {
+        khq_compress_k_kernel<CMP_KROWS><<<grid(((long long)n + CMP_KROWS - 1) / CMP_KROWS), CMP_WARPS * 32, 0,
+                                           stream>>>(x, dv, ro, ce, static_cast<unsigned int*>(out_mask), on, orn, op,
+                                                     om, d, n, threshold_scale, segs, rows_per_seg, x_byte_offset);
+    } else if (!is_v) {
+        khq_compress_k_kernel<1><<<grid(n), CMP_WARPS * 32, 0, stream>>>(
             x, dv, ro, ce, static_cast<unsigned int*>(out_mask), on, orn, op, om, d, n, threshold_scale, segs,
             rows_per_seg, x_byte_offset);
     } else if (n >= CMP_VROWS_MIN_N) {
