@@ -1,4 +1,5 @@
-// khq_compress.cu -- KHQ compress for sm_100a: one warp per (token, kv-head) row.
+// khq_compress.cu -- KHQ compress for sm_100a: one warp per (token, kv-head) row, or per group of
+// two (K) or four (V) rows in large launches.
 //
 // Code words must be bit-identical to the reference kernel's, which evaluates every row in one
 // thread in a fixed fp32 order.  The work is therefore split in two kinds:
@@ -8,14 +9,15 @@
 //     minimum == first strict minimum of an ascending scan), max reductions, bit packing;
 //   * the few order-sensitive scalar sums (sum of squares over 256 dims, the two conditional
 //     sums behind the K base multiplier, the two 64-term energy sums of V) are staged in shared
-//     memory and accumulated strictly in index order.
+//     memory and accumulated strictly in index order; with a group of R rows lane l follows the
+//     chain of row l % R, so one pass serves R rows.
 // Arithmetic that feeds a threshold or a rounding is written with explicit __fmaf_rn where the
 // reference's build (default -fmad=true) fuses a multiply into the following add/subtract.
 #include "khq_common.cuh"
 
 namespace khq {
 
-constexpr int CMP_WARPS = 4;  // warps per block, each on its own row (K) or group of rows (V)
+constexpr int CMP_WARPS = 4;  // warps per block, each on its own row or group of rows
 constexpr int CMP_KROWS = 2;  // rows of a K group (large launches); four would halve the blocks per SM
 constexpr int CMP_VROWS = 4;  // rows a warp carries through the V code search together (large launches)
 // Below this a launch keeps one row per warp: groups of rows would leave SMs without work

@@ -271,7 +271,8 @@ def test_compress_rows_are_independent_at_prompt_size(cuda_ops):
 
 
 def test_compress_grouped_rows_ragged_tail_and_run_table(cuda_ops):
-    """Large V launches carry four rows per warp through the code search.  A row count that is not
+    """Large launches give a warp a group of rows (two K rows, four V rows: the in-order sums of the
+    group run side by side, the V code search shares one codebook load).  A row count that is not
     a multiple of four (32 768 + 3 rows) and a table-driven launch of 65 runs of 512 rows (33 280
     rows, sources scattered) must write, row for row, what small launches (one row per warp) write."""
     import torch
