@@ -336,6 +336,40 @@ __device__ __forceinline__ unsigned long long f2_mul(unsigned long long a, unsig
     return r;
 }
 
+// Code search of one (row, patch): every lane scans its 8 consecutive codes in ascending order, then
+// the warp takes the lexicographic (distance, index) minimum.  cc[k][i] = (code 2i, code 2i+1) of
+// dim k of the lane's 8 codes, as packed fp32 pairs.
+__device__ __forceinline__ void v_search_row(const float* __restrict__ proj_row, unsigned short* __restrict__ code_row,
+                                             int p, const unsigned long long (&cc)[3][4],
+                                             unsigned long long nalpha2, int lane) {
+    const float4 v = *reinterpret_cast<const float4*>(&proj_row[p * 4]);
+    const unsigned long long v0 = f2_pack(v.x, v.x), v1 = f2_pack(v.y, v.y), v2 = f2_pack(v.z, v.z);
+    float best = 1e20f;
+    unsigned bl = 0;  // index among the lane's 8 codes
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        // d = v - c * alpha with one rounding (c * -alpha is the exact negative of c * alpha),
+        // dist = d2*d2 + (d0*d0 + d1*d1) in the reference's order
+        const unsigned long long d0 = f2_fma(cc[0][i], nalpha2, v0);
+        const unsigned long long d1 = f2_fma(cc[1][i], nalpha2, v1);
+        const unsigned long long d2 = f2_fma(cc[2][i], nalpha2, v2);
+        const unsigned long long dd = f2_fma(d2, d2, f2_fma(d0, d0, f2_mul(d1, d1)));
+        float da, db;
+        f2_unpack(dd, da, db);
+        if (da < best) { best = da; bl = 2 * i; }
+        if (db < best) { best = db; bl = 2 * i + 1; }
+    }
+    // warp minimum of (distance, index): a lane's best is a non-negative, non-NaN float (it starts
+    // at 1e20 and only a strictly smaller distance replaces it), so its bit pattern orders like
+    // the value and two hardware warp reductions do the work of five shuffle-and-compare steps
+    const unsigned best_bits = __reduce_min_sync(0xFFFFFFFFu, __float_as_uint(best));
+    unsigned bi = __reduce_min_sync(0xFFFFFFFFu, (__float_as_uint(best) == best_bits) ? (unsigned)(lane * 8) + bl : 0xFFFFFFFFu);
+    // The reference starts from min=1e20 with a strict '<': if no distance is below 1e20
+    // (NaN/inf input) it keeps code 0.
+    if (!(__uint_as_float(best_bits) < 1e20f)) bi = 0;
+    if (lane == 0) code_row[p] = (unsigned short)bi;
+}
+
 // ============ V rows: a warp takes R rows through the code search on one codebook load ============
 // The search dominates a V row (64 patches x 256 codes); the codebook slice a lane scans (8 codes
 // of the patch) is loaded and converted once per patch and used for the R rows of the group.
@@ -415,38 +449,12 @@ khq_compress_v_kernel(const __half* __restrict__ x, const __half* __restrict__ d
 #pragma unroll
                 for (int k = 0; k < 3; ++k)
                     cc[k][i] = f2_pack(__half2float(hcb[6 * i + k]), __half2float(hcb[6 * i + 3 + k]));
+            if (nr == R) {
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                if (r < nr) {  // the same for the whole warp
-                    const float4 v = *reinterpret_cast<const float4*>(&S.p[r][p * 4]);
-                    const unsigned long long v0 = f2_pack(v.x, v.x), v1 = f2_pack(v.y, v.y),
-                                             v2 = f2_pack(v.z, v.z);
-                    float best = 1e20f;
-                    unsigned bi = 0;
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        // d = v - c * alpha with one rounding (c * -alpha is the exact negative
-                        // of c * alpha), dist = d2*d2 + (d0*d0 + d1*d1) in the reference's order
-                        const unsigned long long d0 = f2_fma(cc[0][i], nalpha2, v0);
-                        const unsigned long long d1 = f2_fma(cc[1][i], nalpha2, v1);
-                        const unsigned long long d2 = f2_fma(cc[2][i], nalpha2, v2);
-                        const unsigned long long dd = f2_fma(d2, d2, f2_fma(d0, d0, f2_mul(d1, d1)));
-                        float da, db;
-                        f2_unpack(dd, da, db);
-                        if (da < best) { best = da; bi = (unsigned)(lane * 8 + 2 * i); }
-                        if (db < best) { best = db; bi = (unsigned)(lane * 8 + 2 * i + 1); }
-                    }
-                    // warp minimum of (distance, index): a lane's best is a non-negative, non-NaN
-                    // float (it starts at 1e20 and only a strictly smaller distance replaces it),
-                    // so its bit pattern orders like the value and two hardware warp reductions do
-                    // the work of five shuffle-and-compare steps
-                    const unsigned best_bits = __reduce_min_sync(0xFFFFFFFFu, __float_as_uint(best));
-                    bi = __reduce_min_sync(0xFFFFFFFFu, (__float_as_uint(best) == best_bits) ? bi : 0xFFFFFFFFu);
-                    // The reference starts from min=1e20 with a strict '<': if no distance is below
-                    // 1e20 (NaN/inf input) it keeps code 0.
-                    if (!(__uint_as_float(best_bits) < 1e20f)) bi = 0;
-                    if (lane == 0) S.code[r][p] = (unsigned short)bi;
-                }
+                for (int r = 0; r < R; ++r)
+                    v_search_row(S.p[r], S.code[r], p, cc, nalpha2, lane);
+            } else {
+                for (int r = 0; r < nr; ++r) v_search_row(S.p[r], S.code[r], p, cc, nalpha2, lane);
             }
         }
         __syncwarp();
