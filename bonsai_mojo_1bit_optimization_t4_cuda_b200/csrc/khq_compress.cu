@@ -336,6 +336,12 @@ __device__ __forceinline__ unsigned long long f2_mul(unsigned long long a, unsig
     return r;
 }
 
+__device__ __forceinline__ float f_min3(float a, float b, float c) {
+    float d;
+    asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 // Code search of one (row, patch): every lane scans its 8 consecutive codes in ascending order, then
 // the warp takes the lexicographic (distance, index) minimum.  cc[k][i] = (code 2i, code 2i+1) of
 // dim k of the lane's 8 codes, as packed fp32 pairs.
@@ -344,8 +350,7 @@ __device__ __forceinline__ void v_search_row(const float* __restrict__ proj_row,
                                              unsigned long long nalpha2, int lane) {
     const float4 v = *reinterpret_cast<const float4*>(&proj_row[p * 4]);
     const unsigned long long v0 = f2_pack(v.x, v.x), v1 = f2_pack(v.y, v.y), v2 = f2_pack(v.z, v.z);
-    float best = 1e20f;
-    unsigned bl = 0;  // index among the lane's 8 codes
+    float dist[8];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         // d = v - c * alpha with one rounding (c * -alpha is the exact negative of c * alpha),
@@ -353,15 +358,20 @@ __device__ __forceinline__ void v_search_row(const float* __restrict__ proj_row,
         const unsigned long long d0 = f2_fma(cc[0][i], nalpha2, v0);
         const unsigned long long d1 = f2_fma(cc[1][i], nalpha2, v1);
         const unsigned long long d2 = f2_fma(cc[2][i], nalpha2, v2);
-        const unsigned long long dd = f2_fma(d2, d2, f2_fma(d0, d0, f2_mul(d1, d1)));
-        float da, db;
-        f2_unpack(dd, da, db);
-        if (da < best) { best = da; bl = 2 * i; }
-        if (db < best) { best = db; bl = 2 * i + 1; }
+        f2_unpack(f2_fma(d2, d2, f2_fma(d0, d0, f2_mul(d1, d1))), dist[2 * i], dist[2 * i + 1]);
     }
-    // warp minimum of (distance, index): a lane's best is a non-negative, non-NaN float (it starts
-    // at 1e20 and only a strictly smaller distance replaces it), so its bit pattern orders like
-    // the value and two hardware warp reductions do the work of five shuffle-and-compare steps
+    // The reference's ascending scan from 1e20 with a strict '<' ends on the smallest distance
+    // below 1e20 and on the first index that has it: the minimum first (three-input minima, which
+    // pass over a NaN), then the first index equal to it.
+    const float best = f_min3(f_min3(dist[0], dist[1], dist[2]), f_min3(dist[3], dist[4], dist[5]),
+                              f_min3(dist[6], dist[7], 1e20f));
+    unsigned bl = 7;  // index among the lane's 8 codes
+#pragma unroll
+    for (int i = 6; i >= 0; --i)
+        if (dist[i] == best) bl = i;
+    // warp minimum of (distance, index): a lane's best is a non-negative, non-NaN float (at most
+    // 1e20), so its bit pattern orders like the value and two hardware warp reductions do the
+    // work of five shuffle-and-compare steps
     const unsigned best_bits = __reduce_min_sync(0xFFFFFFFFu, __float_as_uint(best));
     unsigned bi = __reduce_min_sync(0xFFFFFFFFu, (__float_as_uint(best) == best_bits) ? (unsigned)(lane * 8) + bl : 0xFFFFFFFFu);
     // The reference starts from min=1e20 with a strict '<': if no distance is below 1e20
