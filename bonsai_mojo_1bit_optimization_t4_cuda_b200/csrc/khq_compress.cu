@@ -482,62 +482,62 @@ khq_compress_v_kernel(const __half* __restrict__ x, const __half* __restrict__ d
                 code[0] = pr & 0xFFFFu;
                 code[1] = pr >> 16;
             }
-        // per-patch energies, dim-3 centroid choice and residual (in the owning lane)
-        float e_true[2], e_vq[2], pres[2];
-        unsigned sel[2];
-        float max_res = 0.0f;
+            // per-patch energies, dim-3 centroid choice and residual (in the owning lane)
+            float e_true[2], e_vq[2], pres[2];
+            unsigned sel[2];
+            float max_res = 0.0f;
 #pragma unroll
-        for (int p = 0; p < 2; ++p) {
-            const int pid = lane * 2 + p;
-            const float v0 = proj[p * 4 + 0], v1 = proj[p * 4 + 1], v2 = proj[p * 4 + 2];
-            const __half* cbp = vq + ((size_t)pid * 256 + code[p]) * 3;
-            const float b0 = __half2float(cbp[0]) * alpha;
-            const float b1 = __half2float(cbp[1]) * alpha;
-            const float b2 = __half2float(cbp[2]) * alpha;
-            e_true[p] = __fmaf_rn(v2, v2, __fmaf_rn(v0, v0, v1 * v1));
-            e_vq[p] = __fmaf_rn(b2, b2, __fmaf_rn(b0, b0, b1 * b1));
-            const float v3 = proj[p * 4 + 3];
-            const float c0 = __half2float(cents[0 * D + pid * 4 + 3]);
-            const float c1 = __half2float(cents[1 * D + pid * 4 + 3]);
-            const float dist0 = fabsf(__fmaf_rn(-c0, alpha, v3));
-            const float dist1 = fabsf(__fmaf_rn(-c1, alpha, v3));
-            // ascending scan from min=1e20 with strict '<': index 1 only when strictly closer
-            unsigned s = 0;
-            float bd = 1e20f;
-            if (dist0 < bd) { bd = dist0; s = 0; }
-            if (dist1 < bd) { bd = dist1; s = 1; }
-            sel[p] = s;
-            const float cbest = s ? c1 : c0;
-            pres[p] = __fmaf_rn(-cbest, alpha, v3);
-            max_res = fmaxf(max_res, fabsf(pres[p]));
-            S.a[r][pid] = e_true[p];
-            S.b[r][pid] = e_vq[p];
-        }
+            for (int p = 0; p < 2; ++p) {
+                const int pid = lane * 2 + p;
+                const float v0 = proj[p * 4 + 0], v1 = proj[p * 4 + 1], v2 = proj[p * 4 + 2];
+                const __half* cbp = vq + ((size_t)pid * 256 + code[p]) * 3;
+                const float b0 = __half2float(cbp[0]) * alpha;
+                const float b1 = __half2float(cbp[1]) * alpha;
+                const float b2 = __half2float(cbp[2]) * alpha;
+                e_true[p] = __fmaf_rn(v2, v2, __fmaf_rn(v0, v0, v1 * v1));
+                e_vq[p] = __fmaf_rn(b2, b2, __fmaf_rn(b0, b0, b1 * b1));
+                const float v3 = proj[p * 4 + 3];
+                const float c0 = __half2float(cents[0 * D + pid * 4 + 3]);
+                const float c1 = __half2float(cents[1 * D + pid * 4 + 3]);
+                const float dist0 = fabsf(__fmaf_rn(-c0, alpha, v3));
+                const float dist1 = fabsf(__fmaf_rn(-c1, alpha, v3));
+                // ascending scan from min=1e20 with strict '<': index 1 only when strictly closer
+                unsigned s = 0;
+                float bd = 1e20f;
+                if (dist0 < bd) { bd = dist0; s = 0; }
+                if (dist1 < bd) { bd = dist1; s = 1; }
+                sel[p] = s;
+                const float cbest = s ? c1 : c0;
+                pres[p] = __fmaf_rn(-cbest, alpha, v3);
+                max_res = fmaxf(max_res, fabsf(pres[p]));
+                S.a[r][pid] = e_true[p];
+                S.b[r][pid] = e_vq[p];
+            }
 #pragma unroll
-        for (int m = 16; m > 0; m >>= 1)
-            max_res = fmaxf(max_res, __shfl_xor_sync(0xFFFFFFFFu, max_res, m));
-        if (lane == 0) *reinterpret_cast<float*>(out_shared_meta + row * 4) = max_res;
-        const float rs = fmaxf(max_res, 1e-4f);
-        unsigned f24 = 0, hb = 0;
+            for (int m = 16; m > 0; m >>= 1)
+                max_res = fmaxf(max_res, __shfl_xor_sync(0xFFFFFFFFu, max_res, m));
+            if (lane == 0) *reinterpret_cast<float*>(out_shared_meta + row * 4) = max_res;
+            const float rs = fmaxf(max_res, 1e-4f);
+            unsigned f24 = 0, hb = 0;
 #pragma unroll
-        for (int p = 0; p < 2; ++p) {
-            const float scaled = __fmaf_rn(__fdiv_rn(pres[p], rs), 7.0f, 8.0f);
-            const unsigned dump = (unsigned)fmaxf(0.0f, fminf(15.0f, roundf(scaled)));
-            const unsigned f = (code[p] & 0x7Fu) | ((sel[p] & 1u) << 7) | ((dump & 0xFu) << 8);
-            f24 |= f << (12 * p);
-            hb |= ((code[p] >> 7) & 1u) << p;
-        }
-        // 8 patches = 4 lanes = 96 bits = 3 words; lane k of the quad holds bits [24k, 24k+24)
-        const unsigned nxt = __shfl_down_sync(0xFFFFFFFFu, f24, 1);
-        unsigned int* prow = reinterpret_cast<unsigned int*>(out_payload + row * V_PAY);
-        const int k4 = lane & 3, g = lane >> 2;
-        if (k4 == 0) prow[g * 3 + 0] = f24 | (nxt << 24);
-        else if (k4 == 1) prow[g * 3 + 1] = (f24 >> 8) | (nxt << 16);
-        else if (k4 == 2) prow[g * 3 + 2] = (f24 >> 16) | (nxt << 8);
-        const unsigned hv = hb << (2 * (lane & 15));
-        const unsigned lo = __reduce_or_sync(0xFFFFFFFFu, lane < 16 ? hv : 0u);
-        const unsigned hi = __reduce_or_sync(0xFFFFFFFFu, lane >= 16 ? hv : 0u);
-        if (lane == 0) { prow[24] = lo; prow[25] = hi; }
+            for (int p = 0; p < 2; ++p) {
+                const float scaled = __fmaf_rn(__fdiv_rn(pres[p], rs), 7.0f, 8.0f);
+                const unsigned dump = (unsigned)fmaxf(0.0f, fminf(15.0f, roundf(scaled)));
+                const unsigned f = (code[p] & 0x7Fu) | ((sel[p] & 1u) << 7) | ((dump & 0xFu) << 8);
+                f24 |= f << (12 * p);
+                hb |= ((code[p] >> 7) & 1u) << p;
+            }
+            // 8 patches = 4 lanes = 96 bits = 3 words; lane k of the quad holds bits [24k, 24k+24)
+            const unsigned nxt = __shfl_down_sync(0xFFFFFFFFu, f24, 1);
+            unsigned int* prow = reinterpret_cast<unsigned int*>(out_payload + row * V_PAY);
+            const int k4 = lane & 3, g = lane >> 2;
+            if (k4 == 0) prow[g * 3 + 0] = f24 | (nxt << 24);
+            else if (k4 == 1) prow[g * 3 + 1] = (f24 >> 8) | (nxt << 16);
+            else if (k4 == 2) prow[g * 3 + 2] = (f24 >> 16) | (nxt << 8);
+            const unsigned hv = hb << (2 * (lane & 15));
+            const unsigned lo = __reduce_or_sync(0xFFFFFFFFu, lane < 16 ? hv : 0u);
+            const unsigned hi = __reduce_or_sync(0xFFFFFFFFu, lane >= 16 ? hv : 0u);
+            if (lane == 0) { prow[24] = lo; prow[25] = hi; }
         }
         __syncwarp();
         // the two energy sums strictly in patch order, the R rows at once
