@@ -167,6 +167,11 @@ def test_library_loads_and_exports_every_declared_symbol():
     assert len({a, b, c}) == 3 and L.khq_state_slot(7) == a and L.khq_state_slot(-1) == a
     assert L.launch_khq_compress_fp16(0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 256, 1.0, 1.0, 0, 0) == -100
     assert L.launch_khq_merge_gate_fp16(0, 0, 0, 0, 0, 256, 1, 0) == -100
+    # the table-driven compress launch: no runs, a wrong head_dim, a source offset off the 16-byte grid
+    null9 = [0] * 9
+    assert L.launch_khq_compress_batched_fp16(0, 0, 512, *null9, 256, 1.0, 1.0, 0, 0, 0) == -100
+    assert L.launch_khq_compress_batched_fp16(1, 1, 512, *null9, 128, 1.0, 1.0, 0, 0, 0) == -100
+    assert L.launch_khq_compress_batched_fp16(1, 1, 512, *null9, 256, 1.0, 1.0, 1, 8, 0) == -104
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
